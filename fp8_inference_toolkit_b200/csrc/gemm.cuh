@@ -1,0 +1,52 @@
+// W4A4 tile GEMM for sm_100a: declarations shared by the dense and the MoE entry points.
+#pragma once
+#include "common.cuh"
+#include <cuda.h>
+
+namespace i4tc {
+
+// How the epilogue turns int32 accumulators into the output.
+enum EpiMode : int {
+  EPI_INT32 = 0,        // one flush per tile: out int32 = acc
+  EPI_CHANNEL = 1,      // one flush per tile: out = cast((acc * s_col) * s_row)  (reference order b then a)
+  EPI_GROUP = 2,        // a flush per K-group: f += (acc_g * sa[g,m]) * sb[g,n]; out = bf16(f)
+  EPI_GROUP_INT32 = 3,  // a flush per K-group: out int32 [G, M, N] = acc_g
+};
+
+// One GEMM problem as the kernel sees it.  "P" is the operand on the 128-row side of the MMA
+// (TMEM lanes), "Q" the operand on the BN-column side.  Normally P = activations (rows m) and
+// Q = weights (rows n); with `swap` set P = weights and Q = activations (small M).
+struct GemmParams {
+  int P_rows;        // valid rows of the P operand (dense) or total sorted rows (MoE)
+  int Q_rows;        // valid rows of the Q operand
+  int G;             // number of 128-element K groups
+  int p_rowmajor;    // 1: P tensor map is 2-D [rows, K/2] (x = g*64); 0: 3-D [G', rows, 64] (z = g)
+  int q_rowmajor;
+  int swap;          // output element (p, q) is out[q, p] instead of out[p, q]
+  int epi_mode;      // EpiMode
+  int out_dtype;     // I4TC_BF16 / I4TC_FP16 / I4TC_INT32
+  const float* sp;   // P-side scales, element (g, p) at sp[g * sp_gstride + p]
+  const float* sq;   // Q-side scales, element (g, q) at sq[g * sq_gstride + q]
+  long long sp_gstride;
+  long long sq_gstride;
+  void* out;
+  long long ldc;        // row stride of out in elements
+  long long out_gstride;// EPI_GROUP_INT32: elements between consecutive groups
+  int num_p_tiles;   // dense only
+  int num_q_tiles;
+  // MoE: rows [expert_offsets[e], expert_offsets[e+1]) of P use Q slab e.
+  const int* expert_offsets;  // nullptr for a dense problem
+  int num_experts;
+  long long sq_estride;  // floats between experts in sq
+  unsigned int* status;  // device status word, bit 0 = a bounded wait expired
+};
+
+int launch_w4a4_gemm(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int bn, int grid,
+                     cudaStream_t st);
+
+// Builds (or fetches from a small per-device cache) a tensor map over packed int4 data.
+// rowmajor: 2-D view [rows, row_bytes]; otherwise 3-D view [slabs, rows, 64].
+int get_tensor_map(int device, const void* base, bool rowmajor, long long rows, long long row_bytes_or_slabs,
+                   int box_rows, CUtensorMap* out);
+
+}  // namespace i4tc

@@ -1,0 +1,222 @@
+// Host side of the dense and MoE W4A4 GEMM entry points: argument checks, tensor maps,
+// tile-shape choice and launch.
+#include "gemm.cuh"
+
+namespace i4tc {
+
+static int g_force_bn = 0;    // 0 = choose automatically
+static int g_force_swap = -1; // -1 = choose automatically
+
+struct Shape {
+  int bn;
+  bool swap;
+};
+
+// Picks the tile width and operand orientation.  Small M puts the weights on the 128-row side of
+// the MMA (so that no tensor-core rows are wasted on padding and more CTAs stream weights);
+// otherwise the width with the fewest (cost-weighted) waves over the SMs wins.
+static Shape choose_shape(long long M, long long N, int sms, bool allow_swap) {
+  Shape s;
+  s.swap = allow_swap && M <= 128;
+  if (g_force_swap >= 0 && allow_swap) s.swap = g_force_swap != 0;
+  if (g_force_bn) {
+    s.bn = g_force_bn;
+    return s;
+  }
+  if (s.swap) {
+    s.bn = M <= 64 ? 64 : 128;
+    return s;
+  }
+  const long long mt = (M + 127) / 128;
+  double best = 1e30;
+  s.bn = 256;
+  const int cands[2] = {256, 128};
+  for (int c = 0; c < 2; ++c) {
+    const int bn = cands[c];
+    const long long tiles = mt * ((N + bn - 1) / bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    const double cost = (double)waves * bn * (bn == 128 ? 1.08 : 1.0);
+    if (cost < best) {
+      best = cost;
+      s.bn = bn;
+    }
+  }
+  return s;
+}
+
+struct DenseArgs {
+  const uint8_t* a;
+  const uint8_t* b;
+  const float* sa;
+  const float* sb;
+  void* out;
+  int out_dtype;
+  long long M, N;
+  int G;
+  bool rowmajor;    // operands are [rows, K/2] (else group-major [G, rows, 64])
+  long long K;      // only for rowmajor
+  int epi_mode;
+};
+
+static int run_dense(const DenseArgs& d, int device, void* stream) {
+  const DeviceInfo* info;
+  if (int rc = device_info(device, &info)) return rc;
+  I4TC_REQUIRE(info->cc_major == 10, I4TC_EDEVICE, "device %d is sm_%d%d; this library needs sm_100", device,
+               info->cc_major, info->cc_minor);
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  I4TC_REQUIRE(d.M < (1ll << 31) - 256 && d.N < (1ll << 31) - 256, I4TC_EINVAL, "M or N too large");
+
+  const Shape sh = choose_shape(d.M, d.N, info->sm_count, true);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.G = d.G;
+  p.swap = sh.swap ? 1 : 0;
+  p.epi_mode = d.epi_mode;
+  p.out_dtype = d.out_dtype;
+  p.out = d.out;
+  p.ldc = d.N;
+  p.out_gstride = d.M * d.N;
+  p.status = info->status;
+  p.p_rowmajor = p.q_rowmajor = d.rowmajor ? 1 : 0;
+  const bool per_group_scales = d.epi_mode == EPI_GROUP;
+  const uint8_t *pbase, *qbase;
+  long long prow, qrow;
+  if (!sh.swap) {
+    pbase = d.a; qbase = d.b; prow = d.M; qrow = d.N;
+    p.sp = d.sa; p.sq = d.sb;
+    p.sp_gstride = per_group_scales ? d.M : 0;
+    p.sq_gstride = per_group_scales ? d.N : 0;
+  } else {
+    pbase = d.b; qbase = d.a; prow = d.N; qrow = d.M;
+    p.sp = d.sb; p.sq = d.sa;
+    p.sp_gstride = per_group_scales ? d.N : 0;
+    p.sq_gstride = per_group_scales ? d.M : 0;
+  }
+  p.P_rows = (int)prow;
+  p.Q_rows = (int)qrow;
+  p.num_p_tiles = (int)((prow + 127) / 128);
+  p.num_q_tiles = (int)((qrow + sh.bn - 1) / sh.bn);
+  const long long tiles = (long long)p.num_p_tiles * p.num_q_tiles;
+  I4TC_REQUIRE(tiles < (1ll << 31), I4TC_EINVAL, "too many tiles");
+
+  CUtensorMap tmP, tmQ;
+  const long long extent = d.rowmajor ? d.K / 2 : (long long)d.G;
+  if (int rc = get_tensor_map(device, pbase, d.rowmajor, prow, extent, 128, &tmP)) return rc;
+  if (int rc = get_tensor_map(device, qbase, d.rowmajor, qrow, extent, sh.bn, &tmQ)) return rc;
+  const int grid = (int)(tiles < info->sm_count ? tiles : info->sm_count);
+  return launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, static_cast<cudaStream_t>(stream));
+}
+
+static int check_dense_common(const void* a, const void* b, const void* out, long long M, long long N) {
+  I4TC_REQUIRE(M >= 0 && N >= 0, I4TC_EINVAL, "negative size");
+  if (M == 0 || N == 0) return 1;  // nothing to do
+  I4TC_REQUIRE(a && b && out, I4TC_EINVAL, "null pointer");
+  return I4TC_OK;
+}
+
+}  // namespace i4tc
+
+using namespace i4tc;
+
+extern "C" int i4tc_set_tuning(int tile_n, int swap) {
+  I4TC_REQUIRE(tile_n == 0 || tile_n == 64 || tile_n == 128 || tile_n == 256, I4TC_EINVAL,
+               "tile_n must be 0 (automatic), 64, 128 or 256");
+  I4TC_REQUIRE(swap >= -1 && swap <= 1, I4TC_EINVAL, "swap must be -1 (automatic), 0 or 1");
+  g_force_bn = tile_n;
+  g_force_swap = swap;
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_gemm_int32(const uint8_t* a, const uint8_t* b, int32_t* c, int64_t M, int64_t N, int64_t K,
+                               int device, void* stream) {
+  I4TC_REQUIRE(K > 0 && K % 64 == 0, I4TC_EINVAL, "K must be a positive multiple of 64");
+  I4TC_REQUIRE(K <= 65536, I4TC_EINVAL, "K must not exceed 65536");
+  int rc = check_dense_common(a, b, c, M, N);
+  if (rc) return rc < 0 ? rc : I4TC_OK;
+  DenseArgs d{a, b, nullptr, nullptr, c, I4TC_INT32, M, N, (int)((K + 127) / 128), true, K, EPI_INT32};
+  return run_dense(d, device, stream);
+}
+
+extern "C" int i4tc_gemm_scaled(const uint8_t* a, const uint8_t* b, const float* scale_a, const float* scale_b,
+                                void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int device,
+                                void* stream) {
+  I4TC_REQUIRE(K > 0 && K % 64 == 0, I4TC_EINVAL, "K must be a positive multiple of 64");
+  I4TC_REQUIRE(K <= 65536, I4TC_EINVAL, "K must not exceed 65536");
+  I4TC_REQUIRE(out_dtype == I4TC_BF16 || out_dtype == I4TC_FP16, I4TC_EUNSUPPORTED, "out must be bf16 or fp16");
+  int rc = check_dense_common(a, b, out, M, N);
+  if (rc) return rc < 0 ? rc : I4TC_OK;
+  I4TC_REQUIRE(scale_a && scale_b, I4TC_EINVAL, "null scale pointer");
+  DenseArgs d{a, b, scale_a, scale_b, out, out_dtype, M, N, (int)((K + 127) / 128), true, K, EPI_CHANNEL};
+  return run_dense(d, device, stream);
+}
+
+extern "C" int i4tc_gemm_grouped(const uint8_t* a, const uint8_t* b, const float* scale_a, const float* scale_b,
+                                 void* out, int64_t M, int64_t N, int64_t group_size, int64_t num_groups,
+                                 int device, void* stream) {
+  I4TC_REQUIRE(group_size == 128, I4TC_EUNSUPPORTED, "fused grouped GEMM only supports group_size=128");
+  I4TC_REQUIRE(num_groups > 0 && num_groups <= 512, I4TC_EINVAL, "num_groups must be in [1, 512]");
+  int rc = check_dense_common(a, b, out, M, N);
+  if (rc) return rc < 0 ? rc : I4TC_OK;
+  I4TC_REQUIRE(scale_a && scale_b, I4TC_EINVAL, "null scale pointer");
+  DenseArgs d{a, b, scale_a, scale_b, out, I4TC_BF16, M, N, (int)num_groups, false, 0, EPI_GROUP};
+  return run_dense(d, device, stream);
+}
+
+extern "C" int i4tc_gemm_grouped_int32(const uint8_t* a, const uint8_t* b, int32_t* out, int64_t M, int64_t N,
+                                       int64_t num_groups, int device, void* stream) {
+  I4TC_REQUIRE(num_groups > 0 && num_groups <= 512, I4TC_EINVAL, "num_groups must be in [1, 512]");
+  int rc = check_dense_common(a, b, out, M, N);
+  if (rc) return rc < 0 ? rc : I4TC_OK;
+  DenseArgs d{a, b, nullptr, nullptr, out, I4TC_INT32, M, N, (int)num_groups, false, 0, EPI_GROUP_INT32};
+  return run_dense(d, device, stream);
+}
+
+extern "C" int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, const uint8_t* b,
+                                     const float* scale_b, const int32_t* expert_offsets, void* out,
+                                     int64_t num_pairs, int64_t N, int64_t num_groups, int64_t num_experts,
+                                     int device, void* stream) {
+  I4TC_REQUIRE(num_pairs >= 0 && N >= 0, I4TC_EINVAL, "negative size");
+  I4TC_REQUIRE(num_groups > 0 && num_groups <= 512, I4TC_EINVAL, "num_groups must be in [1, 512]");
+  I4TC_REQUIRE(num_experts > 0 && num_experts <= 65536, I4TC_EINVAL, "num_experts out of range");
+  if (num_pairs == 0 || N == 0) return I4TC_OK;
+  I4TC_REQUIRE(a && b && scale_a && scale_b && expert_offsets && out, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(num_pairs < (1ll << 31) - 256 && N * num_experts < (1ll << 31), I4TC_EINVAL, "sizes too large");
+  const DeviceInfo* info;
+  if (int rc = device_info(device, &info)) return rc;
+  I4TC_REQUIRE(info->cc_major == 10, I4TC_EDEVICE, "device %d is sm_%d%d; this library needs sm_100", device,
+               info->cc_major, info->cc_minor);
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+
+  // Average rows per expert decide the tile width: narrow tiles keep more SMs busy when the
+  // per-expert problems are small.
+  int bn = g_force_bn ? g_force_bn : 128;
+  if (!g_force_bn && N % 256 == 0 && num_pairs / num_experts >= 512) bn = 256;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.P_rows = (int)num_pairs;
+  p.Q_rows = (int)N;
+  p.G = (int)num_groups;
+  p.epi_mode = EPI_GROUP;
+  p.out_dtype = I4TC_BF16;
+  p.sp = scale_a;
+  p.sq = scale_b;
+  p.sp_gstride = num_pairs;
+  p.sq_gstride = N;
+  p.sq_estride = num_groups * N;
+  p.out = out;
+  p.ldc = N;
+  p.num_q_tiles = (int)((N + bn - 1) / bn);
+  p.expert_offsets = expert_offsets;
+  p.num_experts = (int)num_experts;
+  p.status = info->status;
+  CUtensorMap tmP, tmQ;
+  if (int rc = get_tensor_map(device, a, false, num_pairs, num_groups, 128, &tmP)) return rc;
+  // weights of all experts as one [E*G, N, 64] stack
+  if (int rc = get_tensor_map(device, b, false, N, num_experts * num_groups, bn, &tmQ)) return rc;
+  // upper bound on tiles: every expert may add one partial row tile
+  const long long max_tiles = ((num_pairs + 127) / 128 + num_experts) * p.num_q_tiles;
+  const int grid = (int)(max_tiles < info->sm_count ? max_tiles : info->sm_count);
+  return launch_w4a4_gemm(p, tmP, tmQ, bn, grid, static_cast<cudaStream_t>(stream));
+}

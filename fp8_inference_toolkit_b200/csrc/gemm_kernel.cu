@@ -1,0 +1,600 @@
+// Persistent warp-specialised W4A4 GEMM kernel for sm_100a (tcgen05 + TMEM + TMA).
+//
+// sm_100 tensor cores have no int4 MMA kind, so packed int4 tiles are staged by TMA, expanded
+// to int8 by converter warps and multiplied with tcgen05.mma kind::i8 into int32 accumulators
+// that live in tensor memory.  One K group of 128 codes is exactly one 128-byte swizzled row of
+// int8, i.e. four K=32 MMAs.
+//
+// Expansion trick: a nibble moved to the top of its byte is the code times 16 as a signed int8
+//   hi = w & 0xF0F0F0F0          (odd elements)      lo = (w << 4) & 0xF0F0F0F0   (even elements)
+// so both operands carry 16*code, every product is 256*(a*b) and the int32 accumulator is exactly
+// 256 times the true sum (|256 * 64 * K| < 2^31 for K <= 65536).  The factor is removed exactly
+// in the epilogue (arithmetic shift, or a 2^-8 folded into a scale).  Even and odd elements of a
+// 32-code chunk land in different 16-byte K slots; A and B use the same permutation, and integer
+// sums do not depend on the order of k.
+//
+// Roles (512 threads):
+//   warp 0      TMA producer: packed P (128 x 64 B) and Q (BN x 64 B) tiles, one K group per stage
+//   warp 1      MMA issuer (one lane) and owner of the TMEM allocation
+//   warps 4-7   converters: packed stage -> 128B-swizzled K-major int8 stage
+//   warps 8-15  epilogue: tcgen05.ld, int32 -> fp32, scales, fp32 accumulation across groups, store
+// Two TMEM accumulators (2 x BN columns) let group g+1 be multiplied while group g is drained.
+// Every wait is bounded: on expiry the kernel sets bit 0 of the status word, all roles leave
+// their loops, TMEM is released and the kernel returns.
+#include "gemm.cuh"
+#include "ptx.cuh"
+
+namespace i4tc {
+
+using namespace ptx;
+
+constexpr int kBM = 128;             // rows of the P tile == TMEM lanes
+constexpr int kPackedRow = 64;       // bytes of one packed row of one group
+constexpr int kI8Row = 128;          // bytes of one int8 row of one group (the swizzle width)
+constexpr int kThreads = 512;
+constexpr int kConvWarp0 = 4, kConvWarps = 4;
+constexpr int kEpiWarp0 = 8, kEpiWarps = 8;
+constexpr int kNI = 2;               // int8 stages
+// register budgets per role (whole warpgroups): 128*56 + 128*72 + 256*192 = 65536
+constexpr int kRegsWg0 = 56, kRegsConv = 72, kRegsEpi = 192;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+
+template <int BN>
+struct Cfg {
+  static constexpr int NP = (BN >= 256) ? 5 : 6;                       // packed stages
+  static constexpr int PK_P = kBM * kPackedRow;                        // 8 KB
+  static constexpr int PK_Q = BN * kPackedRow;
+  static constexpr int I8_P = kBM * kI8Row;                            // 16 KB
+  static constexpr int I8_Q = BN * kI8Row;
+  static constexpr int COLS_PER_WARP = BN / 2;                         // epilogue columns per thread
+  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;        // power of two for BN in {16..256}
+  // shared memory layout (offsets from a 1024-byte aligned base)
+  static constexpr int OFF_I8 = 0;
+  static constexpr int OFF_PK = OFF_I8 + kNI * (I8_P + I8_Q);
+  static constexpr int OFF_SQ = OFF_PK + NP * (PK_P + PK_Q);          // per-warp column scales, 2 buffers
+  static constexpr int OFF_BAR = OFF_SQ + kEpiWarps * 2 * COLS_PER_WARP * 4;
+  static constexpr int NUM_BARS = 2 * NP + 2 * kNI + 4;
+  static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // tmem ptr, abort flag
+  static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;              // + alignment slack
+};
+
+struct TileInfo {
+  int p0, q0;        // first row of the P / Q tile
+  int p_lim, q_lim;  // exclusive row limits for output
+  int zq;            // slab offset of the Q operand (MoE: expert * G)
+  long long sq_off;  // float offset into sq (MoE: expert * sq_estride)
+};
+
+// Static persistent schedule: CTA b takes tiles b, b + grid, ...  P tiles vary fastest so that
+// CTAs running together share Q (weight) tiles in L2.
+struct Sched {
+  int tile;
+  int e;
+  int tile_base;
+  __device__ Sched() : tile(blockIdx.x), e(0), tile_base(0) {}
+  template <int BN>
+  __device__ bool next(const GemmParams& p, TileInfo& ti) {
+    if (p.expert_offsets == nullptr) {
+      if (tile >= p.num_p_tiles * p.num_q_tiles) return false;
+      const int pt = tile % p.num_p_tiles, qt = tile / p.num_p_tiles;
+      ti.p0 = pt * kBM; ti.q0 = qt * BN; ti.p_lim = p.P_rows; ti.q_lim = p.Q_rows; ti.zq = 0; ti.sq_off = 0;
+    } else {
+      for (;;) {
+        if (e >= p.num_experts) return false;
+        const int r0 = __ldg(p.expert_offsets + e), r1 = __ldg(p.expert_offsets + e + 1);
+        const int npt = (r1 - r0 + kBM - 1) / kBM;
+        const int nt = npt * p.num_q_tiles;
+        if (tile < tile_base + nt) {
+          const int local = tile - tile_base;
+          const int pt = local % npt, qt = local / npt;
+          ti.p0 = r0 + pt * kBM; ti.p_lim = r1; ti.q0 = qt * BN; ti.q_lim = p.Q_rows;
+          ti.zq = e * p.G; ti.sq_off = (long long)e * p.sq_estride;
+          break;
+        }
+        tile_base += nt; ++e;
+      }
+    }
+    tile += gridDim.x;
+    return true;
+  }
+};
+
+// Bounded mbarrier wait, uniform across the warp.  Returns false (and raises the abort flag)
+// when the limit expires or another role has already aborted.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  bool ok = mbar_try_wait(bar, parity);
+  if (!ok) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+      ok = mbar_try_wait(bar, parity);
+      if (ok) break;
+      if ((++spins & 63u) == 0) {
+        if (*abort_flag) break;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+      }
+    }
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (!ok) *abort_flag = 1;
+  return ok;
+}
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+  // K-major, 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart (SBO), LBO unused (1),
+  // descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
+  // D = S32 (2 << 4), A = B = signed int8 (1 << 7, 1 << 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+// Expand one packed tile (rows x 64 B, dense) into a swizzled int8 tile (rows x 128 B).
+// 16-byte packed chunk j of a row becomes int8 chunks 2j (even codes) and 2j+1 (odd codes).
+template <int ROWS>
+__device__ __forceinline__ void convert_tile(uint32_t pk, uint32_t i8, int tid) {
+  constexpr int CHUNKS = ROWS * 4;
+  constexpr int PER_THREAD = CHUNKS / (kConvWarps * 32);
+  static_assert(CHUNKS % (kConvWarps * 32) == 0, "tile rows must be a multiple of 32");
+#pragma unroll
+  for (int i0 = 0; i0 < PER_THREAD; i0 += 4) {
+    uint4 w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (i0 + i < PER_THREAD) w[i] = lds128(pk + (uint32_t)(tid + (i0 + i) * kConvWarps * 32) * 16u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (i0 + i < PER_THREAD) {
+        const int q = tid + (i0 + i) * kConvWarps * 32;
+        const int row = q >> 2, j = q & 3;
+        uint4 lo, hi;
+        lo.x = (w[i].x << 4) & 0xF0F0F0F0u; hi.x = w[i].x & 0xF0F0F0F0u;
+        lo.y = (w[i].y << 4) & 0xF0F0F0F0u; hi.y = w[i].y & 0xF0F0F0F0u;
+        lo.z = (w[i].z << 4) & 0xF0F0F0F0u; hi.z = w[i].z & 0xF0F0F0F0u;
+        lo.w = (w[i].w << 4) & 0xF0F0F0F0u; hi.w = w[i].w & 0xF0F0F0F0u;
+        const uint32_t c0 = (uint32_t)((2 * j) ^ (row & 7));
+        const uint32_t base = i8 + (uint32_t)row * kI8Row;
+        sts128(base + c0 * 16u, lo);
+        sts128(base + (c0 ^ 1u) * 16u, hi);
+      }
+    }
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT cast_out(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 cast_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half cast_out<__half>(float v) { return __float2half_rn(v); }
+
+// Stores 32 consecutive output values of one tile row (normal) or 32 values of one tile column
+// spread over 32 rows (swap).  `vals` are fp32 (cast to OutT) or raw int32.
+template <typename OutT>
+__device__ __forceinline__ void store_chunk_f(const GemmParams& p, const float (&v)[32], int prow, int qcol0,
+                                              const TileInfo& ti) {
+  OutT* out = static_cast<OutT*>(p.out);
+  if (prow >= ti.p_lim) return;
+  if (!p.swap) {
+    OutT* dst = out + (long long)prow * p.ldc + qcol0;
+    const bool vec = (qcol0 + 32 <= ti.q_lim) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        union { OutT h[8]; uint4 u; } pk;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) pk.h[k] = cast_out<OutT>(v[i + k]);
+        *reinterpret_cast<uint4*>(dst + i) = pk.u;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (qcol0 + i < ti.q_lim) dst[i] = cast_out<OutT>(v[i]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (qcol0 + i < ti.q_lim) out[(long long)(qcol0 + i) * p.ldc + prow] = cast_out<OutT>(v[i]);
+  }
+}
+
+__device__ __forceinline__ void store_chunk_i(const GemmParams& p, int32_t* out, const uint32_t (&r)[32], int prow,
+                                              int qcol0, const TileInfo& ti) {
+  if (prow >= ti.p_lim) return;
+  if (!p.swap) {
+    int32_t* dst = out + (long long)prow * p.ldc + qcol0;
+    const bool vec = (qcol0 + 32 <= ti.q_lim) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        int4 o = make_int4(((int32_t)r[i]) >> 8, ((int32_t)r[i + 1]) >> 8, ((int32_t)r[i + 2]) >> 8,
+                           ((int32_t)r[i + 3]) >> 8);
+        *reinterpret_cast<int4*>(dst + i) = o;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (qcol0 + i < ti.q_lim) dst[i] = ((int32_t)r[i]) >> 8;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (qcol0 + i < ti.q_lim) out[(long long)(qcol0 + i) * p.ldc + prow] = ((int32_t)r[i]) >> 8;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Epilogue bodies
+// ------------------------------------------------------------------------------------------
+// Per-group accumulate: a flush per K group, fp32 running sums in registers.
+template <int BN, typename OutT>
+__device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
+                                               uint32_t bar_tm_full, uint32_t bar_tm_empty,
+                                               volatile int* abort_flag) {
+  using C = Cfg<BN>;
+  constexpr int NCH = C::COLS_PER_WARP / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ew = warp - kEpiWarp0;
+  const int quad = warp & 3;         // TMEM lane quarter this warp may access
+  const int half = ew >> 2;          // which half of the BN columns
+  const int col_base = half * C::COLS_PER_WARP;
+  float* sq_s = reinterpret_cast<float*>(smem + C::OFF_SQ) + ew * 2 * C::COLS_PER_WARP;
+  // order of the two multiplies: normal (p = m): (acc * sp) * sq ; swapped (p = n): (acc * sq) * sp
+  const bool pq_order = !p.swap;
+  constexpr float kInv256 = 1.0f / 256.0f;
+
+  Sched sched;
+  TileInfo ti;
+  uint32_t flush = 0;
+  while (sched.next<BN>(p, ti)) {
+    float f[C::COLS_PER_WARP];
+#pragma unroll
+    for (int i = 0; i < C::COLS_PER_WARP; ++i) f[i] = 0.f;
+    const int prow = ti.p0 + quad * 32 + lane;
+    const bool prow_ok = prow < ti.p_lim;
+    __syncwarp();  // the previous tile's last reads of sq_s precede this tile's first writes
+    // software-pipelined scale fetch: values for group g+1 are requested while group g is drained
+    float sp_next = 0.f, sq_next[NCH];
+    auto fetch = [&](int g) {
+      sp_next = prow_ok ? __ldg(p.sp + (long long)g * p.sp_gstride + prow) : 0.f;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int q = ti.q0 + col_base + c * 32 + lane;
+        sq_next[c] = (q < ti.q_lim) ? __ldg(p.sq + ti.sq_off + (long long)g * p.sq_gstride + q) : 0.f;
+      }
+    };
+    fetch(0);
+    bool ok = true;
+    for (int g = 0; g < p.G; ++g) {
+      float* sq_buf = sq_s + (g & 1) * C::COLS_PER_WARP;
+      const float sp = sp_next * (pq_order ? kInv256 : 1.0f);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) sq_buf[c * 32 + lane] = sq_next[c] * (pq_order ? 1.0f : kInv256);
+      __syncwarp();
+      if (g + 1 < p.G) fetch(g + 1);
+      const uint32_t buf = flush & 1u;
+      ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (c == NCH - 1) {
+          // all of this warp's columns of the buffer are in registers: hand it back to the MMA warp
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tm_empty + buf * 8);
+        }
+        if (pq_order) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 s = *reinterpret_cast<const float4*>(sq_buf + c * 32 + i);
+            f[c * 32 + i + 0] = fmaf(__int2float_rn((int32_t)r[i + 0]) * sp, s.x, f[c * 32 + i + 0]);
+            f[c * 32 + i + 1] = fmaf(__int2float_rn((int32_t)r[i + 1]) * sp, s.y, f[c * 32 + i + 1]);
+            f[c * 32 + i + 2] = fmaf(__int2float_rn((int32_t)r[i + 2]) * sp, s.z, f[c * 32 + i + 2]);
+            f[c * 32 + i + 3] = fmaf(__int2float_rn((int32_t)r[i + 3]) * sp, s.w, f[c * 32 + i + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 s = *reinterpret_cast<const float4*>(sq_buf + c * 32 + i);
+            f[c * 32 + i + 0] = fmaf(__int2float_rn((int32_t)r[i + 0]) * s.x, sp, f[c * 32 + i + 0]);
+            f[c * 32 + i + 1] = fmaf(__int2float_rn((int32_t)r[i + 1]) * s.y, sp, f[c * 32 + i + 1]);
+            f[c * 32 + i + 2] = fmaf(__int2float_rn((int32_t)r[i + 2]) * s.z, sp, f[c * 32 + i + 2]);
+            f[c * 32 + i + 3] = fmaf(__int2float_rn((int32_t)r[i + 3]) * s.w, sp, f[c * 32 + i + 3]);
+          }
+        }
+      }
+      ++flush;
+    }
+    if (!ok) break;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = f[c * 32 + i];
+      store_chunk_f<OutT>(p, v, prow, ti.q0 + col_base + c * 32, ti);
+    }
+  }
+}
+
+// One flush per tile (EPI_INT32, EPI_CHANNEL) or raw per-group dumps (EPI_GROUP_INT32).
+template <int BN, typename OutT>
+__device__ __forceinline__ void epilogue_simple(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
+                                                uint32_t bar_tm_full, uint32_t bar_tm_empty,
+                                                volatile int* abort_flag) {
+  using C = Cfg<BN>;
+  constexpr int NCH = C::COLS_PER_WARP / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ew = warp - kEpiWarp0;
+  const int quad = warp & 3;
+  const int half = ew >> 2;
+  const int col_base = half * C::COLS_PER_WARP;
+  float* sq_s = reinterpret_cast<float*>(smem + C::OFF_SQ) + ew * 2 * C::COLS_PER_WARP;
+  const bool per_group = p.epi_mode == EPI_GROUP_INT32;
+  const int nflush = per_group ? p.G : 1;
+  constexpr float kInv256 = 1.0f / 256.0f;
+  // reference order (acc * scale_b[n]) * scale_a[m]: normal -> column scale first; swapped -> row scale first
+  const bool q_first = !p.swap;
+
+  Sched sched;
+  TileInfo ti;
+  uint32_t flush = 0;
+  bool ok = true;
+  while (ok && sched.next<BN>(p, ti)) {
+    const int prow = ti.p0 + quad * 32 + lane;
+    float sp = 0.f;
+    if (p.epi_mode == EPI_CHANNEL) {
+      sp = (prow < ti.p_lim) ? __ldg(p.sp + prow) : 0.f;
+      if (!q_first) sp *= kInv256;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int q = ti.q0 + col_base + c * 32 + lane;
+        const float s = (q < ti.q_lim) ? __ldg(p.sq + ti.sq_off + q) : 0.f;
+        sq_s[c * 32 + lane] = q_first ? s * kInv256 : s;
+      }
+      __syncwarp();
+    }
+    for (int fl = 0; fl < nflush; ++fl) {
+      const uint32_t buf = flush & 1u;
+      ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (c == NCH - 1) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tm_empty + buf * 8);
+        }
+        const int qcol0 = ti.q0 + col_base + c * 32;
+        if (p.epi_mode == EPI_CHANNEL) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float a = __int2float_rn((int32_t)r[i]);
+            const float s = sq_s[c * 32 + i];
+            v[i] = q_first ? (a * s) * sp : (a * sp) * s;
+          }
+          store_chunk_f<OutT>(p, v, prow, qcol0, ti);
+        } else {
+          int32_t* out = static_cast<int32_t*>(p.out) + (per_group ? (long long)fl * p.out_gstride : 0ll);
+          store_chunk_i(p, out, r, prow, qcol0, ti);
+        }
+      }
+      ++flush;
+    }
+    __syncwarp();  // sq_s is rewritten at the next tile
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// The kernel
+// ------------------------------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmP,
+                 const __grid_constant__ CUtensorMap tmQ) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const uint32_t bar0 = sbase + C::OFF_BAR;
+  const uint32_t bar_pk_full = bar0;
+  const uint32_t bar_pk_empty = bar_pk_full + C::NP * 8;
+  const uint32_t bar_i8_full = bar_pk_empty + C::NP * 8;
+  const uint32_t bar_i8_empty = bar_i8_full + kNI * 8;
+  const uint32_t bar_tm_full = bar_i8_empty + kNI * 8;
+  const uint32_t bar_tm_empty = bar_tm_full + 2 * 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 8);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::NP; ++i) { mbar_init(bar_pk_full + i * 8, 1); mbar_init(bar_pk_empty + i * 8, kConvWarps); }
+    for (int i = 0; i < kNI; ++i) { mbar_init(bar_i8_full + i * 8, kConvWarps); mbar_init(bar_i8_empty + i * 8, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_tm_full + i * 8, 1); mbar_init(bar_tm_empty + i * 8, kEpiWarps); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmP);
+    prefetch_tensormap(&tmQ);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Rebalance registers between the roles (whole warpgroups): the epilogue keeps up to BN/2 fp32
+  // running sums per thread.  128*56 + 128*72 + 256*192 = 65536 registers.
+  // The setmaxnreg of each role sits at the top of that role's branch below.
+
+  const bool per_group_flush = (p.epi_mode == EPI_GROUP) || (p.epi_mode == EPI_GROUP_INT32);
+
+  if (warp < 4) {
+  setmaxnreg_dec<kRegsWg0>();
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    Sched sched;
+    TileInfo ti;
+    uint32_t it = 0;
+    bool ok = true;
+    while (ok && sched.next<BN>(p, ti)) {
+      for (int g = 0; g < p.G; ++g, ++it) {
+        const uint32_t s = it % C::NP, ph = (it / C::NP) & 1u;
+        ok = wait_bar(bar_pk_empty + s * 8, ph ^ 1u, abort_flag);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t full = bar_pk_full + s * 8;
+          const uint32_t dstP = sbase + C::OFF_PK + s * (C::PK_P + C::PK_Q);
+          const uint32_t dstQ = dstP + C::PK_P;
+          mbar_arrive_expect_tx(full, C::PK_P + C::PK_Q);
+          if (p.p_rowmajor) tma_load_2d(dstP, &tmP, full, g * kPackedRow, ti.p0);
+          else tma_load_3d(dstP, &tmP, full, 0, ti.p0, g);
+          if (p.q_rowmajor) tma_load_2d(dstQ, &tmQ, full, g * kPackedRow, ti.q0);
+          else tma_load_3d(dstQ, &tmQ, full, 0, ti.q0, ti.zq + g);
+        }
+        __syncwarp();
+      }
+    }
+    if (!ok) {
+      // aborting: wait (bounded) for copies that may still be in flight into this CTA's shared memory
+      const uint32_t n = it < (uint32_t)C::NP ? it : (uint32_t)C::NP;
+      for (uint32_t j = it - n; j < it; ++j) {
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(bar_pk_full + (j % C::NP) * 8, (j / C::NP) & 1u)) {
+          if (globaltimer_ns() - t0 > 100000000ull) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t idesc = make_idesc<BN>();
+    Sched sched;
+    TileInfo ti;
+    uint32_t it = 0, flush = 0;
+    bool ok = true;
+    while (ok && sched.next<BN>(p, ti)) {
+      for (int g = 0; g < p.G; ++g, ++it) {
+        const bool first = per_group_flush || g == 0;
+        const bool last = per_group_flush || g == p.G - 1;
+        const uint32_t buf = flush & 1u;
+        if (first) {
+          ok = wait_bar(bar_tm_empty + buf * 8, ((flush >> 1) & 1u) ^ 1u, abort_flag);
+          if (!ok) break;
+        }
+        const uint32_t s = it % kNI, ph = (it / kNI) & 1u;
+        ok = wait_bar(bar_i8_full + s * 8, ph, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t aP = sbase + C::OFF_I8 + s * (C::I8_P + C::I8_Q);
+          const uint32_t aQ = aP + C::I8_P;
+          const uint64_t dP = make_desc(aP), dQ = make_desc(aQ);
+          const uint32_t d_tmem = tmem_base + buf * BN;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // 32 bytes of K per MMA: advance the start-address field by 32 >> 4
+            mma_i8(d_tmem, dP + (uint64_t)(2 * k), dQ + (uint64_t)(2 * k), idesc, (first && k == 0) ? 0u : 1u);
+          }
+          tc_commit(bar_i8_empty + s * 8);
+          if (last) tc_commit(bar_tm_full + buf * 8);
+        }
+        __syncwarp();
+        if (last) ++flush;
+      }
+    }
+  }
+  } else if (warp < kConvWarp0 + kConvWarps) {
+    // ---------------- converters ----------------
+    setmaxnreg_dec<kRegsConv>();
+    const int tid = threadIdx.x - kConvWarp0 * 32;
+    Sched sched;
+    TileInfo ti;
+    uint32_t it = 0;
+    bool ok = true;
+    while (ok && sched.next<BN>(p, ti)) {
+      for (int g = 0; g < p.G; ++g, ++it) {
+        const uint32_t sp_ = it % C::NP, php = (it / C::NP) & 1u;
+        const uint32_t si = it % kNI, phi = (it / kNI) & 1u;
+        ok = wait_bar(bar_pk_full + sp_ * 8, php, abort_flag);
+        if (!ok) break;
+        ok = wait_bar(bar_i8_empty + si * 8, phi ^ 1u, abort_flag);
+        if (!ok) break;
+        const uint32_t pkP = sbase + C::OFF_PK + sp_ * (C::PK_P + C::PK_Q);
+        const uint32_t i8P = sbase + C::OFF_I8 + si * (C::I8_P + C::I8_Q);
+        convert_tile<kBM>(pkP, i8P, tid);
+        convert_tile<BN>(pkP + C::PK_P, i8P + C::I8_P, tid);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar_i8_full + si * 8);
+          mbar_arrive(bar_pk_empty + sp_ * 8);
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    setmaxnreg_inc<kRegsEpi>();
+    if (p.epi_mode == EPI_GROUP) {
+      epilogue_group<BN, __nv_bfloat16>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+    } else if (p.epi_mode == EPI_CHANNEL && p.out_dtype == I4TC_FP16) {
+      epilogue_simple<BN, __half>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+    } else {
+      epilogue_simple<BN, __nv_bfloat16>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, 1u);
+}
+
+template <int BN>
+static int launch_bn(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int grid, cudaStream_t st) {
+  using C = Cfg<BN>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  I4TC_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    I4TC_CUDA(cudaFuncSetAttribute(w4a4_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    configured[dev] = true;
+  }
+  w4a4_gemm_kernel<BN><<<grid, kThreads, C::SMEM_BYTES, st>>>(p, tmP, tmQ);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+int launch_w4a4_gemm(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int bn, int grid,
+                     cudaStream_t st) {
+  switch (bn) {
+    case 64: return launch_bn<64>(p, tmP, tmQ, grid, st);
+    case 128: return launch_bn<128>(p, tmP, tmQ, grid, st);
+    case 256: return launch_bn<256>(p, tmP, tmQ, grid, st);
+    default: return fail(I4TC_EINVAL, "unsupported tile width %d", bn);
+  }
+}
+
+}  // namespace i4tc

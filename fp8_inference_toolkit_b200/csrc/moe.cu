@@ -1,0 +1,193 @@
+// MoE support kernels: device-side stable counting sort of (token, slot) pairs by expert, and the
+// weighted combine of expert outputs.  The reference has no MoE path; these feed the grouped-tile
+// W4A4 GEMM, which walks the sorted rows expert by expert.
+//
+// Sort = three small launches over chunks of 1024 pairs:
+//   1. per-chunk histogram                    -> scratch counts [chunks, E]
+//   2. scan over chunks and experts           -> scratch bases  [chunks, E], expert_offsets [E+1]
+//   3. stable rank inside the chunk + scatter -> sorted_pairs, inv_pairs
+// The scratch ([chunks, E] int32) is caller-provided global memory.
+#include "common.cuh"
+
+namespace i4tc {
+
+constexpr int kSortChunk = 1024;
+constexpr int kMaxExperts = 256;
+
+// Stable rank of every element of a 1024-pair chunk among equal expert ids.
+// On return: rank (this thread's rank inside the chunk among its expert), and s_cnt[32][E] holds, per
+// warp, the exclusive prefix over earlier warps; total[e] (threads < E) is the chunk's count for e.
+__device__ __forceinline__ void chunk_rank(int e, bool valid, int E, int (*s_cnt)[kMaxExperts], int& rank,
+                                           int& total_for_thread_expert) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 32 * kMaxExperts; i += kSortChunk) (&s_cnt[0][0])[i] = 0;
+  __syncthreads();
+  const int key = valid ? e : -1 - lane;  // invalid lanes match nobody
+  const unsigned mask = __match_any_sync(0xffffffffu, key);
+  const int rank_w = __popc(mask & ((1u << lane) - 1u));
+  if (valid && rank_w == 0) s_cnt[warp][e] = __popc(mask);
+  __syncthreads();
+  total_for_thread_expert = 0;
+  if ((int)threadIdx.x < E) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = s_cnt[w][threadIdx.x];
+      s_cnt[w][threadIdx.x] = run;
+      run += c;
+    }
+    total_for_thread_expert = run;
+  }
+  __syncthreads();
+  rank = valid ? s_cnt[warp][e] + rank_w : 0;
+}
+
+__global__ void __launch_bounds__(kSortChunk) moe_hist_kernel(const int32_t* __restrict__ ids, int P, int E,
+                                                             int32_t* __restrict__ counts) {
+  __shared__ int s_cnt[32][kMaxExperts];
+  const int i = blockIdx.x * kSortChunk + threadIdx.x;
+  const bool in = i < P;
+  const int e = in ? ids[i] : 0;
+  const bool valid = in && e >= 0 && e < E;
+  int rank, total;
+  chunk_rank(e, valid, E, s_cnt, rank, total);
+  if ((int)threadIdx.x < E) counts[(long long)blockIdx.x * E + threadIdx.x] = total;
+}
+
+// One block of E (<= 256) threads: exclusive scan over chunks per expert, then over experts.
+__global__ void __launch_bounds__(kMaxExperts) moe_scan_kernel(int32_t* __restrict__ counts, int chunks, int E,
+                                                              int32_t* __restrict__ expert_offsets) {
+  __shared__ int s_tot[kMaxExperts];
+  __shared__ int s_off[kMaxExperts + 1];
+  const int e = threadIdx.x;
+  int run = 0;
+  if (e < E) {
+    for (int c = 0; c < chunks; ++c) {
+      const int v = counts[(long long)c * E + e];
+      counts[(long long)c * E + e] = run;
+      run += v;
+    }
+    s_tot[e] = run;
+  }
+  __syncthreads();
+  if (e == 0) {
+    int acc = 0;
+    for (int i = 0; i < E; ++i) {
+      s_off[i] = acc;
+      acc += s_tot[i];
+    }
+    s_off[E] = acc;
+  }
+  __syncthreads();
+  if (e < E) {
+    const int off = s_off[e];
+    expert_offsets[e] = off;
+    for (int c = 0; c < chunks; ++c) counts[(long long)c * E + e] += off;
+  }
+  if (e == 0) expert_offsets[E] = s_off[E];
+}
+
+__global__ void __launch_bounds__(kSortChunk) moe_scatter_kernel(const int32_t* __restrict__ ids, int P, int E,
+                                                                const int32_t* __restrict__ bases,
+                                                                int32_t* __restrict__ sorted_pairs,
+                                                                int32_t* __restrict__ inv_pairs) {
+  __shared__ int s_cnt[32][kMaxExperts];
+  const int i = blockIdx.x * kSortChunk + threadIdx.x;
+  const bool in = i < P;
+  const int e = in ? ids[i] : 0;
+  const bool valid = in && e >= 0 && e < E;
+  int rank, total;
+  chunk_rank(e, valid, E, s_cnt, rank, total);
+  if (valid) {
+    const int pos = bases[(long long)blockIdx.x * E + e] + rank;
+    sorted_pairs[pos] = i;
+    if (inv_pairs) inv_pairs[i] = pos;
+  } else if (in && inv_pairs) {
+    inv_pairs[i] = -1;
+  }
+}
+
+// out[t, :] = bf16( sum_j w[t, j] * y[inv[t*k + j], :] ), fp32 accumulation in ascending j.
+__global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y,
+                                                         const int32_t* __restrict__ inv,
+                                                         const float* __restrict__ w, int top_k, int H,
+                                                         __nv_bfloat16* __restrict__ out) {
+  const long long t = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < H; c += 256 * 8) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int j = 0; j < top_k; ++j) {
+      const int row = __ldg(inv + t * top_k + j);
+      if (row < 0) continue;
+      const float wj = __ldg(w + t * top_k + j);
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(y + (long long)row * H + c));
+      const uint32_t ww[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[2 * i] += wj * __uint_as_float(ww[i] << 16);
+        acc[2 * i + 1] += wj * __uint_as_float(ww[i] & 0xFFFF0000u);
+      }
+    }
+    union { __nv_bfloat16 h[8]; uint4 u; } pk;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pk.h[i] = __float2bfloat16_rn(acc[i]);
+    *reinterpret_cast<uint4*>(out + t * H + c) = pk.u;
+  }
+}
+
+int moe_sort_launch(const int32_t* ids, int64_t P, int64_t E, int32_t* sorted_pairs, int32_t* inv_pairs,
+                    int32_t* expert_offsets, int32_t* scratch, cudaStream_t st) {
+  const int chunks = (int)((P + kSortChunk - 1) / kSortChunk);
+  moe_hist_kernel<<<chunks, kSortChunk, 0, st>>>(ids, (int)P, (int)E, scratch);
+  moe_scan_kernel<<<1, kMaxExperts, 0, st>>>(scratch, chunks, (int)E, expert_offsets);
+  moe_scatter_kernel<<<chunks, kSortChunk, 0, st>>>(ids, (int)P, (int)E, scratch, sorted_pairs, inv_pairs);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+}  // namespace i4tc
+
+using namespace i4tc;
+
+extern "C" int64_t i4tc_moe_sort_scratch_bytes(int64_t num_pairs, int64_t num_experts) {
+  if (num_pairs < 0 || num_experts <= 0) return 0;
+  const int64_t chunks = (num_pairs + kSortChunk - 1) / kSortChunk;
+  return (chunks > 0 ? chunks : 1) * num_experts * (int64_t)sizeof(int32_t);
+}
+
+extern "C" int i4tc_moe_sort(const int32_t* expert_ids, int64_t num_pairs, int64_t num_experts,
+                             int32_t* sorted_pairs, int32_t* inv_pairs, int32_t* expert_offsets, void* scratch,
+                             int64_t scratch_bytes, int device, void* stream) {
+  I4TC_REQUIRE(num_pairs >= 0 && num_pairs < (1ll << 31), I4TC_EINVAL, "num_pairs out of range");
+  I4TC_REQUIRE(num_experts > 0 && num_experts <= kMaxExperts, I4TC_EINVAL, "num_experts must be in [1, %d]",
+               kMaxExperts);
+  I4TC_REQUIRE(expert_offsets != nullptr, I4TC_EINVAL, "null expert_offsets");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (num_pairs == 0) {
+    I4TC_CUDA(cudaMemsetAsync(expert_offsets, 0, (num_experts + 1) * sizeof(int32_t), st));
+    return I4TC_OK;
+  }
+  I4TC_REQUIRE(expert_ids && sorted_pairs && scratch, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(scratch_bytes >= i4tc_moe_sort_scratch_bytes(num_pairs, num_experts), I4TC_EINVAL,
+               "scratch too small: need %lld bytes", (long long)i4tc_moe_sort_scratch_bytes(num_pairs, num_experts));
+  return moe_sort_launch(expert_ids, num_pairs, num_experts, sorted_pairs, inv_pairs, expert_offsets,
+                         static_cast<int32_t*>(scratch), st);
+}
+
+extern "C" int i4tc_moe_combine(const void* y, const int32_t* inv_pairs, const float* w, int64_t T, int64_t top_k,
+                                int64_t H, void* out, int device, void* stream) {
+  I4TC_REQUIRE(T >= 0 && top_k > 0 && H >= 0, I4TC_EINVAL, "bad sizes");
+  I4TC_REQUIRE(H % 8 == 0, I4TC_EINVAL, "H must be a multiple of 8");
+  I4TC_REQUIRE(T < (1ll << 31), I4TC_EINVAL, "too many tokens");
+  if (T == 0 || H == 0) return I4TC_OK;
+  I4TC_REQUIRE(y && inv_pairs && w && out, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(aligned_to(y, 16) && aligned_to(out, 16), I4TC_EALIGN, "y and out must be 16-byte aligned");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  moe_combine_kernel<<<(unsigned)T, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y), inv_pairs, w, (int)top_k, (int)H, static_cast<__nv_bfloat16*>(out));
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}

@@ -1,0 +1,231 @@
+"""PyTorch-facing op surface: same names, argument order, dtypes, shapes and return conventions
+as the reference extension ``int4_native_tc_ops`` (``int4_native_tc/csrc/bindings.cpp:208-309``).
+
+PyTorch is only plumbing here: it owns the device memory and the stream; every op is one or more
+calls into the C-ABI library.  Quantise ops allocate and return their outputs, scaled GEMMs write
+into the caller's ``out`` and return ``None`` -- the reference's ownership rules
+(``int4_quant.cu:209-212``, ``int4_gemm.cu:831-837``).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+from ._cabi import check, lib
+
+_DTYPES = {torch.bfloat16: _cabi.BF16, torch.float16: _cabi.FP16, torch.float32: _cabi.FP32}
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _dev(t: torch.Tensor) -> int:
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _cuda2d(t: torch.Tensor, name: str) -> None:
+    _require(isinstance(t, torch.Tensor) and t.is_cuda, f"{name} must be CUDA tensor")
+    _require(t.dim() == 2, f"{name} must be 2D")
+
+
+def _float_input(t: torch.Tensor, name: str) -> torch.Tensor:
+    _require(t.dtype in _DTYPES, f"{name} must be bfloat16, float16 or float32")
+    if t.stride(1) != 1 or (t.stride(0) * t.element_size()) % 16 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+def _same_device(*ts: torch.Tensor) -> None:
+    d = ts[0].device
+    for t in ts[1:]:
+        _require(t.device == d, "all tensors must be on the same device")
+
+
+def _packed(t: torch.Tensor, name: str) -> torch.Tensor:
+    _require(t.is_cuda, f"{name} must be CUDA tensor")
+    _require(t.dtype == torch.uint8, f"{name} must be uint8")
+    _require(t.is_contiguous(), f"{name} must be contiguous")
+    return t
+
+
+def _f32(t: torch.Tensor, name: str, numel: int) -> torch.Tensor:
+    _require(t.is_cuda and t.dtype == torch.float32, f"{name} must be a float32 CUDA tensor")
+    _require(t.is_contiguous(), f"{name} must be contiguous")
+    _require(t.numel() == numel, f"{name} has {t.numel()} elements, expected {numel}")
+    return t
+
+
+# --------------------------------------------------------------------------- #
+# quantise / pack
+# --------------------------------------------------------------------------- #
+def _quant_rowwise(x: torch.Tensor, role: int, who: str):
+    _cuda2d(x, "input" if role == _cabi.ROLE_ACTIVATION else "weight")
+    R, K = x.shape
+    _require(K % 2 == 0, "K must be even for INT4 packing")
+    x = _float_input(x, who)
+    packed = torch.empty((R, K // 2), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((R,), dtype=torch.float32, device=x.device)
+    check(lib.i4tc_quant_rowwise(x.data_ptr(), _DTYPES[x.dtype], R, K, x.stride(0), packed.data_ptr(),
+                                 scale.data_ptr(), role, _dev(x), _stream(x)), who)
+    return packed, scale
+
+
+def _quant_grouped(x: torch.Tensor, group_size: int, role: int, who: str):
+    _cuda2d(x, "input" if role == _cabi.ROLE_ACTIVATION else "weight")
+    R, K = x.shape
+    group_size = int(group_size)
+    _require(group_size > 0 and K % group_size == 0, "K must be divisible by group_size")
+    _require(group_size % 2 == 0, "group_size must be even")
+    x = _float_input(x, who)
+    G = K // group_size
+    packed = torch.empty((G, R, group_size // 2), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((G, R), dtype=torch.float32, device=x.device)
+    check(lib.i4tc_quant_grouped(x.data_ptr(), _DTYPES[x.dtype], R, K, x.stride(0), group_size,
+                                 packed.data_ptr(), scale.data_ptr(), role, _dev(x), _stream(x)), who)
+    return packed, scale
+
+
+def dynamic_int4_quant(input: torch.Tensor):
+    """[M,K] -> (packed u8 [M,K/2], scale f32 [M]).  Reference: ``int4_quant.cu:201``."""
+    return _quant_rowwise(input, _cabi.ROLE_ACTIVATION, "dynamic_int4_quant")
+
+
+def static_int4_weight_quant(weight: torch.Tensor):
+    """[N,K] -> (packed u8 [N,K/2], scale f32 [N]).  Reference: ``int4_quant.cu:289``."""
+    return _quant_rowwise(weight, _cabi.ROLE_WEIGHT, "static_int4_weight_quant")
+
+
+def dynamic_int4_quant_grouped(input: torch.Tensor, group_size: int):
+    """[M,K] -> (packed u8 [G,M,gs/2], scale f32 [G,M]).  Reference: ``int4_quant.cu:806``."""
+    return _quant_grouped(input, group_size, _cabi.ROLE_ACTIVATION, "dynamic_int4_quant_grouped")
+
+
+def static_int4_weight_quant_grouped(weight: torch.Tensor, group_size: int):
+    """[N,K] -> (packed u8 [G,N,gs/2], scale f32 [G,N]).  Reference: ``int4_quant.cu:712``."""
+    return _quant_grouped(weight, group_size, _cabi.ROLE_WEIGHT, "static_int4_weight_quant_grouped")
+
+
+def int4_quant_with_scales(input: torch.Tensor, scale: torch.Tensor, group_size: int = 0):
+    """Quantise with caller-supplied divisors (no reference op; the "identical scales" form used to
+    compare codes bit for bit).  ``scale`` [M] -> packed [M,K/2]; ``scale`` [G,M] -> packed [G,M,gs/2]."""
+    _cuda2d(input, "input")
+    R, K = input.shape
+    x = _float_input(input, "int4_quant_with_scales")
+    _same_device(x, scale)
+    if group_size:
+        G = K // group_size
+        _f32(scale, "scale", G * R)
+        packed = torch.empty((G, R, group_size // 2), dtype=torch.uint8, device=x.device)
+    else:
+        _f32(scale, "scale", R)
+        packed = torch.empty((R, K // 2), dtype=torch.uint8, device=x.device)
+    check(lib.i4tc_quant_with_scales(x.data_ptr(), _DTYPES[x.dtype], R, K, x.stride(0), int(group_size),
+                                     scale.data_ptr(), packed.data_ptr(), _dev(x), _stream(x)),
+          "int4_quant_with_scales")
+    return packed
+
+
+def unpack_int4_to_int8(packed: torch.Tensor, K: int) -> torch.Tensor:
+    """packed u8 [N,K/2] -> int8 [N,K].  Reference: ``int4_quant.cu:593``."""
+    _require(packed.is_cuda, "packed must be CUDA tensor")
+    _require(packed.dim() == 2, "packed must be 2D [N, K/2]")
+    _require(packed.dtype == torch.uint8, "packed must be uint8")
+    _require(packed.size(1) * 2 == K, "packed.size(1) must equal K/2")
+    packed = packed.contiguous()
+    N = packed.size(0)
+    out = torch.empty((N, K), dtype=torch.int8, device=packed.device)
+    check(lib.i4tc_unpack_int4_to_int8(packed.data_ptr(), N, K, out.data_ptr(), _dev(packed), _stream(packed)),
+          "unpack_int4_to_int8")
+    return out
+
+
+# --------------------------------------------------------------------------- #
+# GEMMs
+# --------------------------------------------------------------------------- #
+def cutlass_int4_gemm(a_packed: torch.Tensor, b_packed: torch.Tensor, M: int, N: int, K: int) -> torch.Tensor:
+    """int32 [M,N] = A[M,K] . B[N,K]^T over packed int4.  Reference: ``int4_gemm.cu:779``."""
+    _packed(a_packed, "a_packed")
+    _packed(b_packed, "b_packed")
+    _same_device(a_packed, b_packed)
+    _require(K % 64 == 0, "K must be a multiple of 64")
+    _require(a_packed.numel() == M * (K // 2), "a_packed does not have M*K/2 bytes")
+    _require(b_packed.numel() == N * (K // 2), "b_packed does not have N*K/2 bytes")
+    out = torch.empty((M, N), dtype=torch.int32, device=a_packed.device)
+    check(lib.i4tc_gemm_int32(a_packed.data_ptr(), b_packed.data_ptr(), out.data_ptr(), M, N, K,
+                              _dev(a_packed), _stream(a_packed)), "cutlass_int4_gemm")
+    return out
+
+
+def cutlass_int4_scaled_mm(a_packed, b_packed, scale_a, scale_b, out, M: int, N: int, K: int) -> None:
+    """out[m,n] = cast((acc * scale_b[n]) * scale_a[m]) into the caller's bf16/fp16 ``out``.
+    Reference: ``int4_gemm.cu:831``."""
+    _packed(a_packed, "a_packed")
+    _packed(b_packed, "b_packed")
+    _same_device(a_packed, b_packed, scale_a, scale_b, out)
+    _require(K % 64 == 0, "K must be a multiple of 64")
+    _require(out.dtype in (torch.bfloat16, torch.float16), "out must be bfloat16 or float16")
+    _require(out.is_contiguous() and out.numel() == M * N, "out must be a contiguous [M,N] tensor")
+    _require(a_packed.numel() == M * (K // 2), "a_packed does not have M*K/2 bytes")
+    _require(b_packed.numel() == N * (K // 2), "b_packed does not have N*K/2 bytes")
+    _f32(scale_a, "scale_a", M)
+    _f32(scale_b, "scale_b", N)
+    check(lib.i4tc_gemm_scaled(a_packed.data_ptr(), b_packed.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(),
+                               out.data_ptr(), _DTYPES[out.dtype], M, N, K, _dev(out), _stream(out)),
+          "cutlass_int4_scaled_mm")
+
+
+def cutlass_int4_fused_grouped_gemm(a_packed, b_packed, scale_a, scale_b, out, M: int, N: int,
+                                    group_size: int, num_groups: int) -> None:
+    """Per-group-128 fused linear into the caller's bf16 ``out`` [M,N].
+    Reference: ``int4_gemm.cu:4231`` (checks at ``:4243-4252``)."""
+    _packed(a_packed, "a_packed")
+    _packed(b_packed, "b_packed")
+    _same_device(a_packed, b_packed, scale_a, scale_b, out)
+    _require(group_size == 128, "fused grouped GEMM only supports group_size=128")
+    _require(out.dtype == torch.bfloat16, "fused grouped GEMM only supports BF16 output")
+    _require(out.is_contiguous() and out.numel() == M * N, "out must be a contiguous [M,N] tensor")
+    _require(a_packed.numel() == num_groups * M * 64, "a_packed must be [G, M, 64]")
+    _require(b_packed.numel() == num_groups * N * 64, "b_packed must be [G, N, 64]")
+    _f32(scale_a, "scale_a", num_groups * M)
+    _f32(scale_b, "scale_b", num_groups * N)
+    check(lib.i4tc_gemm_grouped(a_packed.data_ptr(), b_packed.data_ptr(), scale_a.data_ptr(),
+                                scale_b.data_ptr(), out.data_ptr(), M, N, group_size, num_groups,
+                                _dev(out), _stream(out)), "cutlass_int4_fused_grouped_gemm")
+
+
+# Same contract, different kernels in the reference (int4_gemm.cu:3751, 4073, 4007, 3932, 929).
+cutlass_int4_fused_grouped_gemm_v5 = cutlass_int4_fused_grouped_gemm
+cutlass_int4_fused_grouped_gemm_v7 = cutlass_int4_fused_grouped_gemm
+cutlass_int4_fused_grouped_gemm_v8 = cutlass_int4_fused_grouped_gemm
+cutlass_int4_fused_grouped_gemm_v9 = cutlass_int4_fused_grouped_gemm
+cutlass_int4_scaled_mm_grouped = cutlass_int4_fused_grouped_gemm
+
+
+def int4_grouped_partials(a_packed, b_packed, M: int, N: int, num_groups: int) -> torch.Tensor:
+    """int32 [G,M,N]: the per-group integer accumulators of the fused kernel (no reference op)."""
+    _packed(a_packed, "a_packed")
+    _packed(b_packed, "b_packed")
+    _same_device(a_packed, b_packed)
+    _require(a_packed.numel() == num_groups * M * 64, "a_packed must be [G, M, 64]")
+    _require(b_packed.numel() == num_groups * N * 64, "b_packed must be [G, N, 64]")
+    out = torch.empty((num_groups, M, N), dtype=torch.int32, device=a_packed.device)
+    check(lib.i4tc_gemm_grouped_int32(a_packed.data_ptr(), b_packed.data_ptr(), out.data_ptr(), M, N,
+                                      num_groups, _dev(out), _stream(out)), "int4_grouped_partials")
+    return out
+
+
+def set_tuning(tile_n: int = 0, swap: int = -1) -> None:
+    """Force the GEMM tile width / operand orientation (tests); ``set_tuning()`` restores automatic."""
+    check(lib.i4tc_set_tuning(tile_n, swap), "set_tuning")
+
+
+def check_status(device=None) -> None:
+    """Raise if any kernel gave up on a bounded wait since the last call (synchronises the stream)."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    check(lib.i4tc_check_status(dev, torch.cuda.current_stream(dev).cuda_stream), "check_status")

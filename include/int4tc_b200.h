@@ -1,0 +1,166 @@
+/*
+ * int4tc_b200 -- C ABI of the B200 (sm_100a) W4A4 int4 x int4 library.
+ *
+ * Every entry point takes raw device pointers, sizes, a CUDA device ordinal and a
+ * CUDA stream handle (a `cudaStream_t` passed as `void*`; NULL = the legacy default
+ * stream).  Nothing here depends on PyTorch.  Work is enqueued on `stream` and the
+ * call returns without synchronising unless stated otherwise.
+ *
+ * Return value: 0 on success; a negative I4TC_E* code for a rejected argument; a
+ * positive value is a `cudaError_t` raised by the runtime.  `i4tc_last_error()`
+ * returns a human-readable message for the calling thread's last failure.
+ *
+ * Each declaration cites the reference interface it replaces, as
+ * `file:line` inside the reference project (gkswns0531/fp8_inference_toolkit).
+ *
+ * Data formats (identical to the reference's):
+ *   packed int4   : two's-complement nibbles, element 2i in the low nibble of byte i
+ *                   (int4_native_tc/csrc/int4_quant.cu:49-51)
+ *   row-major     : codes [R, K/2] u8, scale [R] f32               (per token / per channel)
+ *   group-major   : codes [G, R, gs/2] u8, scale [G, R] f32, G=K/gs (int4_quant.cu:651-653)
+ */
+#ifndef INT4TC_B200_H_
+#define INT4TC_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error codes ---------------------------------------------------------- */
+#define I4TC_OK 0
+#define I4TC_EINVAL (-1)      /* bad shape / size / flag                         */
+#define I4TC_EALIGN (-2)      /* pointer or stride not aligned as required       */
+#define I4TC_EUNSUPPORTED (-3)/* combination not implemented                     */
+#define I4TC_EDEVICE (-4)     /* device is not compute capability 10.x           */
+#define I4TC_EKERNEL (-5)     /* a kernel reported a bounded-wait timeout        */
+
+/* element types of floating-point inputs / outputs */
+#define I4TC_BF16 0
+#define I4TC_FP16 1
+#define I4TC_FP32 2
+#define I4TC_INT32 3
+
+/* scale conventions (int4_quant.cu:142 vs :267) */
+#define I4TC_ROLE_ACTIVATION 0 /* scale = max(absmax/7, 1/(7*512))              */
+#define I4TC_ROLE_WEIGHT 1     /* scale = absmax/7, or 1.0 for an all-zero slice */
+
+int i4tc_version(void);
+const char* i4tc_last_error(void);
+
+/* Number of SMs of `device` (cached); negative on error. */
+int i4tc_sm_count(int device);
+
+/* Test / tuning hook: force the GEMM tile width (64, 128, 256; 0 = automatic) and the operand
+ * orientation (1 = weights on the 128-row side of the MMA, 0 = activations, -1 = automatic).
+ * Process-wide.  Results do not depend on it. */
+int i4tc_set_tuning(int tile_n, int swap);
+
+/* ---- quantise + pack ------------------------------------------------------- */
+
+/* Per-row symmetric int4 quantise + pack, one pass over the input.
+ * Replaces dynamic_int4_quant (int4_native_tc/csrc/int4_quant.cu:201, kernel :100)
+ * and static_int4_weight_quant (int4_quant.cu:289, kernel :240); `role` selects
+ * between their scale conventions.  x: [rows, K] of `dtype`, row stride `ldx`
+ * elements; packed: [rows, K/2]; scale: [rows].  K must be even. */
+int i4tc_quant_rowwise(const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx,
+                       uint8_t* packed, float* scale, int role, int device, void* stream);
+
+/* Per-(row, group) symmetric int4 quantise + pack with group-major outputs.
+ * Replaces dynamic_int4_quant_grouped (int4_quant.cu:806, kernel :759) and
+ * static_int4_weight_quant_grouped (int4_quant.cu:712, kernel :665).
+ * packed: [K/gs, rows, gs/2]; scale: [K/gs, rows].  gs in {32,64,128,256}, K % gs == 0. */
+int i4tc_quant_grouped(const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx,
+                       int64_t group_size, uint8_t* packed, float* scale, int role,
+                       int device, void* stream);
+
+/* Quantise + pack with caller-supplied divisors: q = clamp(rint(x / scale), -8, 7).
+ * group_size == 0: scale [rows], packed row-major; otherwise scale [K/gs, rows] and
+ * packed group-major.  No reference op has this signature; it is the "identical
+ * scales" form under which codes are compared bit for bit with the CPU oracle
+ * (arithmetic of benchmark/benchmark_w4a8fp8.py:200-204). */
+int i4tc_quant_with_scales(const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx,
+                           int64_t group_size, const float* scale, uint8_t* packed,
+                           int device, void* stream);
+
+/* packed [rows, K/2] -> int8 [rows, K] with sign extension.
+ * Replaces unpack_int4_to_int8 (int4_quant.cu:593, kernel :553). */
+int i4tc_unpack_int4_to_int8(const uint8_t* packed, int64_t rows, int64_t K, int8_t* out,
+                             int device, void* stream);
+
+/* ---- dense W4A4 GEMM ------------------------------------------------------- */
+
+/* C[m,n] = sum_k A[m,k] * B[n,k], int32 out [M,N] (row stride N).
+ * a: [M, K/2], b: [N, K/2] row-major packed.  K % 64 == 0.
+ * Replaces cutlass_int4_gemm (int4_native_tc/csrc/int4_gemm.cu:779). */
+int i4tc_gemm_int32(const uint8_t* a, const uint8_t* b, int32_t* c, int64_t M, int64_t N,
+                    int64_t K, int device, void* stream);
+
+/* out[m,n] = cast((float(acc) * scale_b[n]) * scale_a[m]); out_dtype BF16 or FP16, [M,N].
+ * Replaces cutlass_int4_scaled_mm (int4_gemm.cu:831; epilogue :137-150). */
+int i4tc_gemm_scaled(const uint8_t* a, const uint8_t* b, const float* scale_a,
+                     const float* scale_b, void* out, int out_dtype, int64_t M, int64_t N,
+                     int64_t K, int device, void* stream);
+
+/* Per-group-128 fused linear:
+ *   out[m,n] = bf16( sum_g (float(acc_g[m,n]) * scale_a[g,m]) * scale_b[g,n] ), g ascending.
+ * a: [G, M, 64], b: [G, N, 64] group-major packed; scale_a [G,M]; scale_b [G,N]; out bf16 [M,N].
+ * Replaces cutlass_int4_fused_grouped_gemm and its same-contract aliases _v5/_v7/_v8/_v9
+ * (int4_gemm.cu:4231, 3751, 4073, 4007, 3932) and cutlass_int4_scaled_mm_grouped (:929).
+ * `group_size` must be 128 (as int4_gemm.cu:4243). */
+int i4tc_gemm_grouped(const uint8_t* a, const uint8_t* b, const float* scale_a,
+                      const float* scale_b, void* out, int64_t M, int64_t N,
+                      int64_t group_size, int64_t num_groups, int device, void* stream);
+
+/* int32 partial sums of every group, out [G, M, N]: the integer accumulators that the fused
+ * kernel drains.  No reference op exposes them; used to check the integer path bit for bit. */
+int i4tc_gemm_grouped_int32(const uint8_t* a, const uint8_t* b, int32_t* out, int64_t M,
+                            int64_t N, int64_t num_groups, int device, void* stream);
+
+/* ---- MoE (no counterpart in the reference; composition of the grouped ops) -- */
+
+/* Stable counting sort of the T*top_k (token, slot) pairs by expert id.
+ * expert_ids: [num_pairs] int32 in [0, E); ids outside that range are left out.
+ * Outputs: sorted_pairs [num_pairs] int32 (pair index = token*top_k + slot, ascending inside an
+ * expert), inv_pairs [num_pairs] (sorted position of each pair, -1 if left out; may be NULL),
+ * expert_offsets [E+1] int32.  E <= 256.  `scratch` is caller-provided device memory of at least
+ * i4tc_moe_sort_scratch_bytes(num_pairs, E) bytes that the sort uses for per-chunk histograms. */
+int64_t i4tc_moe_sort_scratch_bytes(int64_t num_pairs, int64_t num_experts);
+int i4tc_moe_sort(const int32_t* expert_ids, int64_t num_pairs, int64_t num_experts,
+                  int32_t* sorted_pairs, int32_t* inv_pairs, int32_t* expert_offsets,
+                  void* scratch, int64_t scratch_bytes, int device, void* stream);
+
+/* Gather rows x[sorted_pairs[i] / top_k] and grouped-quantise them (gs=128, activation
+ * role) straight into expert-sorted group-major layout: packed [K/128, P, 64], scale [K/128, P]. */
+int i4tc_moe_gather_quant(const void* x, int dtype, int64_t K, int64_t ldx,
+                          const int32_t* sorted_pairs, int64_t num_pairs, int64_t top_k,
+                          uint8_t* packed, float* scale, int device, void* stream);
+
+/* Grouped-tile W4A4 GEMM over expert-sorted rows:
+ *   for rows r in [expert_offsets[e], expert_offsets[e+1]):  out[r, :] = linear_grouped(a[:, r, :], W_e)
+ * a: [G, P, 64], scale_a [G, P]; b: [E, G, N, 64], scale_b [E, G, N]; out bf16 [P, N].
+ * `expert_offsets` is read on the device (no host synchronisation). */
+int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, const uint8_t* b,
+                          const float* scale_b, const int32_t* expert_offsets, void* out,
+                          int64_t num_pairs, int64_t N, int64_t num_groups,
+                          int64_t num_experts, int device, void* stream);
+
+/* SwiGLU + grouped re-quantise: h bf16 [P, 2I] laid out [gate | up] ->
+ * act = bf16(silu(gate) * up) -> packed [I/128, P, 64], scale [I/128, P]. */
+int i4tc_moe_silu_mul_quant(const void* h, int64_t P, int64_t I, uint8_t* packed, float* scale,
+                            int device, void* stream);
+
+/* out[t, :] = bf16( sum_j w[t, j] * y[inv_pairs[t*top_k + j], :] ), j ascending, fp32 sum.
+ * y bf16 [P, H]; inv_pairs[pair] = sorted position of that pair. */
+int i4tc_moe_combine(const void* y, const int32_t* inv_pairs, const float* w, int64_t T,
+                     int64_t top_k, int64_t H, void* out, int device, void* stream);
+
+/* Polls the device-side status word written by bounded waits; 0 if no kernel timed out since
+ * the last call, else I4TC_EKERNEL.  Synchronises `stream`. */
+int i4tc_check_status(int device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INT4TC_B200_H_ */

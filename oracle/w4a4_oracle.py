@@ -1,0 +1,272 @@
+"""CPU oracle for the int4_native_tc W4A4 hot path.  TEST INFRASTRUCTURE ONLY.
+
+This module restates, in numpy/torch on the CPU, the arithmetic of the
+reference's quantise -> pack -> int4 x int4 integer matmul -> fp32 dequant path.
+Only tests, the smoke check and the CPU-baseline leg of the benchmark may import
+it; the product (the CUDA library and its Python op surface) never does.
+
+Pinning status
+--------------
+* pack / unpack / integer GEMM: pinned.  Checked against outputs of the
+  reference's own CPU helpers (``int4_native_tc/test_correctness.py:20-54``,
+  ``benchmark/verify_int4_matmul_precision.py:16-29``) executed on the
+  reference's own seeds; see ``tests/golden/make_golden.py``.
+* quantiser codes: **parity unpinned** by the reference's tests (they check only
+  ranges, ``int4_native_tc/test_correctness.py:61-124``).  The reference CUDA
+  kernel multiplies by ``7/absmax`` under fast-math
+  (``int4_native_tc/csrc/int4_quant.cu:146,160-163``), which no CPU can
+  reproduce; every torch restatement inside the reference divides by
+  ``absmax/7`` instead (``benchmark/benchmark_w4a8fp8.py:200-204``,
+  ``int4_native_tc/profile_bottleneck.py:21-29``).  The oracle and the CUDA
+  kernels both use that second, IEEE-reproducible form (see ``quant_codes``).
+* MoE: **parity unpinned** (the reference has no MoE); it is a composition of
+  the grouped quantiser and the grouped linear below.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+F32 = np.float32
+#: activation scale floor, ``int4_native_tc/csrc/int4_quant.cu:97``
+K_MIN_SCALE = F32(1.0) / (F32(7.0) * F32(512.0))
+GROUP = 128
+
+
+# --------------------------------------------------------------------------- #
+# pack / unpack  (int4_native_tc/test_correctness.py:20-48, int4_quant.cu:49-59)
+# --------------------------------------------------------------------------- #
+def pack_int4(codes: np.ndarray) -> np.ndarray:
+    """[..., K] int codes in [-8, 7] -> [..., K/2] uint8, element 2i in the low nibble."""
+    codes = np.asarray(codes)
+    assert codes.shape[-1] % 2 == 0
+    c = codes.astype(np.int16)
+    lo = c[..., 0::2] & 0x0F
+    hi = c[..., 1::2] & 0x0F
+    return ((hi << 4) | lo).astype(np.uint8)
+
+
+def unpack_int4(packed: np.ndarray) -> np.ndarray:
+    """[..., K/2] uint8 -> [..., K] int8, sign-extending each nibble."""
+    p = np.asarray(packed, dtype=np.uint8).astype(np.int16)
+    lo = p & 0x0F
+    hi = (p >> 4) & 0x0F
+    lo = np.where(lo >= 8, lo - 16, lo)
+    hi = np.where(hi >= 8, hi - 16, hi)
+    out = np.empty(p.shape[:-1] + (p.shape[-1] * 2,), dtype=np.int8)
+    out[..., 0::2] = lo
+    out[..., 1::2] = hi
+    return out
+
+
+# --------------------------------------------------------------------------- #
+# quantise
+# --------------------------------------------------------------------------- #
+def _to_f32(x) -> np.ndarray:
+    """bf16/fp16/fp32 torch tensor or ndarray -> float32 ndarray (exact widening)."""
+    if isinstance(x, torch.Tensor):
+        return x.detach().to(torch.float32).cpu().numpy()
+    return np.asarray(x, dtype=np.float32)
+
+
+def quant_codes(xf: np.ndarray, absmax: np.ndarray) -> np.ndarray:
+    """Canonical code arithmetic shared by the oracle and the CUDA kernels.
+
+    ``q = clamp(rint(x / (absmax / 7)), -8, 7)`` with IEEE fp32 division and
+    round-half-to-even; ``q = 0`` where ``absmax == 0``.  The divisor is the
+    un-floored ``absmax/7``: the reference derives codes from ``absmax`` and
+    applies the floor to the *returned* scale only (``int4_quant.cu:142,146``).
+    ``absmax`` broadcasts against ``xf`` along the last axis.
+    """
+    s = (absmax.astype(F32) / F32(7.0)).astype(F32)
+    safe = np.where(s == 0, F32(1.0), s).astype(F32)
+    q = np.rint((xf.astype(F32) / safe).astype(F32))
+    q = np.clip(q, -8.0, 7.0)
+    q = np.where(s == 0, F32(0.0), q)
+    return q.astype(np.int8)
+
+
+def _scale_out(absmax: np.ndarray, role: str) -> np.ndarray:
+    s = (absmax.astype(F32) / F32(7.0)).astype(F32)
+    if role == "activation":  # int4_quant.cu:142, 789
+        return np.maximum(s, K_MIN_SCALE).astype(F32)
+    if role == "weight":  # int4_quant.cu:267, 692
+        return np.where(absmax == 0, F32(1.0), s).astype(F32)
+    raise ValueError(role)
+
+
+def quant_rowwise(x, role: str = "activation"):
+    """Per-row symmetric int4 (``dynamic_int4_quant`` / ``static_int4_weight_quant``,
+    ``int4_quant.cu:201,289``).  Returns (codes int8 [R,K], scale f32 [R])."""
+    xf = _to_f32(x)
+    absmax = np.abs(xf).max(axis=1) if xf.shape[1] else np.zeros(xf.shape[0], F32)
+    codes = quant_codes(xf, absmax[:, None])
+    return codes, _scale_out(absmax, role)
+
+
+def quant_grouped(x, group_size: int = GROUP, role: str = "activation"):
+    """Per-(row, K-group) symmetric int4 with **group-major** outputs
+    (``dynamic_int4_quant_grouped`` / ``static_int4_weight_quant_grouped``,
+    ``int4_quant.cu:806,712``; layout ``:678-680,772-774``).
+    Returns (codes int8 [G,R,gs], scale f32 [G,R])."""
+    xf = _to_f32(x)
+    R, K = xf.shape
+    assert K % group_size == 0 and group_size % 2 == 0
+    G = K // group_size
+    xg = xf.reshape(R, G, group_size).transpose(1, 0, 2)  # [G,R,gs]
+    absmax = np.abs(xg).max(axis=2)
+    codes = quant_codes(xg, absmax[:, :, None])
+    return np.ascontiguousarray(codes), _scale_out(absmax, role)
+
+
+def quant_with_scales(x, scale: np.ndarray, group_size: int | None = None) -> np.ndarray:
+    """Quantise with caller-supplied divisors: ``q = clamp(rint(x / scale), -8, 7)``.
+    ``scale`` is [R] (row-wise; codes [R,K]) or [G,R] (grouped; codes [G,R,gs])."""
+    xf = _to_f32(x)
+    scale = np.asarray(scale, dtype=F32)
+    if scale.ndim == 1:
+        q = np.rint((xf / scale[:, None]).astype(F32))
+    else:
+        R, K = xf.shape
+        G = scale.shape[0]
+        gs = group_size or K // G
+        xg = xf.reshape(R, G, gs).transpose(1, 0, 2)
+        q = np.rint((xg / scale[:, :, None]).astype(F32))
+    return np.ascontiguousarray(np.clip(q, -8, 7).astype(np.int8))
+
+
+def quant_codes_refcuda_form(xf: np.ndarray, absmax: np.ndarray) -> np.ndarray:
+    """The reference CUDA kernel's formulation ``rint(x * (7/absmax))`` evaluated
+    in IEEE fp32 (``int4_quant.cu:146,160-163``).  Informational only: used to
+    report how often it differs from ``quant_codes`` on near-tie inputs."""
+    inv = np.where(absmax == 0, F32(0.0), F32(7.0) / np.where(absmax == 0, F32(1.0), absmax)).astype(F32)
+    q = np.rint((xf.astype(F32) * inv).astype(F32))
+    return np.clip(q, -8.0, 7.0).astype(np.int8)
+
+
+# --------------------------------------------------------------------------- #
+# integer GEMM and dequant epilogues
+# --------------------------------------------------------------------------- #
+def int_gemm(a_codes: np.ndarray, b_codes: np.ndarray) -> np.ndarray:
+    """``C[m,n] = sum_k A[m,k] * B[n,k]`` exactly, int32
+    (``int4_native_tc/test_correctness.py:51-54``).
+
+    For |code| <= 8 and K <= 2**17 every partial sum is an integer below 2**24,
+    so an fp32 BLAS product of the float-cast codes is exact; larger K falls
+    back to an int64 product."""
+    a = np.asarray(a_codes)
+    b = np.asarray(b_codes)
+    K = a.shape[-1]
+    if K * 64 < (1 << 24):
+        return (a.astype(F32) @ b.astype(F32).T).astype(np.int32)
+    return (a.astype(np.int64) @ b.astype(np.int64).T).astype(np.int32)
+
+
+def int_gemm_int32_torch(a_codes: torch.Tensor, b_codes: torch.Tensor) -> torch.Tensor:
+    """The reference's own formulation: ``torch.matmul`` on int32 operands
+    (``benchmark/verify_int4_matmul_precision.py:23-25``).  This is the *timed*
+    CPU baseline; ``int_gemm`` above is the fast exact checker."""
+    return torch.matmul(a_codes.to(torch.int32), b_codes.to(torch.int32).T)
+
+
+def to_bf16(f: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(f, dtype=F32)).to(torch.bfloat16)
+
+
+def dequant_per_channel(acc: np.ndarray, scale_a: np.ndarray, scale_b: np.ndarray) -> np.ndarray:
+    """``(float(acc) * scale_b[n]) * scale_a[m]`` in fp32, the order of the
+    reference's scaled epilogue (``int4_gemm.cu:137-150``)."""
+    t = (acc.astype(F32) * scale_b.astype(F32)[None, :]).astype(F32)
+    return (t * scale_a.astype(F32)[:, None]).astype(F32)
+
+
+def linear_per_channel(a_codes, b_codes, scale_a, scale_b) -> torch.Tensor:
+    """Per-channel W4A4 linear -> bf16 [M,N] (``cutlass_int4_scaled_mm``, ``int4_gemm.cu:831``)."""
+    return to_bf16(dequant_per_channel(int_gemm(a_codes, b_codes), scale_a, scale_b))
+
+
+def linear_grouped_f32(a_codes, b_codes, scale_a, scale_b) -> np.ndarray:
+    """Per-group W4A4 linear before the final cast.  ``a_codes`` [G,M,gs],
+    ``b_codes`` [G,N,gs], scales [G,M] / [G,N].  fp32 accumulation in ascending
+    group order: ``f += (float(acc_g) * sx[g,m]) * sw[g,n]``
+    (``int4_gemm.cu:1436,1859-1862,2462``)."""
+    G, M, _ = a_codes.shape
+    N = b_codes.shape[1]
+    f = np.zeros((M, N), dtype=F32)
+    for g in range(G):
+        acc = int_gemm(a_codes[g], b_codes[g]).astype(F32)
+        t = (acc * scale_a[g].astype(F32)[:, None]).astype(F32)
+        f = (f + (t * scale_b[g].astype(F32)[None, :]).astype(F32)).astype(F32)
+    return f
+
+
+def linear_grouped(a_codes, b_codes, scale_a, scale_b) -> torch.Tensor:
+    """Per-group-128 W4A4 linear -> bf16 [M,N] (``cutlass_int4_fused_grouped_gemm``, ``int4_gemm.cu:4231``)."""
+    return to_bf16(linear_grouped_f32(a_codes, b_codes, scale_a, scale_b))
+
+
+def grouped_int_partials(a_codes, b_codes) -> np.ndarray:
+    """int32 partial sums per group, [G,M,N]; the integer accumulators the fused kernel drains."""
+    return np.stack([int_gemm(a_codes[g], b_codes[g]) for g in range(a_codes.shape[0])])
+
+
+# --------------------------------------------------------------------------- #
+# MoE composition (no reference counterpart; built from the functions above)
+# --------------------------------------------------------------------------- #
+def moe_route(logits: torch.Tensor, top_k: int = 8):
+    """softmax over experts, top-k, renormalise the k weights to sum to one."""
+    p = torch.softmax(logits.float(), dim=-1)
+    w, idx = torch.topk(p, top_k, dim=-1)
+    w = w / w.sum(dim=-1, keepdim=True)
+    return idx.to(torch.int32), w.to(torch.float32)
+
+
+def moe_sort(expert_ids: np.ndarray, num_experts: int):
+    """Stable counting sort of the flattened (token, slot) pairs by expert.
+    Returns (sorted_pair_ids [T*k], expert_offsets [E+1])."""
+    flat = np.asarray(expert_ids).reshape(-1)
+    order = np.argsort(flat, kind="stable").astype(np.int32)
+    counts = np.bincount(flat, minlength=num_experts)
+    offsets = np.zeros(num_experts + 1, dtype=np.int32)
+    offsets[1:] = np.cumsum(counts)
+    return order, offsets
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """SwiGLU on a bf16 [R, 2I] tensor laid out [gate | up]; fp32 math, bf16 result."""
+    I = gate_up.shape[1] // 2
+    g = gate_up[:, :I].float()
+    u = gate_up[:, I:].float()
+    return (g * torch.sigmoid(g) * u).to(torch.bfloat16)
+
+
+def moe_layer(x: torch.Tensor, expert_ids, expert_w, w_gate_up_q, w_down_q, num_experts: int):
+    """Reference composition for one MoE layer.
+
+    ``x`` bf16 [T,H]; ``expert_ids`` int [T,k]; ``expert_w`` f32 [T,k];
+    ``w_gate_up_q[e] = (codes [G1,2I,gs], scale [G1,2I])`` and
+    ``w_down_q[e] = (codes [G2,H,gs], scale [G2,H])`` are per-expert grouped
+    weight quantisations.  Per expert: grouped-quantise its tokens, grouped
+    linear -> bf16, SwiGLU -> bf16, grouped-quantise, grouped linear -> bf16;
+    then ``out[t] = sum_j w[t,j] * y_j[t]`` accumulated in fp32 in ascending
+    slot order j and cast to bf16."""
+    T, H = x.shape
+    k = expert_ids.shape[1]
+    ids = np.asarray(expert_ids)
+    y = torch.zeros(T, k, H, dtype=torch.float32)
+    for e in range(num_experts):
+        tok, slot = np.nonzero(ids == e)
+        if tok.size == 0:
+            continue
+        xa, sa = quant_grouped(x[tok], GROUP, "activation")
+        wq, ws = w_gate_up_q[e]
+        h = linear_grouped(xa, wq, sa, ws)
+        act = silu_mul(h)
+        ha, hs = quant_grouped(act, GROUP, "activation")
+        dq, ds = w_down_q[e]
+        o = linear_grouped(ha, dq, hs, ds)
+        y[tok, slot] = o.float()
+    out = torch.zeros(T, H, dtype=torch.float32)
+    for j in range(k):
+        out = out + expert_w[:, j : j + 1].float() * y[:, j]
+    return out.to(torch.bfloat16)
