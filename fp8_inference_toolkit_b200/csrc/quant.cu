@@ -69,14 +69,55 @@ __device__ __forceinline__ float absmax8(const Vec8<T>& x) {
   return m;
 }
 
-// Eight codes -> one 32-bit word, element 0 in the lowest nibble.
+// Eight codes -> one 32-bit word, element 0 in the lowest nibble.  Exact-division path.
 template <typename T>
-__device__ __forceinline__ uint32_t pack8(const Vec8<T>& x, float s, bool zero) {
-  if (zero) return 0u;
+__device__ __forceinline__ uint32_t pack8_div(const Vec8<T>& x, float s) {
   uint32_t w = 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i) w |= code4(x.v[i], s) << (4 * i);
   return w;
+}
+
+// Per-slice constants of the fast path: r = RN(1/s).  `fast` is false when r is not a normal
+// number of moderate size, in which case every vector takes the exact-division path.
+struct Recip {
+  float r;
+  bool fast;
+};
+__device__ __forceinline__ Recip make_recip(float s) {
+  Recip q;
+  q.r = __frcp_rn(s);
+  q.fast = (q.r > 7.8886090522e-31f) && (q.r < 1.2676506002e30f);  // 2^-100 < r < 2^100
+  return q;
+}
+
+// Same result as pack8_div, bit for bit, at about a fifth of the instructions.
+//   y8 = x*r + 8 (one FMA)      u = y8 + 1.5*2^23 rounds y8 to the nearest-even integer n+8 in [0,15]
+//   v  = u - 1.5*2^23 = n+8     the eight v's are combined with exact FMAs (16 bits per half)
+// |y8 - 8 - RN(x/s)| < 1.5e-6 for |x/s| <= 8, so unless some y8 lies within 1e-5 of a rounding
+// boundary (k + 0.5) the rounded integers are those of the exact division.  Vectors with such an
+// element (a few in 10^5) are redone with the exact division.  CLAMP: the caller supplied the
+// divisor, so x/s may leave [-8, 7].
+template <typename T, bool CLAMP>
+__device__ __forceinline__ uint32_t pack8(const Vec8<T>& x, float s, Recip q, bool zero) {
+  if (zero) return 0u;
+  if (!q.fast) return pack8_div(x, s);
+  constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+  float v[8], worst = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float y8 = fmaf(x.v[i], q.r, 8.0f);
+    if (CLAMP) y8 = fminf(fmaxf(y8, 0.0f), 15.0f);
+    const float u = y8 + kMagic;
+    v[i] = u - kMagic;
+    worst = fmaxf(worst, fabsf(y8 - v[i]));
+  }
+  if (!(worst <= 0.5f - 1e-5f)) return pack8_div(x, s);
+  const float lo = fmaf(v[3], 4096.f, fmaf(v[2], 256.f, fmaf(v[1], 16.f, v[0])));
+  const float hi = fmaf(v[7], 4096.f, fmaf(v[6], 256.f, fmaf(v[5], 16.f, v[4])));
+  const uint32_t wl = __float_as_uint(lo + kMagic) & 0xFFFFu;
+  const uint32_t wh = __float_as_uint(hi + kMagic) << 16;
+  return (wl | wh) ^ 0x88888888u;  // offset-binary nibbles (n+8) -> two's complement
 }
 
 // silu(g) * u rounded to bf16 and widened again: the value the next quantiser sees.
@@ -156,7 +197,7 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
       if ((lane % LPG) == 0) s_scale[j * GROUPS_PER_STEP + gl][warp] = scale_out(absmax, role);
     }
     if (ok) {
-      const uint32_t w = pack8(v[j], divisor, !GIVEN && absmax == 0.f);
+      const uint32_t w = pack8<T, GIVEN>(v[j], divisor, make_recip(divisor), !GIVEN && absmax == 0.f);
       uint8_t* dst = packed + ((int64_t)g * rows + r) * (GS / 2) + (lane % LPG) * 4;
       *reinterpret_cast<uint32_t*>(dst) = w;
     }
@@ -208,10 +249,11 @@ __global__ void __launch_bounds__(256) quant_rowwise_kernel(const T* __restrict_
     if (t == 0) scale[r] = scale_out(absmax, role);
   }
   uint8_t* dst = packed + r * (int64_t)(K / 2);
+  const Recip rcp = make_recip(divisor);
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int k = c * 2048 + t * 8;
-    if (k < K) *reinterpret_cast<uint32_t*>(dst + k / 2) = pack8(v[c], divisor, !GIVEN && absmax == 0.f);
+    if (k < K) *reinterpret_cast<uint32_t*>(dst + k / 2) = pack8<T, GIVEN>(v[c], divisor, rcp, !GIVEN && absmax == 0.f);
   }
 }
 

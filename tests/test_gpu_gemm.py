@@ -1,0 +1,222 @@
+"""GPU parity: the tcgen05 W4A4 GEMM against the CPU oracle.  int32 accumulators are compared bit
+for bit; bf16 outputs within 1e-2 relative and cosine >= 0.9999 (per-channel outputs are in fact
+compared bit for bit as well, since the epilogue uses the oracle's multiplication order)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import w4a4_oracle as O
+from tests.helpers import assert_close_bf16, dev_f32, dev_packed, rand_codes
+
+pytestmark = pytest.mark.gpu
+
+TUNINGS = [(0, -1), (64, 1), (128, 1), (64, 0), (128, 0), (256, 0)]
+
+
+@pytest.fixture(scope="module")
+def tc():
+    import int4_native_tc
+
+    return int4_native_tc
+
+
+@pytest.fixture()
+def ops():
+    from fp8_inference_toolkit_b200 import ops as _ops
+
+    yield _ops
+    _ops.set_tuning(0, -1)
+    _ops.check_status()
+
+
+@pytest.mark.parametrize("tile_n,swap", TUNINGS)
+def test_kat_small(tc, ops, golden_dir, tile_n, swap):
+    z = np.load(os.path.join(golden_dir, "kat_gemm_4x128x8.npz"))
+    ops.set_tuning(tile_n, swap)
+    out = tc.cutlass_int4_gemm(torch.from_numpy(z["a_packed"]).cuda(), torch.from_numpy(z["b_packed"]).cuda(), 4, 8, 128)
+    ops.check_status()
+    assert out.dtype == torch.int32 and out.shape == (4, 8)
+    assert np.array_equal(out.cpu().numpy(), z["c"])
+
+
+@pytest.mark.parametrize("tile_n,swap", TUNINGS)
+def test_kat_llm_size(tc, ops, golden_dir, tile_n, swap):
+    z = np.load(os.path.join(golden_dir, "kat_gemm_16x2560x2560.npz"))
+    rng = np.random.RandomState(int(z["seed"]))
+    a = rng.randint(-8, 8, size=(16, 2560)).astype(np.int8)
+    b = rng.randint(-8, 8, size=(2560, 2560)).astype(np.int8)
+    ops.set_tuning(tile_n, swap)
+    out = tc.cutlass_int4_gemm(dev_packed(a), dev_packed(b), 16, 2560, 2560)
+    ops.check_status()
+    assert np.array_equal(out.cpu().numpy(), z["c"])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 64), (17, 100, 192), (128, 256, 128), (129, 1000, 2560),
+                                   (300, 257, 320), (1, 4096, 4096), (513, 72, 12288), (40, 24, 65536)])
+def test_int32_ragged_exact(tc, ops, M, N, K):
+    rng = np.random.RandomState(M * 7 + N * 3 + K)
+    a, b = rand_codes(rng, (M, K)), rand_codes(rng, (N, K))
+    ref = O.int_gemm(a, b) if K * 64 < (1 << 24) else (a.astype(np.int64) @ b.astype(np.int64).T).astype(np.int32)
+    for tile_n, swap in [(0, -1), (128, 0), (64, 1)]:
+        ops.set_tuning(tile_n, swap)
+        out = tc.cutlass_int4_gemm(dev_packed(a), dev_packed(b), M, N, K)
+        ops.check_status()
+        assert np.array_equal(out.cpu().numpy(), ref), (tile_n, swap)
+
+
+def test_extreme_codes_exact(tc, ops):
+    """All codes -8: every product is +64, the largest accumulator the path can see."""
+    M, N, K = 130, 260, 12288
+    a = np.full((M, K), -8, np.int8)
+    b = np.full((N, K), -8, np.int8)
+    out = tc.cutlass_int4_gemm(dev_packed(a), dev_packed(b), M, N, K)
+    assert (out == 64 * K).all()
+    b[:] = 7
+    out = tc.cutlass_int4_gemm(dev_packed(a), dev_packed(b), M, N, K)
+    assert (out == -56 * K).all()
+
+
+def test_scaled_kat(tc, ops, golden_dir):
+    z = np.load(os.path.join(golden_dir, "kat_scaled_8x256x16.npz"))
+    out = torch.empty(8, 16, dtype=torch.bfloat16, device="cuda")
+    tc.cutlass_int4_scaled_mm(dev_packed(z["a"]), dev_packed(z["b"]), dev_f32(z["scale_a"]), dev_f32(z["scale_b"]),
+                              out, 8, 16, 256)
+    ops.check_status()
+    o = out.float().cpu().numpy()
+    rel = np.abs(o - z["ref"]) / (np.abs(z["ref"]) + 1e-10)
+    assert rel.max() < 1e-2  # the reference's own assertion
+    assert torch.equal(out.cpu(), O.linear_per_channel(z["a"], z["b"], z["scale_a"], z["scale_b"]))
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 4096, 4096), (200, 520, 2560), (1024, 512, 1024)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scaled_bit_exact(tc, ops, M, N, K, dtype):
+    rng = np.random.RandomState(M + N + K)
+    a, b = rand_codes(rng, (M, K)), rand_codes(rng, (N, K))
+    sa = (rng.rand(M).astype(np.float32) + 0.01) * 0.1
+    sb = (rng.rand(N).astype(np.float32) + 0.01) * 0.01
+    f = O.dequant_per_channel(O.int_gemm(a, b), sa, sb)
+    ref = torch.from_numpy(f).to(dtype)
+    for tile_n, swap in [(0, -1), (128, 0), (256, 0), (128, 1)]:
+        ops.set_tuning(tile_n, swap)
+        out = torch.empty(M, N, dtype=dtype, device="cuda")
+        tc.cutlass_int4_scaled_mm(dev_packed(a), dev_packed(b), dev_f32(sa), dev_f32(sb), out, M, N, K)
+        ops.check_status()
+        assert torch.equal(out.cpu(), ref), (tile_n, swap)
+
+
+def test_config0_end_to_end(tc, ops):
+    """x [16,4096] with outlier channels, W [4096,4096]: quantise on the GPU, per-channel linear,
+    compare codes, scales and bf16 output with the oracle bit for bit."""
+    from fp8_inference_toolkit_b200 import synthetic
+
+    x = synthetic.activations(16, 4096, seed=0)
+    w = synthetic.weights(4096, 4096, seed=1)
+    xp, xs = tc.dynamic_int4_quant(x.cuda())
+    wp, ws = tc.static_int4_weight_quant(w.cuda())
+    xc, xso = O.quant_rowwise(x, "activation")
+    wc, wso = O.quant_rowwise(w, "weight")
+    assert np.array_equal(xp.cpu().numpy(), O.pack_int4(xc)) and np.array_equal(xs.cpu().numpy(), xso)
+    assert np.array_equal(wp.cpu().numpy(), O.pack_int4(wc)) and np.array_equal(ws.cpu().numpy(), wso)
+    out = torch.empty(16, 4096, dtype=torch.bfloat16, device="cuda")
+    tc.cutlass_int4_scaled_mm(xp, wp, xs, ws, out, 16, 4096, 4096)
+    ops.check_status()
+    ref = O.linear_per_channel(xc, wc, xso, wso)
+    assert torch.equal(out.cpu(), ref)
+    full = x.float() @ w.float().T
+    cos = torch.nn.functional.cosine_similarity(out.float().cpu().flatten(), full.flatten(), dim=0)
+    assert cos > 0.5  # sanity only: per-token int4 with x20 outlier channels is a coarse quantiser
+
+
+@pytest.mark.parametrize("M,N,G", [(1, 8, 1), (10, 96, 3), (64, 128, 2), (100, 3584, 20), (257, 300, 5),
+                                   (700, 512, 20), (32, 2560, 76)])
+def test_grouped_partials_and_output(tc, ops, M, N, G):
+    rng = np.random.RandomState(M + 3 * N + G)
+    a, b = rand_codes(rng, (G, M, 128)), rand_codes(rng, (G, N, 128))
+    sa = (rng.rand(G, M).astype(np.float32) + 0.01) * 0.1
+    sb = (rng.rand(G, N).astype(np.float32) + 0.01) * 0.01
+    part = O.grouped_int_partials(a, b)
+    ref = O.linear_grouped(a, b, sa, sb)
+    ap, bp = dev_packed(a), dev_packed(b)
+    for tile_n, swap in TUNINGS:
+        ops.set_tuning(tile_n, swap)
+        got = ops.int4_grouped_partials(ap, bp, M, N, G)
+        ops.check_status()
+        assert np.array_equal(got.cpu().numpy(), part), (tile_n, swap)
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        tc.cutlass_int4_fused_grouped_gemm(ap, bp, dev_f32(sa), dev_f32(sb), out, M, N, 128, G)
+        ops.check_status()
+        assert_close_bf16(out, ref, f"grouped {M}x{N}x{G} tile {tile_n} swap {swap}")
+        # fp32 accumulation differs from the oracle only by FMA contraction: nearly every bf16 is identical
+        assert (out.cpu() == ref).float().mean() > 0.98
+
+
+def test_grouped_aliases_and_checks(tc, ops):
+    rng = np.random.RandomState(9)
+    M, N, G = 10, 64, 2
+    a, b = rand_codes(rng, (G, M, 128)), rand_codes(rng, (G, N, 128))
+    sa, sb = np.ones((G, M), np.float32), np.ones((G, N), np.float32)
+    outs = []
+    for name in ["cutlass_int4_fused_grouped_gemm", "cutlass_int4_fused_grouped_gemm_v5",
+                 "cutlass_int4_fused_grouped_gemm_v7", "cutlass_int4_fused_grouped_gemm_v8",
+                 "cutlass_int4_fused_grouped_gemm_v9", "cutlass_int4_scaled_mm_grouped"]:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        getattr(tc, name)(dev_packed(a), dev_packed(b), dev_f32(sa), dev_f32(sb), out, M, N, 128, G)
+        outs.append(out)
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    out16 = torch.empty(M, N, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="BF16"):
+        tc.cutlass_int4_fused_grouped_gemm(dev_packed(a), dev_packed(b), dev_f32(sa), dev_f32(sb), out16, M, N, 128, G)
+    with pytest.raises(RuntimeError, match="group_size=128"):
+        tc.cutlass_int4_fused_grouped_gemm(dev_packed(a), dev_packed(b), dev_f32(sa), dev_f32(sb), outs[0], M, N, 64, G)
+    with pytest.raises(RuntimeError, match="multiple of 64"):
+        tc.cutlass_int4_gemm(dev_packed(a[0]), dev_packed(b[0]), M, N, 100)
+
+
+@pytest.mark.parametrize("M", [1, 16, 128, 1024])
+@pytest.mark.parametrize("shape", ["qkv", "o", "down"])
+def test_config1_quantised_linear(tc, ops, M, shape):
+    """Qwen3-8B shapes, group-128: GPU quantise + fused GEMM against the oracle end to end."""
+    from fp8_inference_toolkit_b200 import synthetic
+
+    K, N = synthetic.QWEN3_8B_SHAPES[shape]
+    x = synthetic.activations(M, K, seed=0)
+    w = synthetic.weights(N, K, seed=1)
+    xp, xs = tc.dynamic_int4_quant_grouped(x.cuda(), 128)
+    wp, ws = tc.static_int4_weight_quant_grouped(w.cuda(), 128)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    tc.cutlass_int4_fused_grouped_gemm(xp, wp, xs, ws, out, M, N, 128, K // 128)
+    ops.check_status()
+    xc, xso = O.quant_grouped(x, 128, "activation")
+    wc, wso = O.quant_grouped(w, 128, "weight")
+    assert np.array_equal(xp.cpu().numpy(), O.pack_int4(xc))
+    assert np.array_equal(wp.cpu().numpy(), O.pack_int4(wc))
+    assert_close_bf16(out, O.linear_grouped(xc, wc, xso, wso), f"{shape} M={M}")
+
+
+def test_config1_largest_sampled_rows(tc, ops):
+    """M=8192, gate+up (K=4096, N=24576): 32 sampled rows against the oracle, plus linearity in the
+    activation scales (doubling scale_a doubles the output exactly in bf16)."""
+    from fp8_inference_toolkit_b200 import synthetic
+
+    M, (K, N) = 8192, synthetic.QWEN3_8B_SHAPES["gate_up"]
+    G = K // 128
+    x = synthetic.activations(M, K, seed=0, device="cuda")
+    w = synthetic.weights(N, K, seed=1, device="cuda")
+    xp, xs = tc.dynamic_int4_quant_grouped(x, 128)
+    wp, ws = tc.static_int4_weight_quant_grouped(w, 128)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    tc.cutlass_int4_fused_grouped_gemm(xp, wp, xs, ws, out, M, N, 128, G)
+    ops.check_status()
+    rows = np.random.RandomState(1).choice(M, 32, replace=False)
+    ridx = torch.from_numpy(rows).cuda()
+    xc = O.unpack_int4(xp[:, ridx].cpu().numpy())
+    wc = O.unpack_int4(wp.cpu().numpy())
+    ref = O.linear_grouped(xc, wc, xs[:, ridx].cpu().numpy(), ws.cpu().numpy())
+    assert_close_bf16(out[ridx], ref, "gate_up M=8192 sampled rows")
+    out2 = torch.empty_like(out)
+    tc.cutlass_int4_fused_grouped_gemm(xp, wp, (xs * 2).contiguous(), ws, out2, M, N, 128, G)
+    assert torch.equal(out2.float(), out.float() * 2)
