@@ -1,0 +1,338 @@
+#!/usr/bin/env python3
+"""Benchmark of the W4A4 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m M]
+
+One step = one pass of the four Qwen3-8B linears (QKV 4096->6144, O 4096->4096, gate+up
+4096->24576, down 12288->4096) over M tokens with per-group-128 scales: fused activation
+quantise+pack followed by the W4A4 GEMM, i.e. what the linear method's ``apply`` does.  The
+metric is GEMM throughput in TOPS (2*M*N*K per linear) over the whole step.  With N > 1 every
+rank owns N/n output columns of each weight (no collective) and the value is the whole-job
+aggregate.  Prints ONE JSON line on rank 0.
+
+``--impl reference`` times the reference's own CPU formulation of the same path (fp32 quantise,
+pack, int32 ``torch.matmul``, fp32 scales -> bf16) on the host cores, on a bounded row sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+SHAPES = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 24576), ("down", 12288, 4096)]
+METRIC = "w4a4_gemm_tops_qwen3_8b_shapes_g128"
+UNIT = "TOPS"
+GROUP = 128
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- #
+# clocks
+# --------------------------------------------------------------------------- #
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.05)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [c for c in sm if c > 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- #
+# reference CPU formulation (bounded sample)
+# --------------------------------------------------------------------------- #
+def cpu_reference_step(rows: int, seed: int = 0):
+    """The reference's torch CPU path on `rows` tokens of every linear: quantise as
+    benchmark/benchmark_w4a8fp8.py:200-204, pack as int4_native_tc/profile_bottleneck.py:25-28,
+    int32 torch.matmul + fp32 scales as benchmark/verify_int4_matmul_precision.py:23-29
+    (per group, accumulated in fp32), bf16 result.  Returns (seconds, ops)."""
+    from fp8_inference_toolkit_b200 import synthetic
+    from oracle import w4a4_oracle as O  # CPU baseline leg: the one place the bench runs the oracle package
+
+    total_t, total_ops = 0.0, 0
+    for i, (_, K, N) in enumerate(SHAPES):
+        x = synthetic.activations(rows, K, seed)
+        w = synthetic.weights(N, K, seed + 1 + i)
+        G = K // GROUP
+        wq = w.float().reshape(N, G, GROUP)
+        ws = (wq.abs().amax(dim=2).clamp(min=1e-12) / 7.0)
+        wc = torch.clamp(torch.round(wq / ws.unsqueeze(2)), -8, 7).to(torch.int32)  # weights: load time, untimed
+        t0 = time.perf_counter()
+        xq = x.float().reshape(rows, G, GROUP)
+        xs = (xq.abs().amax(dim=2).clamp(min=1e-12) / 7.0)
+        xc = torch.clamp(torch.round(xq / xs.unsqueeze(2)), -8, 7).to(torch.int8)
+        packed = (xc[..., 0::2] & 0x0F) | ((xc[..., 1::2] & 0x0F) << 4)  # noqa: F841  (the pack step)
+        acc = torch.zeros(rows, N, dtype=torch.float32)
+        xi = xc.to(torch.int32)
+        for g in range(G):
+            part = O.int_gemm_int32_torch(xi[:, g], wc[:, g])
+            acc += part.float() * xs[:, g].unsqueeze(1) * ws[:, g].unsqueeze(0)
+        out = acc.to(torch.bfloat16)  # noqa: F841
+        total_t += time.perf_counter() - t0
+        total_ops += 2 * rows * N * K
+    return total_t, total_ops
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    budget = 150.0  # seconds for the whole run
+    t, ops = cpu_reference_step(2)
+    per_row = max(t / 2, 1e-4)
+    rows = int(max(1, min(args.m, budget / (args.steps + args.warmup) / per_row)))
+    for _ in range(args.warmup):
+        cpu_reference_step(rows)
+    t_sum, ops_sum = 0.0, 0
+    for _ in range(args.steps):
+        t, ops = cpu_reference_step(rows)
+        t_sum += t
+        ops_sum += ops
+    value = ops_sum / t_sum / 1e12
+    sample = f"{rows} of {args.m} token rows of each of the 4 linears per step (activation quantise+pack, int32 torch.matmul per group, fp32 scales)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_sum / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s4*s4->s32, f32 dequant",
+        "data": "synthetic", "config": workload_config(args.m, 1),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(M: int, n_gpus: int) -> dict:
+    return {
+        "workload": f"BASELINE configs[1]: dense W4A4 per-group-128 linears at Qwen3-8B shapes "
+                    f"(K,N) in (4096,6144),(4096,4096),(4096,24576),(12288,4096), M={M} tokens; "
+                    f"step = quantise+pack of the activations then the fused GEMM, for each shape",
+        "M": M, "group_size": GROUP, "n_split": n_gpus,
+        "l2": "inputs larger than L2 (weights + activations + outputs of one step exceed 126 MB)",
+    }
+
+
+# --------------------------------------------------------------------------- #
+# our arm
+# --------------------------------------------------------------------------- #
+def gemm_bytes(M, N, K):
+    G = K // GROUP
+    return M * K // 2 + N * K // 2 + 4 * G * (M + N) + 2 * M * N
+
+
+def run_ours(args) -> None:
+    import torch.distributed as dist
+
+    import int4_native_tc as tc
+    from fp8_inference_toolkit_b200 import ops, synthetic
+    from fp8_inference_toolkit_b200.linear import W4A4Linear
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    M = args.m
+    peaks = load_peaks()
+
+    # ---- inputs resident in HBM: activations per shape, this rank's column slice of the weights
+    layers, xs_dev = [], []
+    for i, (name, K, N) in enumerate(SHAPES):
+        assert N % world == 0
+        n_loc = N // world
+        w = synthetic.weights(N, K, seed=1 + i)[rank * n_loc:(rank + 1) * n_loc].to(dev)
+        lin = W4A4Linear(K, n_loc, per_channel=False, device=dev)
+        lin.weight.data.copy_(w)
+        lin.quantize_()
+        layers.append(lin)
+        xs_dev.append(synthetic.activations(M, K, seed=0, device=dev))
+        del w
+    outs = [torch.empty(M, l.out_features, dtype=torch.bfloat16, device=dev) for l in layers]
+    ops_per_step = sum(2 * M * N * K for _, K, N in SHAPES)  # whole job, all ranks
+
+    def step(events=None):
+        for i, (name, K, N) in enumerate(SHAPES):
+            lin = layers[i]
+            xp, xsc = tc.dynamic_int4_quant_grouped(xs_dev[i], GROUP)
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+            tc.cutlass_int4_fused_grouped_gemm(xp, lin.weight_int4, xsc, lin.weight_scale, outs[i], M,
+                                               lin.out_features, GROUP, K // GROUP)
+            if events is not None:
+                e1.record()
+                events.append((i, e0, e1))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ops.check_status()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    events = []
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        step(events)
+    t1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_status()
+    elapsed_ms = t0.elapsed_time(t1)
+    if world > 1:
+        tt = torch.tensor([elapsed_ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        elapsed_ms = tt.item()
+    ms_per_step = elapsed_ms / args.steps
+    value = ops_per_step / (ms_per_step * 1e-3) / 1e12
+
+    # dominant kernel: the W4A4 GEMM (this rank's launches), averaged per shape over the timed region
+    per_shape = {}
+    for i, e0, e1 in events:
+        per_shape.setdefault(i, []).append(e0.elapsed_time(e1) * 1e-3)
+    gemm_s = sum(statistics.mean(v) for v in per_shape.values())
+    gemm_ops_rank = ops_per_step / world
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    achieved = gemm_ops_rank / gemm_s / 1e12
+
+    # ---- e2e: host buffers through the linear module, copies inside the timed region
+    x_host = [synthetic.activations(M, K, seed=0).pin_memory() for _, K, _ in SHAPES]
+    o_host = [torch.empty(M, l.out_features, dtype=torch.bfloat16).pin_memory() for l in layers]
+    h2d = sum(x.numel() * 2 for x in x_host)
+    d2h = sum(o.numel() * 2 for o in o_host)
+
+    def e2e_step():
+        for i, lin in enumerate(layers):
+            xd = x_host[i].to(dev, non_blocking=True)
+            y = lin(xd)
+            o_host[i].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e2e_steps = max(1, min(args.steps, 5))
+    w0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = (time.perf_counter() - w0) / e2e_steps
+    if world > 1:
+        tt = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_s = tt.item()
+    e2e_val = ops_per_step / e2e_s / 1e12
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "s4*s4->s32, f32 dequant", "data": "synthetic",
+            "config": workload_config(M, world), "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h * 1,
+                    "ms_per_step": e2e_s * 1e3},
+            "gpu_launches": args.steps * 2 * len(SHAPES),
+            "roofline": {
+                "bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOPS",
+                "frac": achieved / int8_peak, "traffic": None,
+                "kernel": "w4a4_gemm_kernel (per-group-128 epilogue), 4 launches per step",
+                "peak_source": f"2 x bf16 burst of MEASURED_PEAKS.json ({peaks['source']}); int8 dense = 2 x bf16 on B200",
+                "per_shape_us": {SHAPES[i][0]: statistics.mean(v) * 1e6 for i, v in per_shape.items()},
+            },
+        }
+        if world == 1:
+            t, cops = cpu_reference_step(16)
+            t, cops = cpu_reference_step(16)
+            line["cpu_baseline"] = {
+                "value": cops / t / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                "sample": "16 of %d token rows of each of the 4 linears, one pass" % M,
+            }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=8192, help="tokens per step")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
