@@ -291,6 +291,8 @@ def run_ours(args) -> None:
         e2e_s = tt.item()
     e2e_val = ops_per_step / e2e_s / 1e12
 
+    moe_result = bench_moe(args, world, rank, dev, peaks)
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -308,6 +310,7 @@ def run_ours(args) -> None:
                 "per_shape_us": {SHAPES[i][0]: statistics.mean(v) * 1e6 for i, v in per_shape.items()},
             },
         }
+        line["moe"] = moe_result
         if world == 1:
             t, cops = cpu_reference_step(16)
             t, cops = cpu_reference_step(16)
@@ -318,6 +321,61 @@ def run_ours(args) -> None:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_moe(args, world, rank, dev, peaks) -> dict:
+    """MoE grouped W4A4 layer (BASELINE configs[3]): 128 experts, top-8, 4096 tokens, hidden 2048,
+    intermediate 768, group-128; experts and tokens split evenly across ranks, all-to-all dispatch and
+    combine.  Timed from (token rows, expert ids, routing weights) to the combined bf16 output."""
+    import torch.distributed as dist
+
+    from fp8_inference_toolkit_b200 import moe, moe_ep, ops, synthetic
+
+    T, H, I, E, k = 4096, 2048, 768, 128, 8
+    t_loc, e_loc = T // world, E // world
+    x, logits = synthetic.moe_inputs(T, H, E, k, seed=0)
+    ids, w = moe.moe_route(logits.to(dev), k)
+    sl = slice(rank * t_loc, (rank + 1) * t_loc)
+    x_l, ids_l, w_l = x[sl].to(dev).contiguous(), ids[sl].contiguous(), w[sl].contiguous()
+    gu, dn = synthetic.moe_weights(e_loc, H, I, seed=10 + rank, device=dev)
+    mw = moe.MoEWeights.quantize(gu, dn)
+    del gu, dn
+
+    def layer():
+        if world == 1:
+            return moe.moe_layer(x_l, ids_l, w_l, mw)
+        return moe_ep.moe_layer_ep(x_l, ids_l, w_l, mw, E)
+
+    for _ in range(5):
+        layer()
+    ops.check_status()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    steps = max(args.steps, 10)
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        layer()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        tt = torch.tensor([ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = tt.item()
+    ops.check_status()
+    ops_layer = T * k * (2 * H * 2 * I + 2 * I * H)
+    int8_peak = 2.0 * peaks["bf16_tflops"] * world
+    return {
+        "metric": "moe_w4a4_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "ms_per_layer": ms, "tops": ops_layer / (ms * 1e-3) / 1e12,
+        "frac_of_int8_peak": ops_layer / (ms * 1e-3) / 1e12 / int8_peak,
+        "config": {"workload": "BASELINE configs[3]: 128 experts, top-8 of softmax(N(0,1) logits), 4096 tokens, "
+                               "hidden 2048, intermediate 768, group-128; %d experts and %d tokens per rank"
+                               % (e_loc, t_loc),
+                   "timed": "sort + dispatch + gather-quantise + gate/up GEMM + SwiGLU-quantise + down GEMM + combine"},
+    }
 
 
 def main() -> None:
