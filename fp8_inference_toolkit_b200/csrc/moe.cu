@@ -176,6 +176,66 @@ extern "C" int i4tc_moe_sort(const int32_t* expert_ids, int64_t num_pairs, int64
                          static_cast<int32_t*>(scratch), st);
 }
 
+// ------------------------------------------------------------------------------------------
+// Sort variant that allocates nothing.
+//
+// Some callers cannot obtain device memory at call time: a serving engine that handed every free
+// byte of HBM to its own cache pool at start-up (a later cudaMalloc fails), or a latency-critical
+// loop that must not pay for cudaMalloc / cudaFree, which synchronise the whole device.  For them
+// the per-chunk histogram scratch of the sort lives in this fixed array instead of a caller buffer.
+// Every GPU that loads the library holds the 64 KiB until the process exits.
+//
+// In host code `g_sort_scratch` is only a host-side stand-in for the symbol, never a device
+// address: the address is resolved once per device with cudaGetSymbolAddress (below) and that
+// pointer is what the kernels receive.
+// ------------------------------------------------------------------------------------------
+constexpr int kNoAllocScratchInts = 16384;  // ceil(num_pairs / 1024) * num_experts must not exceed this
+static __device__ __align__(256) int32_t g_sort_scratch[kNoAllocScratchInts];
+
+static int32_t* g_sort_scratch_ptr[64] = {nullptr};
+
+// Resolves the device address of g_sort_scratch for `device` (which must be current).
+static int sort_scratch_for(int device, int32_t** out) {
+  I4TC_REQUIRE(device >= 0 && device < 64, I4TC_EINVAL, "device ordinal %d out of range", device);
+  if (g_sort_scratch_ptr[device] == nullptr) {
+    int32_t* ptr = nullptr;
+    I4TC_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_sort_scratch));
+    I4TC_REQUIRE(ptr != nullptr, I4TC_EDEVICE, "could not resolve the device address of the sort scratch");
+    g_sort_scratch_ptr[device] = ptr;
+  }
+  *out = g_sort_scratch_ptr[device];
+  return I4TC_OK;
+}
+
+extern "C" int64_t i4tc_moe_sort_noalloc_max_scratch_ints(void) { return kNoAllocScratchInts; }
+
+extern "C" int i4tc_moe_sort_noalloc(const int32_t* expert_ids, int64_t num_pairs, int64_t num_experts,
+                                     int32_t* sorted_pairs, int32_t* inv_pairs, int32_t* expert_offsets,
+                                     int device, void* stream) {
+  I4TC_REQUIRE(num_pairs >= 0 && num_pairs < (1ll << 31), I4TC_EINVAL, "num_pairs out of range");
+  I4TC_REQUIRE(num_experts > 0 && num_experts <= kMaxExperts, I4TC_EINVAL, "num_experts must be in [1, %d]",
+               kMaxExperts);
+  const int64_t chunks = (num_pairs + kSortChunk - 1) / kSortChunk;
+  I4TC_REQUIRE(chunks * num_experts <= kNoAllocScratchInts, I4TC_EINVAL,
+               "i4tc_moe_sort_noalloc: ceil(num_pairs/1024) * num_experts = %lld exceeds the built-in scratch of "
+               "%d entries; use i4tc_moe_sort with a caller-provided scratch buffer",
+               (long long)(chunks * num_experts), kNoAllocScratchInts);
+  I4TC_REQUIRE(expert_offsets != nullptr, I4TC_EINVAL, "null expert_offsets");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (num_pairs == 0) {
+    I4TC_CUDA(cudaMemsetAsync(expert_offsets, 0, (num_experts + 1) * sizeof(int32_t), st));
+    return I4TC_OK;
+  }
+  I4TC_REQUIRE(expert_ids && sorted_pairs, I4TC_EINVAL, "null pointer");
+  int32_t* scratch = nullptr;
+  if (int rc = sort_scratch_for(device, &scratch)) return rc;
+  // Nothing in the scratch has to start at zero: the histogram pass writes every entry that the
+  // scan and scatter passes of this call read, so the previous call's contents are never seen.
+  return moe_sort_launch(expert_ids, num_pairs, num_experts, sorted_pairs, inv_pairs, expert_offsets, scratch, st);
+}
+
 extern "C" int i4tc_moe_combine(const void* y, const int32_t* inv_pairs, const float* w, int64_t T, int64_t top_k,
                                 int64_t H, void* out, int device, void* stream) {
   I4TC_REQUIRE(T >= 0 && top_k > 0 && H >= 0, I4TC_EINVAL, "bad sizes");

@@ -131,6 +131,23 @@ int i4tc_moe_sort(const int32_t* expert_ids, int64_t num_pairs, int64_t num_expe
                   int32_t* sorted_pairs, int32_t* inv_pairs, int32_t* expert_offsets,
                   void* scratch, int64_t scratch_bytes, int device, void* stream);
 
+/* The same sort for callers that cannot allocate device memory when they call it -- for example an
+ * inference server whose own pool already owns all free HBM, or a latency-critical loop that must
+ * avoid cudaMalloc/cudaFree because they synchronise the device.  It has no counterpart in the
+ * reference.  The scratch is a fixed 64 KiB array inside the library (held by every GPU that loads
+ * it, until exit), so the limit is ceil(num_pairs / 1024) * num_experts <= 16384 entries
+ * (i4tc_moe_sort_noalloc_max_scratch_ints()); larger problems are rejected with I4TC_EINVAL and
+ * should use i4tc_moe_sort.  The call allocates nothing: no cudaMalloc, no cudaFree, no library
+ * allocator.  The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call before starting any stream capture.  All calls
+ * share the one array, which keeps whatever the last call left in it (no entry has to start at
+ * zero: each call overwrites what it reads), so two calls that overlap on the GPU -- different
+ * streams, or different threads -- race; keep them ordered.  Outputs are identical to i4tc_moe_sort. */
+int64_t i4tc_moe_sort_noalloc_max_scratch_ints(void);
+int i4tc_moe_sort_noalloc(const int32_t* expert_ids, int64_t num_pairs, int64_t num_experts,
+                          int32_t* sorted_pairs, int32_t* inv_pairs, int32_t* expert_offsets,
+                          int device, void* stream);
+
 /* Gather rows x[sorted_pairs[i] / top_k] and grouped-quantise them (gs=128, activation
  * role) straight into expert-sorted group-major layout: packed [K/128, P, 64], scale [K/128, P]. */
 int i4tc_moe_gather_quant(const void* x, int dtype, int64_t K, int64_t ldx,
