@@ -378,15 +378,73 @@ def bench_moe(args, world, rank, dev, peaks) -> dict:
     }
 
 
+def run_quant(args) -> None:
+    """BASELINE configs[2]: fused activation quantise+pack, bf16 [M, K] with 1 % outlier channels x20,
+    per-token and per-group-128 scales.  One step = both variants over the same input; HBM-bound."""
+    import int4_native_tc as tc
+    from fp8_inference_toolkit_b200 import synthetic
+
+    torch.cuda.set_device(0)
+    M, K = args.m, args.k
+    peaks = load_peaks()
+    xs = [synthetic.activations(M, K, seed=i, outlier_frac=0.01, device="cuda") for i in range(2)]
+    ev = {"row": [], "group": []}
+
+    def step(timed):
+        for i, x in enumerate(xs):
+            for mode in ("row", "group"):
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+                if mode == "row":
+                    tc.dynamic_int4_quant(x)
+                else:
+                    tc.dynamic_int4_quant_grouped(x, GROUP)
+                e1.record()
+                if timed:
+                    ev[mode].append((e0, e1))
+
+    for _ in range(max(args.warmup, 3)):
+        step(False)
+    torch.cuda.synchronize()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        step(True)
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / args.steps
+    res = {}
+    for mode, gs in (("row", 1), ("group", K // GROUP)):
+        byts = 2 * M * K + M * K // 2 + 4 * M * gs
+        us = statistics.mean(a.elapsed_time(b) for a, b in ev[mode]) * 1e3
+        res[mode] = {"us": us, "GBs": byts / us / 1e3, "frac": byts / us / 1e3 / peaks["hbm_gbs"], "bytes": byts}
+    tot_bytes = 2 * (res["row"]["bytes"] + res["group"]["bytes"])
+    print(json.dumps({
+        "metric": "int4_quant_pack_gbs", "value": tot_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "dtype": "f32 on bf16 -> s4", "data": "synthetic",
+        "config": {"workload": f"BASELINE configs[2]: fused quantise+pack, bf16 [{M},{K}], per-token and per-group-128",
+                   "l2": "two input copies of %d MB alternate" % (2 * M * K // 2 ** 20)},
+        "roofline": {"bound": "hbm", "achieved": res["group"]["GBs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": res["group"]["frac"], "traffic": None, "kernel": "quant_grouped_kernel",
+                     "per_kernel": res},
+    }), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="linear", choices=["linear", "quant"],
+                    help="linear: the headline W4A4 linears (default); quant: quantise+pack only")
+    ap.add_argument("--k", type=int, default=12288, help="row length for --workload quant")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=8192, help="tokens per step")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "quant":
+        run_quant(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

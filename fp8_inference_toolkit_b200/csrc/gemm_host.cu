@@ -1,6 +1,7 @@
 // Host side of the dense and MoE W4A4 GEMM entry points: argument checks, tensor maps,
 // tile-shape choice and launch.
 #include "gemm.cuh"
+#include <stdlib.h>
 
 namespace i4tc {
 
@@ -15,7 +16,7 @@ struct Shape {
 // Picks the tile width and operand orientation.  Small M puts the weights on the 128-row side of
 // the MMA (so that no tensor-core rows are wasted on padding and more CTAs stream weights);
 // otherwise the width with the fewest (cost-weighted) waves over the SMs wins.
-static Shape choose_shape(long long M, long long N, int sms, bool allow_swap) {
+static Shape choose_shape(long long M, long long N, int sms, bool allow_swap, bool group_mode) {
   Shape s;
   s.swap = allow_swap && M <= 128;
   if (g_force_swap >= 0 && allow_swap) s.swap = g_force_swap != 0;
@@ -27,6 +28,7 @@ static Shape choose_shape(long long M, long long N, int sms, bool allow_swap) {
     s.bn = M <= 64 ? 64 : 128;
     return s;
   }
+  (void)group_mode;
   const long long mt = (M + 127) / 128;
   double best = 1e30;
   s.bn = 256;
@@ -67,7 +69,8 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   I4TC_CUDA(guard.err);
   I4TC_REQUIRE(d.M < (1ll << 31) - 256 && d.N < (1ll << 31) - 256, I4TC_EINVAL, "M or N too large");
 
-  const Shape sh = choose_shape(d.M, d.N, info->sm_count, true);
+  const bool group_mode = d.epi_mode == EPI_GROUP || d.epi_mode == EPI_GROUP_INT32;
+  const Shape sh = choose_shape(d.M, d.N, info->sm_count, true, group_mode);
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.G = d.G;
@@ -192,7 +195,6 @@ extern "C" int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, con
   // Average rows per expert decide the tile width: narrow tiles keep more SMs busy when the
   // per-expert problems are small.
   int bn = g_force_bn ? g_force_bn : 128;
-  if (!g_force_bn && N % 256 == 0 && num_pairs / num_experts >= 512) bn = 256;
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.P_rows = (int)num_pairs;

@@ -21,7 +21,9 @@ __device__ __forceinline__ float scale_out(float absmax, int role) {
   return absmax == 0.0f ? 1.0f : s;
 }
 
-// Eight consecutive elements as floats, loaded with 128-bit loads.
+// Eight consecutive elements.  bf16 keeps the raw 128 bits (4 registers) and widens on use; the
+// absmax is taken on the packed halves (|x| and max are exact in bf16).  Other types are widened
+// at load time.
 template <typename T>
 struct Vec8 {
   float v[8];
@@ -30,18 +32,45 @@ struct Vec8 {
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = 0.f;
   }
+  __device__ __forceinline__ float get(int i) const { return v[i]; }
+  __device__ __forceinline__ void set_all(const float (&f)[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = f[i];
+  }
+  __device__ __forceinline__ float absmax() const {
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+    return m;
+  }
 };
 
 template <>
-__device__ __forceinline__ void Vec8<__nv_bfloat16>::load(const __nv_bfloat16* p) {
-  uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
-  uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+struct Vec8<__nv_bfloat16> {
+  uint32_t w[4];
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+    w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
   }
-}
+  __device__ __forceinline__ void zero() { w[0] = w[1] = w[2] = w[3] = 0u; }
+  __device__ __forceinline__ float get(int i) const {
+    return (i & 1) ? __uint_as_float(w[i >> 1] & 0xFFFF0000u) : __uint_as_float(w[i >> 1] << 16);
+  }
+  __device__ __forceinline__ void set_all(const float (&f)[8]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  __device__ __forceinline__ float absmax() const {
+    __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[0]));
+#pragma unroll
+    for (int i = 1; i < 4; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[i])));
+    return fmaxf(__low2float(m), __high2float(m));
+  }
+};
+
 template <>
 __device__ __forceinline__ void Vec8<__half>::load(const __half* p) {
   uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
@@ -62,61 +91,74 @@ __device__ __forceinline__ void Vec8<float>::load(const float* p) {
 }
 
 template <typename T>
-__device__ __forceinline__ float absmax8(const Vec8<T>& x) {
-  float m = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(x.v[i]));
-  return m;
-}
+__device__ __forceinline__ float absmax8(const Vec8<T>& x) { return x.absmax(); }
 
 // Eight codes -> one 32-bit word, element 0 in the lowest nibble.  Exact-division path.
 template <typename T>
 __device__ __forceinline__ uint32_t pack8_div(const Vec8<T>& x, float s) {
   uint32_t w = 0;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) w |= code4(x.v[i], s) << (4 * i);
+  for (int i = 0; i < 8; ++i) w |= code4(x.get(i), s) << (4 * i);
   return w;
 }
 
-// Per-slice constants of the fast path: r = RN(1/s).  `fast` is false when r is not a normal
-// number of moderate size, in which case every vector takes the exact-division path.
+// Reciprocal of the divisor for the fast path.  rcp.approx is within 2^-23 of 1/s; `fast` is false
+// when r is not a normal number of moderate size, and then every vector takes the exact path.
 struct Recip {
-  float r;
+  float r;      // approximately 1 / divisor
+  float base;   // absmax (FROM_ABSMAX) or the divisor itself
   bool fast;
 };
-__device__ __forceinline__ Recip make_recip(float s) {
+// FROM_ABSMAX: the divisor is absmax / 7, so r = 7 * rcp(absmax) (within 2^-22 of 1 / RN(absmax/7));
+// the IEEE division absmax / 7 is then only needed on the rare exact path.
+template <bool FROM_ABSMAX>
+__device__ __forceinline__ Recip make_recip(float base) {
   Recip q;
-  q.r = __frcp_rn(s);
+  q.base = base;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(q.r) : "f"(base));
+  if (FROM_ABSMAX) q.r *= 7.0f;
   q.fast = (q.r > 7.8886090522e-31f) && (q.r < 1.2676506002e30f);  // 2^-100 < r < 2^100
   return q;
 }
+template <bool FROM_ABSMAX>
+__device__ __forceinline__ float exact_divisor(const Recip& q) {
+  return FROM_ABSMAX ? __fdiv_rn(q.base, 7.0f) : q.base;
+}
 
-// Same result as pack8_div, bit for bit, at about a fifth of the instructions.
+// Same result as pack8_div, bit for bit, at a fraction of the instructions (packed f32x2 math).
 //   y8 = x*r + 8 (one FMA)      u = y8 + 1.5*2^23 rounds y8 to the nearest-even integer n+8 in [0,15]
 //   v  = u - 1.5*2^23 = n+8     the eight v's are combined with exact FMAs (16 bits per half)
-// |y8 - 8 - RN(x/s)| < 1.5e-6 for |x/s| <= 8, so unless some y8 lies within 1e-5 of a rounding
-// boundary (k + 0.5) the rounded integers are those of the exact division.  Vectors with such an
-// element (a few in 10^5) are redone with the exact division.  CLAMP: the caller supplied the
-// divisor, so x/s may leave [-8, 7].
+// |y8 - 8 - RN(x/s)| < 3e-6 for |x/s| <= 8 (r within 2^-22 of 1/s, one rounding in the FMA, one in
+// the exact quotient), so unless some y8 lies within 1e-5 of a rounding boundary (k + 0.5) the
+// rounded integers are those of the exact division.  Vectors with such an element (a few in 10^5)
+// are redone with the exact division.  CLAMP: the caller supplied the divisor, so x/s may leave [-8, 7].
 template <typename T, bool CLAMP>
-__device__ __forceinline__ uint32_t pack8(const Vec8<T>& x, float s, Recip q, bool zero) {
+__device__ __forceinline__ uint32_t pack8(const Vec8<T>& x, const Recip& q, bool zero) {
   if (zero) return 0u;
-  if (!q.fast) return pack8_div(x, s);
+  if (!q.fast) return pack8_div(x, exact_divisor<!CLAMP>(q));
   constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
-  float v[8], worst = 0.f;
+  const float2 r2 = make_float2(q.r, q.r), eight = make_float2(8.f, 8.f), mg = make_float2(kMagic, kMagic);
+  const float2 nmg = make_float2(-kMagic, -kMagic);
+  float2 v[4];  // v[i] = (n_i + 8, n_{i+4} + 8)
+  float worst = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float y8 = fmaf(x.v[i], q.r, 8.0f);
-    if (CLAMP) y8 = fminf(fmaxf(y8, 0.0f), 15.0f);
-    const float u = y8 + kMagic;
-    v[i] = u - kMagic;
-    worst = fmaxf(worst, fabsf(y8 - v[i]));
+  for (int i = 0; i < 4; ++i) {
+    float2 y8 = __ffma2_rn(make_float2(x.get(i), x.get(i + 4)), r2, eight);
+    if (CLAMP) {
+      y8.x = fminf(fmaxf(y8.x, 0.0f), 15.0f);
+      y8.y = fminf(fmaxf(y8.y, 0.0f), 15.0f);
+    }
+    v[i] = __fadd2_rn(__fadd2_rn(y8, mg), nmg);
+    const float2 e = __fadd2_rn(y8, make_float2(-v[i].x, -v[i].y));
+    worst = fmaxf(worst, fmaxf(fabsf(e.x), fabsf(e.y)));
   }
-  if (!(worst <= 0.5f - 1e-5f)) return pack8_div(x, s);
-  const float lo = fmaf(v[3], 4096.f, fmaf(v[2], 256.f, fmaf(v[1], 16.f, v[0])));
-  const float hi = fmaf(v[7], 4096.f, fmaf(v[6], 256.f, fmaf(v[5], 16.f, v[4])));
-  const uint32_t wl = __float_as_uint(lo + kMagic) & 0xFFFFu;
-  const uint32_t wh = __float_as_uint(hi + kMagic) << 16;
+  if (!(worst <= 0.5f - 1e-5f)) return pack8_div(x, exact_divisor<!CLAMP>(q));
+  // (lo, hi) = v0 + 16 v1 + 256 v2 + 4096 v3 for elements 0..3 and 4..7: exact, below 2^16
+  float2 lh = __ffma2_rn(v[3], make_float2(4096.f, 4096.f),
+                         __ffma2_rn(v[2], make_float2(256.f, 256.f), __ffma2_rn(v[1], make_float2(16.f, 16.f), v[0])));
+  lh = __fadd2_rn(lh, mg);
+  const uint32_t wl = __float_as_uint(lh.x) & 0xFFFFu;
+  const uint32_t wh = __float_as_uint(lh.y) << 16;
   return (wl | wh) ^ 0x88888888u;  // offset-binary nibbles (n+8) -> two's complement
 }
 
@@ -136,80 +178,104 @@ __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
 // GIVEN: divisors come from `given_scale` (group-major) instead of the absmax.
 // ------------------------------------------------------------------------------------------
 constexpr int kQRows = 8;
-constexpr int kQSteps = 4;
-constexpr int kQSeg = 32 * 8 * kQSteps;  // 1024 elements
+constexpr int kQVecs = 4;                 // 8-element vectors per lane per segment
+constexpr int kQLane = 8 * kQVecs;        // 32 consecutive elements per lane
+constexpr int kQSeg = 32 * kQLane;        // 1024 elements per warp per segment
 
+template <typename T, int MODE>
+__device__ __forceinline__ void load_segment(Vec8<T> (&v)[kQVecs], const T* src, int k, int K, bool row_ok) {
+  // k = first element of this lane; K % 32 == 0, so the lane's 32 elements are all in range or none
+  if (row_ok && k < K) {
+#pragma unroll
+    for (int j = 0; j < kQVecs; ++j) {
+      if (MODE == 2) {
+        Vec8<T> g, u;
+        g.load(src + k + 8 * j);
+        u.load(src + K + k + 8 * j);
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = silu_mul_bf16(g.get(i), u.get(i));
+        v[j].set_all(f);
+      } else {
+        v[j].load(src + k + 8 * j);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kQVecs; ++j) v[j].zero();
+  }
+}
+
+// Block = 8 warps = 8 consecutive rows.  In a segment every lane owns 32 consecutive elements
+// (64 bytes of bf16), so a group of GS elements is LPG = GS/32 adjacent lanes: its absmax costs
+// log2(LPG) shuffles, its reciprocal is formed once per lane, and each lane leaves 16 packed bytes
+// with one 128-bit store.  The block walks `segs_per_block` segments of its rows and loads segment
+// s+1 while it quantises segment s.
 template <typename T, int LPG, int MODE, bool GIVEN>
 __global__ void __launch_bounds__(256) quant_grouped_kernel(
     const T* __restrict__ x, int64_t rows, int K, int64_t ldx, const int32_t* __restrict__ row_index,
     int index_div, const float* __restrict__ given_scale, uint8_t* __restrict__ packed,
-    float* __restrict__ scale, int role) {
-  constexpr int GS = LPG * 8;
-  constexpr int GROUPS_PER_STEP = 32 / LPG;
-  constexpr int GROUPS_PER_SEG = GROUPS_PER_STEP * kQSteps;
-  __shared__ float s_scale[GROUPS_PER_SEG][kQRows];
+    float* __restrict__ scale, int role, int segs_per_block) {
+  constexpr int GS = LPG * kQLane;
+  constexpr int GROUPS_PER_SEG = 32 / LPG;
+  __shared__ float s_absmax[2][GROUPS_PER_SEG][kQRows];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t r0 = (int64_t)blockIdx.x * kQRows;
   const int64_t r = r0 + warp;
-  const int k0 = blockIdx.y * kQSeg;
   const bool row_ok = r < rows;
+  const int nseg = (K + kQSeg - 1) / kQSeg;
+  const int seg_begin = blockIdx.y * segs_per_block;
+  const int seg_end = min(nseg, seg_begin + segs_per_block);
 
-  Vec8<T> v[kQSteps];
   const T* src = nullptr;
   if (row_ok) {
     int64_t sr = r;
     if (MODE == 1) sr = row_index[r] / index_div;
     src = x + sr * ldx;
   }
-#pragma unroll
-  for (int j = 0; j < kQSteps; ++j) {
-    const int k = k0 + j * 256 + lane * 8;
-    if (row_ok && k < K) {
-      if (MODE == 2) {
-        Vec8<T> g, u;
-        g.load(src + k);
-        u.load(src + K + k);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[j].v[i] = silu_mul_bf16(g.v[i], u.v[i]);
-      } else {
-        v[j].load(src + k);
-      }
-    } else {
-      v[j].zero();
-    }
-  }
-
-  const int gl = lane / LPG;  // group inside a step
-#pragma unroll
-  for (int j = 0; j < kQSteps; ++j) {
-    const int k = k0 + j * 256 + lane * 8;
+  Vec8<T> cur[kQVecs], nxt[kQVecs];
+  load_segment<T, MODE>(cur, src, seg_begin * kQSeg + lane * kQLane, K, row_ok);
+  for (int seg = seg_begin; seg < seg_end; ++seg) {
+    const int k = seg * kQSeg + lane * kQLane;
+    if (seg + 1 < seg_end) load_segment<T, MODE>(nxt, src, k + kQSeg, K, row_ok);
+    const int par = seg & 1;
     const bool ok = row_ok && k < K;
     const int g = k / GS;
-    float divisor, absmax = 0.f;
+    Recip q;
+    float absmax = 0.f;
     if (GIVEN) {
-      divisor = ok ? __ldg(given_scale + (int64_t)g * rows + r) : 1.f;
+      q = make_recip<false>(ok ? __ldg(given_scale + (int64_t)g * rows + r) : 1.f);
     } else {
-      absmax = absmax8(v[j]);
+#pragma unroll
+      for (int j = 0; j < kQVecs; ++j) absmax = fmaxf(absmax, cur[j].absmax());
 #pragma unroll
       for (int o = 1; o < LPG; o <<= 1) absmax = fmaxf(absmax, __shfl_xor_sync(0xffffffffu, absmax, o));
-      divisor = __fdiv_rn(absmax, 7.0f);
-      if ((lane % LPG) == 0) s_scale[j * GROUPS_PER_STEP + gl][warp] = scale_out(absmax, role);
+      q = make_recip<true>(absmax);
+      if ((lane % LPG) == 0) s_absmax[par][lane / LPG][warp] = absmax;
     }
     if (ok) {
-      const uint32_t w = pack8<T, GIVEN>(v[j], divisor, make_recip(divisor), !GIVEN && absmax == 0.f);
-      uint8_t* dst = packed + ((int64_t)g * rows + r) * (GS / 2) + (lane % LPG) * 4;
-      *reinterpret_cast<uint32_t*>(dst) = w;
+      const bool zero = !GIVEN && absmax == 0.f;
+      uint4 w;
+      w.x = pack8<T, GIVEN>(cur[0], q, zero);
+      w.y = pack8<T, GIVEN>(cur[1], q, zero);
+      w.z = pack8<T, GIVEN>(cur[2], q, zero);
+      w.w = pack8<T, GIVEN>(cur[3], q, zero);
+      uint8_t* dst = packed + ((int64_t)g * rows + r) * (GS / 2) + (lane % LPG) * 16;
+      *reinterpret_cast<uint4*>(dst) = w;
     }
-  }
-  if (!GIVEN) {
-    __syncthreads();
-    // 8 consecutive rows of one group are 32 contiguous bytes of the [G, rows] scale array.
-    for (int t = threadIdx.x; t < GROUPS_PER_SEG * kQRows; t += 256) {
-      const int gi = t / kQRows, rr = t % kQRows;
-      const int g = k0 / GS + gi;
-      if (g * GS < K && r0 + rr < rows) scale[(int64_t)g * rows + r0 + rr] = s_scale[gi][rr];
+    if (!GIVEN) {
+      __syncthreads();
+      // 8 consecutive rows of one group are 32 contiguous bytes of the [G, rows] scale array; the
+      // IEEE division absmax / 7 happens here, once per (group, row)
+      for (int t = threadIdx.x; t < GROUPS_PER_SEG * kQRows; t += 256) {
+        const int gi = t / kQRows, rr = t % kQRows;
+        const int gg = (seg * kQSeg) / GS + gi;
+        if (gg * GS < K && r0 + rr < rows) scale[(int64_t)gg * rows + r0 + rr] = scale_out(s_absmax[par][gi][rr], role);
+      }
     }
+#pragma unroll
+    for (int j = 0; j < kQVecs; ++j) cur[j] = nxt[j];
   }
 }
 
@@ -245,15 +311,14 @@ __global__ void __launch_bounds__(256) quant_rowwise_kernel(const T* __restrict_
     absmax = s_max[0];
 #pragma unroll
     for (int i = 1; i < 8; ++i) absmax = fmaxf(absmax, s_max[i]);
-    divisor = __fdiv_rn(absmax, 7.0f);
     if (t == 0) scale[r] = scale_out(absmax, role);
   }
   uint8_t* dst = packed + r * (int64_t)(K / 2);
-  const Recip rcp = make_recip(divisor);
+  const Recip rcp = GIVEN ? make_recip<false>(divisor) : make_recip<true>(absmax);
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int k = c * 2048 + t * 8;
-    if (k < K) *reinterpret_cast<uint32_t*>(dst + k / 2) = pack8<T, GIVEN>(v[c], divisor, rcp, !GIVEN && absmax == 0.f);
+    if (k < K) *reinterpret_cast<uint32_t*>(dst + k / 2) = pack8<T, GIVEN>(v[c], rcp, !GIVEN && absmax == 0.f);
   }
 }
 
@@ -340,16 +405,23 @@ static int launch_grouped_t(const T* x, int64_t rows, int64_t K, int64_t ldx, in
                             int index_div, const float* given, uint8_t* packed, float* scale, int role,
                             cudaStream_t st) {
   if (rows == 0 || K == 0) return I4TC_OK;
-  dim3 grid((unsigned)((rows + kQRows - 1) / kQRows), (unsigned)((K + kQSeg - 1) / kQSeg));
+  // Enough blocks to fill the GPU several times over; beyond that a block walks several segments
+  // of its rows so that loads of the next segment overlap the arithmetic of the current one.
+  const int64_t row_blocks = (rows + kQRows - 1) / kQRows;
+  const int nseg = (int)((K + kQSeg - 1) / kQSeg);
+  int spb = nseg;
+  if (row_blocks < 2048) spb = (int)((int64_t)nseg * row_blocks / 2048);
+  if (spb < 1) spb = 1;
+  dim3 grid((unsigned)row_blocks, (unsigned)((nseg + spb - 1) / spb));
   I4TC_REQUIRE(grid.y <= 65535, I4TC_EINVAL, "K=%lld too large for the grouped quantiser", (long long)K);
 #define I4TC_LAUNCH_G(LPG)                                                                             \
   quant_grouped_kernel<T, LPG, MODE, GIVEN><<<grid, 256, 0, st>>>(x, rows, (int)K, ldx, row_index,     \
-                                                                   index_div, given, packed, scale, role)
+                                                                   index_div, given, packed, scale, role, spb)
   switch (gs) {
-    case 32: I4TC_LAUNCH_G(4); break;
-    case 64: I4TC_LAUNCH_G(8); break;
-    case 128: I4TC_LAUNCH_G(16); break;
-    case 256: I4TC_LAUNCH_G(32); break;
+    case 32: I4TC_LAUNCH_G(1); break;
+    case 64: I4TC_LAUNCH_G(2); break;
+    case 128: I4TC_LAUNCH_G(4); break;
+    case 256: I4TC_LAUNCH_G(8); break;
     default: return fail(I4TC_EUNSUPPORTED, "group_size=%d not supported (32, 64, 128 or 256)", gs);
   }
 #undef I4TC_LAUNCH_G
@@ -376,7 +448,7 @@ static int launch_grouped(const void* x, int dtype, int64_t rows, int64_t K, int
   if (rows == 0 || K == 0) return I4TC_OK;
   I4TC_REQUIRE(x && packed && (GIVEN ? given != nullptr : scale != nullptr), I4TC_EINVAL, "null pointer");
   if (int rc = check_vec_input(x, dtype, ldx, "quant_grouped")) return rc;
-  I4TC_REQUIRE(aligned_to(packed, 4), I4TC_EALIGN, "packed output must be 4-byte aligned");
+  I4TC_REQUIRE(aligned_to(packed, 16), I4TC_EALIGN, "packed output must be 16-byte aligned");
   DeviceGuard guard(device);
   I4TC_CUDA(guard.err);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
