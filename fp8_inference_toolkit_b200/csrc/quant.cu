@@ -63,11 +63,18 @@ struct Vec8<__nv_bfloat16> {
       w[i] = *reinterpret_cast<const uint32_t*>(&h);
     }
   }
-  __device__ __forceinline__ float absmax() const {
+  // |x| maxima of the two 16-bit halves, still packed (max and abs are exact in bf16)
+  __device__ __forceinline__ __nv_bfloat162 absmax2() const {
     __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[0]));
 #pragma unroll
     for (int i = 1; i < 4; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[i])));
-    return fmaxf(__low2float(m), __high2float(m));
+    return m;
+  }
+  __device__ __forceinline__ float absmax() const { return widen_max(absmax2()); }
+  // bf16 -> fp32 by moving the 16 bits up (integer pipe; the conversion instruction is much slower)
+  static __device__ __forceinline__ float widen_max(__nv_bfloat162 m) {
+    const uint32_t b = *reinterpret_cast<const uint32_t*>(&m);
+    return fmaxf(__uint_as_float(b << 16), __uint_as_float(b & 0xFFFF0000u));
   }
 };
 
@@ -125,18 +132,37 @@ __device__ __forceinline__ float exact_divisor(const Recip& q) {
   return FROM_ABSMAX ? __fdiv_rn(q.base, 7.0f) : q.base;
 }
 
+// Exact code (+8) of an element whose quotient lies within ~1e-5 of a rounding boundary h = k + 0.5.
+// No division: with a = |x|, e1 = h*s - a is exactly representable (a is that close to h*s), and
+// RN(a/s) <= h, = h or >= h is decided by comparing e1 with half an ulp of h times s, also exact.
+// rint's tie-to-even then picks k or k+1.  (a/s can never equal the 25-bit midpoint h +- ulp/2.)
+__device__ __forceinline__ float exact_tie_code8(float x, float y8, float s) {
+  const float a = fabsf(x);
+  const float kf = rintf(fabsf(y8 - 8.0f) - 0.5f);      // k >= 0
+  const float h = kf + 0.5f;
+  const float e1 = fmaf(h, s, -a);                       // exact
+  const float pw = __uint_as_float(__float_as_uint(h) & 0x7F800000u);
+  const float cs = pw * (s * 5.9604644775390625e-08f);   // (ulp(h) / 2) * s, exact
+  const bool odd = (__float2int_rn(kf) & 1) != 0;
+  // k even: RN(a/s) <= h rounds to k, above h to k+1.  k odd: RN(a/s) >= h rounds to k+1, below to k.
+  const float mag = odd ? ((e1 > cs) ? kf : kf + 1.0f) : ((-e1 > cs) ? kf + 1.0f : kf);
+  return copysignf(mag, x) + 8.0f;
+}
+
 // Same result as pack8_div, bit for bit, at a fraction of the instructions (packed f32x2 math).
 //   y8 = x*r + 8 (one FMA)      u = y8 + 1.5*2^23 rounds y8 to the nearest-even integer n+8 in [0,15]
 //   v  = u - 1.5*2^23 = n+8     the eight v's are combined with exact FMAs (16 bits per half)
 // |y8 - 8 - RN(x/s)| < 3e-6 for |x/s| <= 8 (r within 2^-22 of 1/s, one rounding in the FMA, one in
-// the exact quotient), so unless some y8 lies within 1e-5 of a rounding boundary (k + 0.5) the
-// rounded integers are those of the exact division.  Vectors with such an element (a few in 10^5)
-// are redone with the exact division.  CLAMP: the caller supplied the divisor, so x/s may leave [-8, 7].
+// the exact quotient), so unless y8 lies within 1e-5 of a rounding boundary (k + 0.5) the rounded
+// integer is that of the exact division.  Elements inside that window (bf16 data produce exact
+// ties in about one element per thousand) are decided exactly by exact_tie_code8.
+// CLAMP: the caller supplied the divisor, so x/s may leave [-8, 7].
 template <typename T, bool CLAMP>
 __device__ __forceinline__ uint32_t pack8(const Vec8<T>& x, const Recip& q, bool zero) {
   if (zero) return 0u;
   if (!q.fast) return pack8_div(x, exact_divisor<!CLAMP>(q));
   constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+  constexpr float kThr = 0.5f - 1e-5f;
   const float2 r2 = make_float2(q.r, q.r), eight = make_float2(8.f, 8.f), mg = make_float2(kMagic, kMagic);
   const float2 nmg = make_float2(-kMagic, -kMagic);
   float2 v[4];  // v[i] = (n_i + 8, n_{i+4} + 8)
@@ -149,10 +175,22 @@ __device__ __forceinline__ uint32_t pack8(const Vec8<T>& x, const Recip& q, bool
       y8.y = fminf(fmaxf(y8.y, 0.0f), 15.0f);
     }
     v[i] = __fadd2_rn(__fadd2_rn(y8, mg), nmg);
-    const float2 e = __fadd2_rn(y8, make_float2(-v[i].x, -v[i].y));
+    const float2 e = __ffma2_rn(v[i], make_float2(-1.f, -1.f), y8);
     worst = fmaxf(worst, fmaxf(fabsf(e.x), fabsf(e.y)));
   }
-  if (!(worst <= 0.5f - 1e-5f)) return pack8_div(x, exact_divisor<!CLAMP>(q));
+  if (!(worst <= kThr)) {
+    const float s = exact_divisor<!CLAMP>(q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float y0 = fmaf(x.get(i), q.r, 8.0f), y1 = fmaf(x.get(i + 4), q.r, 8.0f);
+      if (CLAMP) {
+        y0 = fminf(fmaxf(y0, 0.0f), 15.0f);
+        y1 = fminf(fmaxf(y1, 0.0f), 15.0f);
+      }
+      if (!(fabsf(y0 - v[i].x) <= kThr)) v[i].x = exact_tie_code8(x.get(i), y0, s);
+      if (!(fabsf(y1 - v[i].y) <= kThr)) v[i].y = exact_tie_code8(x.get(i + 4), y1, s);
+    }
+  }
   // (lo, hi) = v0 + 16 v1 + 256 v2 + 4096 v3 for elements 0..3 and 4..7: exact, below 2^16
   float2 lh = __ffma2_rn(v[3], make_float2(4096.f, 4096.f),
                          __ffma2_rn(v[2], make_float2(256.f, 256.f), __ffma2_rn(v[1], make_float2(16.f, 16.f), v[0])));
@@ -206,7 +244,22 @@ __device__ __forceinline__ void load_segment(Vec8<T> (&v)[kQVecs], const T* src,
   }
 }
 
-// Block = 8 warps = 8 consecutive rows.  In a segment every lane owns 32 consecutive elements
+template <typename T>
+__device__ __forceinline__ float absmax_of(const Vec8<T> (&v)[kQVecs]) {
+  float m = 0.f;
+#pragma unroll
+  for (int j = 0; j < kQVecs; ++j) m = fmaxf(m, v[j].absmax());
+  return m;
+}
+template <>
+__device__ __forceinline__ float absmax_of<__nv_bfloat16>(const Vec8<__nv_bfloat16> (&v)[kQVecs]) {
+  __nv_bfloat162 m = v[0].absmax2();
+#pragma unroll
+  for (int j = 1; j < kQVecs; ++j) m = __hmax2(m, v[j].absmax2());
+  return Vec8<__nv_bfloat16>::widen_max(m);
+}
+
+// Block = 8 warps = 8 consecutive rows (the warps are independent).  In a segment every lane owns 32 consecutive elements
 // (64 bytes of bf16), so a group of GS elements is LPG = GS/32 adjacent lanes: its absmax costs
 // log2(LPG) shuffles, its reciprocal is formed once per lane, and each lane leaves 16 packed bytes
 // with one 128-bit store.  The block walks `segs_per_block` segments of its rows and loads segment
@@ -217,9 +270,6 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
     int index_div, const float* __restrict__ given_scale, uint8_t* __restrict__ packed,
     float* __restrict__ scale, int role, int segs_per_block) {
   constexpr int GS = LPG * kQLane;
-  constexpr int GROUPS_PER_SEG = 32 / LPG;
-  __shared__ float s_absmax[2][GROUPS_PER_SEG][kQRows];
-
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t r0 = (int64_t)blockIdx.x * kQRows;
   const int64_t r = r0 + warp;
@@ -239,7 +289,6 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
   for (int seg = seg_begin; seg < seg_end; ++seg) {
     const int k = seg * kQSeg + lane * kQLane;
     if (seg + 1 < seg_end) load_segment<T, MODE>(nxt, src, k + kQSeg, K, row_ok);
-    const int par = seg & 1;
     const bool ok = row_ok && k < K;
     const int g = k / GS;
     Recip q;
@@ -247,12 +296,13 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
     if (GIVEN) {
       q = make_recip<false>(ok ? __ldg(given_scale + (int64_t)g * rows + r) : 1.f);
     } else {
-#pragma unroll
-      for (int j = 0; j < kQVecs; ++j) absmax = fmaxf(absmax, cur[j].absmax());
+      absmax = absmax_of(cur);
 #pragma unroll
       for (int o = 1; o < LPG; o <<= 1) absmax = fmaxf(absmax, __shfl_xor_sync(0xffffffffu, absmax, o));
       q = make_recip<true>(absmax);
-      if ((lane % LPG) == 0) s_absmax[par][lane / LPG][warp] = absmax;
+      // one lane per group writes the scale (the IEEE division absmax / 7 happens here, off the
+      // per-element path); neighbouring rows fill the same 32-byte sector from other warps
+      if (ok && (lane % LPG) == 0) scale[(int64_t)g * rows + r] = scale_out(absmax, role);
     }
     if (ok) {
       const bool zero = !GIVEN && absmax == 0.f;
@@ -263,16 +313,6 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
       w.w = pack8<T, GIVEN>(cur[3], q, zero);
       uint8_t* dst = packed + ((int64_t)g * rows + r) * (GS / 2) + (lane % LPG) * 16;
       *reinterpret_cast<uint4*>(dst) = w;
-    }
-    if (!GIVEN) {
-      __syncthreads();
-      // 8 consecutive rows of one group are 32 contiguous bytes of the [G, rows] scale array; the
-      // IEEE division absmax / 7 happens here, once per (group, row)
-      for (int t = threadIdx.x; t < GROUPS_PER_SEG * kQRows; t += 256) {
-        const int gi = t / kQRows, rr = t % kQRows;
-        const int gg = (seg * kQSeg) / GS + gi;
-        if (gg * GS < K && r0 + rr < rows) scale[(int64_t)gg * rows + r0 + rr] = scale_out(s_absmax[par][gi][rr], role);
-      }
     }
 #pragma unroll
     for (int j = 0; j < kQVecs; ++j) cur[j] = nxt[j];
