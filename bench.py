@@ -49,7 +49,7 @@ def load_peaks():
 # clocks
 # --------------------------------------------------------------------------- #
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -58,9 +58,11 @@ class ClockSampler:
         self.proc = None
 
     def start(self):
+        self.t_begin = None
+        self.t_end = None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -75,6 +77,8 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
+        import datetime
+
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
@@ -82,6 +86,9 @@ class ClockSampler:
             if len(f) < 9:
                 continue
             try:
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                if self.t_begin is not None and not (self.t_begin - 0.05 <= ts <= self.t_end + 0.05):
+                    continue  # keep only samples taken while the load was running
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
             except ValueError:
@@ -91,7 +98,7 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        busy = [c for c in sm if c > 0.5 * max(sm)] or sm
+        busy = sm
         return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
                 "samples": len(sm)}
 
@@ -237,14 +244,26 @@ def run_ours(args) -> None:
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+        time.sleep(0.3)  # let nvidia-smi come up; the GPU is idle meanwhile
+    barrier()
     events = []
+    wall0 = time.time()
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(args.steps):
         step(events)
     t1.record()
     barrier()
+    # the timed region can be a few tens of ms, shorter than the sampler's period: keep the same
+    # load running (untimed) until at least one second of samples exists
+    while time.time() - wall0 < 1.0:
+        step()
+        torch.cuda.synchronize()
+    wall1 = time.time()
+    sampler.t_begin, sampler.t_end = wall0, wall1
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = "timed steps plus untimed repeats of the same step, %.2f s" % (wall1 - wall0)
     ops.check_status()
     elapsed_ms = t0.elapsed_time(t1)
     if world > 1:
@@ -269,11 +288,28 @@ def run_ours(args) -> None:
     h2d = sum(x.numel() * 2 for x in x_host)
     d2h = sum(o.numel() * 2 for o in o_host)
 
+    copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    main = torch.cuda.current_stream(dev)
+
     def e2e_step():
+        # host -> device on one stream, the linear on the main stream, device -> host on a third:
+        # the three overlap across the four linears of a step
+        prev = None
         for i, lin in enumerate(layers):
-            xd = x_host[i].to(dev, non_blocking=True)
+            with torch.cuda.stream(copy_in):
+                xd = x_host[i].to(dev, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(copy_in)
+            main.wait_event(ready)
             y = lin(xd)
-            o_host[i].copy_(y, non_blocking=True)
+            xd.record_stream(main)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(done)
+                o_host[i].copy_(y, non_blocking=True)
+            y.record_stream(copy_out)
+            prev = y
         torch.cuda.synchronize()
 
     for _ in range(2):
@@ -311,6 +347,8 @@ def run_ours(args) -> None:
             },
         }
         line["moe"] = moe_result
+        if world == 1 and not args.no_sweep:
+            line["sweep"] = bench_sweep(dev, peaks)
         if world == 1:
             t, cops = cpu_reference_step(16)
             t, cops = cpu_reference_step(16)
@@ -321,6 +359,61 @@ def run_ours(args) -> None:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def graph_time(fn_list, iters: int = 3) -> float:
+    """Mean device time (s) of one call, timed as a CUDA-graph replay of the whole list so that host
+    launch overhead does not count.  The list should cycle over enough distinct operands to exceed L2."""
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for fn in fn_list[:2]:
+            fn()
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for fn in fn_list:
+                fn()
+        g.replay()
+        side.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        for _ in range(iters):
+            g.replay()
+        e1.record(side)
+        side.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / (iters * len(fn_list))
+
+
+def bench_sweep(dev, peaks) -> list:
+    """BASELINE configs[1] sweep, kernel-only: M in {1,16,128,1024,8192} x the four (K,N) shapes, group-128
+    fused GEMM (quantise excluded).  Operands rotate over enough copies to exceed L2 for the HBM-bound sizes."""
+    import int4_native_tc as tc
+    from fp8_inference_toolkit_b200 import synthetic
+
+    out_rows = []
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    for M in (1, 16, 128, 1024, 8192):
+        for name, K, N in SHAPES:
+            G = K // GROUP
+            w_bytes = N * K // 2
+            copies = 1 if M >= 1024 else max(2, min(24, (300 << 20) // w_bytes))
+            ws_ = [synthetic.random_packed((G, N, 64), 100 + i, dev) for i in range(copies)]
+            wsc = torch.rand(G, N, device=dev) * 0.01
+            xp = synthetic.random_packed((G, M, 64), 7, dev)
+            xsc = torch.rand(G, M, device=dev) * 0.1
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            reps = 2 if M >= 1024 else 1
+            fns = [(lambda w=w: tc.cutlass_int4_fused_grouped_gemm(xp, w, xsc, wsc, out, M, N, GROUP, G))
+                   for _ in range(reps) for w in ws_]
+            t = graph_time(fns)
+            ops_ = 2.0 * M * N * K
+            byts = gemm_bytes(M, N, K)
+            out_rows.append({"M": M, "shape": name, "K": K, "N": N, "us": t * 1e6, "tops": ops_ / t / 1e12,
+                             "gbs": byts / t / 1e9, "frac_int8_peak": ops_ / t / 1e12 / int8_peak,
+                             "frac_hbm": byts / t / 1e9 / peaks["hbm_gbs"]})
+            del ws_, fns
+    return out_rows
 
 
 def bench_moe(args, world, rank, dev, peaks) -> dict:
@@ -436,6 +529,7 @@ def main() -> None:
     ap.add_argument("--workload", default="linear", choices=["linear", "quant"],
                     help="linear: the headline W4A4 linears (default); quant: quantise+pack only")
     ap.add_argument("--k", type=int, default=12288, help="row length for --workload quant")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the kernel-only M x shape sweep")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)

@@ -102,7 +102,10 @@ struct Sched {
 // Bounded mbarrier wait, uniform across the warp.  Returns false (and raises the abort flag)
 // when the limit expires or another role has already aborted.
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  bool ok = mbar_try_wait(bar, parity);
+  // a non-blocking probe first: when the phase has already completed it is much cheaper than the
+  // potentially-suspending try_wait
+  bool ok = mbar_test_wait(bar, parity);
+  if (!ok) ok = mbar_try_wait(bar, parity);
   if (!ok) {
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;

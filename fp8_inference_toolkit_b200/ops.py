@@ -16,12 +16,18 @@ from ._cabi import check, lib
 _DTYPES = {torch.bfloat16: _cabi.BF16, torch.float16: _cabi.FP16, torch.float32: _cabi.FP32}
 
 
-def _stream(t: torch.Tensor) -> int:
-    return torch.cuda.current_stream(t.device).cuda_stream
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
 def _dev(t: torch.Tensor) -> int:
     return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def _stream(t: torch.Tensor) -> int:
+    """Handle of torch's current stream on the tensor's device (the stream the reference launches on)."""
+    if _raw_stream is not None:
+        return _raw_stream(_dev(t))
+    return torch.cuda.current_stream(t.device).cuda_stream
 
 
 def _require(cond: bool, msg: str) -> None:
