@@ -66,10 +66,14 @@ struct DeviceInfo {
   int cc_minor = 0;
   int max_smem_optin = 0;
   unsigned int* status = nullptr;  // device status word written by bounded waits
+  float* split_ws = nullptr;       // split-K partial sums (grown on demand, owned by the library)
+  size_t split_ws_bytes = 0;
 };
 
 // Cached per-device properties; allocates the status word on first use.
 int device_info(int device, const DeviceInfo** out);
+// Returns the library-owned split-K workspace of `device`, at least `bytes` large (reallocated if needed).
+int split_workspace(int device, size_t bytes, float** out);
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 

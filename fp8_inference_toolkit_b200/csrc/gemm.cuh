@@ -39,7 +39,17 @@ struct GemmParams {
   int num_experts;
   long long sq_estride;  // floats between experts in sq
   unsigned int* status;  // device status word, bit 0 = a bounded wait expired
+  // Split-K (dense per-group mode, small M): the K groups are cut into `splits` ranges of
+  // `groups_per_split`; range s writes fp32 partial sums to split_ws + s * ws_stride ([M, N] each),
+  // and a second kernel adds the ranges in ascending order.
+  int splits;
+  int groups_per_split;
+  float* split_ws;
+  long long ws_stride;
 };
+
+// out[i] = bf16(sum_s ws[s * stride + i]), s ascending.
+int launch_split_reduce(const float* ws, long long stride, int splits, long long n, void* out, cudaStream_t st);
 
 int launch_w4a4_gemm(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int bn, int grid,
                      cudaStream_t st);

@@ -7,6 +7,7 @@ namespace i4tc {
 
 static int g_force_bn = 0;    // 0 = choose automatically
 static int g_force_swap = -1; // -1 = choose automatically
+static int g_force_splits = 0; // 0 = choose automatically, 1 = never split, n = n K ranges
 
 struct Shape {
   int bn;
@@ -102,13 +103,45 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   p.num_q_tiles = (int)((qrow + sh.bn - 1) / sh.bn);
   const long long tiles = (long long)p.num_p_tiles * p.num_q_tiles;
   I4TC_REQUIRE(tiles < (1ll << 31), I4TC_EINVAL, "too many tiles");
+  // Split-K for the weight-streaming case (small M, per-group epilogue): a tile's K loop is a serial
+  // chain of per-group handshakes, so when there are fewer tiles than SMs -- or an awkward number
+  // of waves -- the groups are cut into ranges handled by different CTAs and the fp32 partial sums
+  // are added afterwards in a fixed order (deterministic).
+  p.splits = 1;
+  p.groups_per_split = d.G;
+  if (d.epi_mode == EPI_GROUP && sh.swap && g_force_splits != 1) {
+    // cost in microseconds: waves x groups per range x ~0.65 us per group handshake, plus writing and
+    // reading the fp32 partial sums at ~6 TB/s and one more launch
+    int best_s = 1;
+    double best_cost = (double)((tiles + info->sm_count - 1) / info->sm_count) * d.G * 0.65;
+    for (int s = 2; s <= 8 && s <= d.G; ++s) {
+      const long long gps = (d.G + s - 1) / s;
+      const double traffic_us = 2.0 * s * (double)d.M * (double)d.N * 4.0 / 6.0e6;
+      const double cost = (double)((tiles * s + info->sm_count - 1) / info->sm_count) * gps * 0.65 + traffic_us + 3.0;
+      if (cost < best_cost) { best_cost = cost; best_s = s; }
+    }
+    if (g_force_splits > 1) best_s = g_force_splits <= d.G ? g_force_splits : d.G;
+    if (best_s > 1) {
+      p.splits = best_s;
+      p.groups_per_split = (d.G + best_s - 1) / best_s;
+      p.splits = (d.G + p.groups_per_split - 1) / p.groups_per_split;  // no empty range
+      p.ws_stride = d.M * d.N;
+      float* ws = nullptr;
+      if (int rc = split_workspace(device, (size_t)p.splits * d.M * d.N * sizeof(float), &ws)) return rc;
+      p.split_ws = ws;
+    }
+  }
 
   CUtensorMap tmP, tmQ;
   const long long extent = d.rowmajor ? d.K / 2 : (long long)d.G;
   if (int rc = get_tensor_map(device, pbase, d.rowmajor, prow, extent, 128, &tmP)) return rc;
   if (int rc = get_tensor_map(device, qbase, d.rowmajor, qrow, extent, sh.bn, &tmQ)) return rc;
-  const int grid = (int)(tiles < info->sm_count ? tiles : info->sm_count);
-  return launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, static_cast<cudaStream_t>(stream));
+  const long long items = tiles * p.splits;
+  const int grid = (int)(items < info->sm_count ? items : info->sm_count);
+  if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, static_cast<cudaStream_t>(stream))) return rc;
+  if (p.splits > 1)
+    return launch_split_reduce(p.split_ws, p.ws_stride, p.splits, d.M * d.N, d.out, static_cast<cudaStream_t>(stream));
+  return I4TC_OK;
 }
 
 static int check_dense_common(const void* a, const void* b, const void* out, long long M, long long N) {
@@ -128,6 +161,12 @@ extern "C" int i4tc_set_tuning(int tile_n, int swap) {
   I4TC_REQUIRE(swap >= -1 && swap <= 1, I4TC_EINVAL, "swap must be -1 (automatic), 0 or 1");
   g_force_bn = tile_n;
   g_force_swap = swap;
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_set_split_k(int splits) {
+  I4TC_REQUIRE(splits >= 0 && splits <= 8, I4TC_EINVAL, "splits must be 0 (automatic) or 1..8");
+  g_force_splits = splits;
   return I4TC_OK;
 }
 
@@ -212,6 +251,8 @@ extern "C" int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, con
   p.num_q_tiles = (int)((N + bn - 1) / bn);
   p.expert_offsets = expert_offsets;
   p.num_experts = (int)num_experts;
+  p.splits = 1;
+  p.groups_per_split = (int)num_groups;
   p.status = info->status;
   CUtensorMap tmP, tmQ;
   if (int rc = get_tensor_map(device, a, false, num_pairs, num_groups, 128, &tmP)) return rc;

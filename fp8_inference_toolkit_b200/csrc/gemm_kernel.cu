@@ -63,6 +63,8 @@ struct TileInfo {
   int p_lim, q_lim;  // exclusive row limits for output
   int zq;            // slab offset of the Q operand (MoE: expert * G)
   long long sq_off;  // float offset into sq (MoE: expert * sq_estride)
+  int g0, g1;        // K groups [g0, g1) of this work item (all of them unless split-K)
+  int split;
 };
 
 // Static persistent schedule: CTA b takes tiles b, b + grid, ...  P tiles vary fastest so that
@@ -75,9 +77,13 @@ struct Sched {
   template <int BN>
   __device__ bool next(const GemmParams& p, TileInfo& ti) {
     if (p.expert_offsets == nullptr) {
-      if (tile >= p.num_p_tiles * p.num_q_tiles) return false;
-      const int pt = tile % p.num_p_tiles, qt = tile / p.num_p_tiles;
+      const int per_split = p.num_p_tiles * p.num_q_tiles;
+      if (tile >= per_split * p.splits) return false;
+      const int sp = tile / per_split, local = tile - sp * per_split;
+      const int pt = local % p.num_p_tiles, qt = local / p.num_p_tiles;
       ti.p0 = pt * kBM; ti.q0 = qt * BN; ti.p_lim = p.P_rows; ti.q_lim = p.Q_rows; ti.zq = 0; ti.sq_off = 0;
+      ti.split = sp; ti.g0 = sp * p.groups_per_split;
+      ti.g1 = min(p.G, ti.g0 + p.groups_per_split);
     } else {
       for (;;) {
         if (e >= p.num_experts) return false;
@@ -89,6 +95,7 @@ struct Sched {
           const int pt = local % npt, qt = local / npt;
           ti.p0 = r0 + pt * kBM; ti.p_lim = r1; ti.q0 = qt * BN; ti.q_lim = p.Q_rows;
           ti.zq = e * p.G; ti.sq_off = (long long)e * p.sq_estride;
+          ti.split = 0; ti.g0 = 0; ti.g1 = p.G;
           break;
         }
         tile_base += nt; ++e;
@@ -274,15 +281,15 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
         sq_next[c] = (q < ti.q_lim) ? __ldg(p.sq + ti.sq_off + (long long)g * p.sq_gstride + q) : 0.f;
       }
     };
-    fetch(0);
+    fetch(ti.g0);
     bool ok = true;
-    for (int g = 0; g < p.G; ++g) {
+    for (int g = ti.g0; g < ti.g1; ++g) {
       float* sq_buf = sq_s + (g & 1) * C::COLS_PER_WARP;
       const float sp = sp_next * (pq_order ? kInv256 : 1.0f);
 #pragma unroll
       for (int c = 0; c < NCH; ++c) sq_buf[c * 32 + lane] = sq_next[c] * (pq_order ? 1.0f : kInv256);
       __syncwarp();
-      if (g + 1 < p.G) fetch(g + 1);
+      if (g + 1 < ti.g1) fetch(g + 1);
       const uint32_t buf = flush & 1u;
       ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
       if (!ok) break;
@@ -327,7 +334,22 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
       float v[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = f[c * 32 + i];
-      store_chunk_f<OutT>(p, v, prow, ti.q0 + col_base + c * 32, ti);
+      if (p.split_ws != nullptr) {
+        // split-K: fp32 partial sums of this K range, element (m, n) at ws[split][m * ldc + n]
+        float* ws = p.split_ws + (long long)ti.split * p.ws_stride;
+        const int qcol0 = ti.q0 + col_base + c * 32;
+        if (prow < ti.p_lim) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (qcol0 + i < ti.q_lim) {
+              if (!p.swap) ws[(long long)prow * p.ldc + qcol0 + i] = v[i];
+              else ws[(long long)(qcol0 + i) * p.ldc + prow] = v[i];
+            }
+          }
+        }
+      } else {
+        store_chunk_f<OutT>(p, v, prow, ti.q0 + col_base + c * 32, ti);
+      }
     }
   }
 }
@@ -346,7 +368,7 @@ __device__ __forceinline__ void epilogue_simple(const GemmParams& p, uint8_t* sm
   const int col_base = half * C::COLS_PER_WARP;
   float* sq_s = reinterpret_cast<float*>(smem + C::OFF_SQ) + ew * 2 * C::COLS_PER_WARP;
   const bool per_group = p.epi_mode == EPI_GROUP_INT32;
-  const int nflush = per_group ? p.G : 1;
+
   constexpr float kInv256 = 1.0f / 256.0f;
   // reference order (acc * scale_b[n]) * scale_a[m]: normal -> column scale first; swapped -> row scale first
   const bool q_first = !p.swap;
@@ -369,6 +391,7 @@ __device__ __forceinline__ void epilogue_simple(const GemmParams& p, uint8_t* sm
       }
       __syncwarp();
     }
+    const int nflush = per_group ? (ti.g1 - ti.g0) : 1;
     for (int fl = 0; fl < nflush; ++fl) {
       const uint32_t buf = flush & 1u;
       ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
@@ -396,7 +419,7 @@ __device__ __forceinline__ void epilogue_simple(const GemmParams& p, uint8_t* sm
           }
           store_chunk_f<OutT>(p, v, prow, qcol0, ti);
         } else {
-          int32_t* out = static_cast<int32_t*>(p.out) + (per_group ? (long long)fl * p.out_gstride : 0ll);
+          int32_t* out = static_cast<int32_t*>(p.out) + (per_group ? (long long)(ti.g0 + fl) * p.out_gstride : 0ll);
           store_chunk_i(p, out, r, prow, qcol0, ti);
         }
       }
@@ -462,7 +485,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     uint32_t it = 0;
     bool ok = true;
     while (ok && sched.next<BN>(p, ti)) {
-      for (int g = 0; g < p.G; ++g, ++it) {
+      for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         const uint32_t s = it % C::NP, ph = (it / C::NP) & 1u;
         ok = wait_bar(bar_pk_empty + s * 8, ph ^ 1u, abort_flag);
         if (!ok) break;
@@ -497,9 +520,9 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     uint32_t it = 0, flush = 0;
     bool ok = true;
     while (ok && sched.next<BN>(p, ti)) {
-      for (int g = 0; g < p.G; ++g, ++it) {
-        const bool first = per_group_flush || g == 0;
-        const bool last = per_group_flush || g == p.G - 1;
+      for (int g = ti.g0; g < ti.g1; ++g, ++it) {
+        const bool first = per_group_flush || g == ti.g0;
+        const bool last = per_group_flush || g == ti.g1 - 1;
         const uint32_t buf = flush & 1u;
         if (first) {
           ok = wait_bar(bar_tm_empty + buf * 8, ((flush >> 1) & 1u) ^ 1u, abort_flag);
@@ -536,7 +559,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     uint32_t it = 0;
     bool ok = true;
     while (ok && sched.next<BN>(p, ti)) {
-      for (int g = 0; g < p.G; ++g, ++it) {
+      for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         const uint32_t sp_ = it % C::NP, php = (it / C::NP) & 1u;
         const uint32_t si = it % kNI, phi = (it / kNI) & 1u;
         ok = wait_bar(bar_pk_full + sp_ * 8, php, abort_flag);
@@ -586,6 +609,35 @@ static int launch_bn(const GemmParams& p, const CUtensorMap& tmP, const CUtensor
     configured[dev] = true;
   }
   w4a4_gemm_kernel<BN><<<grid, kThreads, C::SMEM_BYTES, st>>>(p, tmP, tmQ);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+__global__ void __launch_bounds__(256) split_reduce_kernel(const float* __restrict__ ws, long long stride, int splits,
+                                                          long long n, __nv_bfloat16* __restrict__ out) {
+  const long long i = ((long long)blockIdx.x * 256 + threadIdx.x) * 4;
+  if (i + 3 < n) {
+    float4 acc = *reinterpret_cast<const float4*>(ws + i);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(ws + (long long)s * stride + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    union { __nv_bfloat16 h[4]; uint2 u; } pk;
+    pk.h[0] = __float2bfloat16_rn(acc.x); pk.h[1] = __float2bfloat16_rn(acc.y);
+    pk.h[2] = __float2bfloat16_rn(acc.z); pk.h[3] = __float2bfloat16_rn(acc.w);
+    *reinterpret_cast<uint2*>(out + i) = pk.u;
+  } else {
+    for (long long j = i; j < n; ++j) {
+      float acc = ws[j];
+      for (int s = 1; s < splits; ++s) acc += ws[(long long)s * stride + j];
+      out[j] = __float2bfloat16_rn(acc);
+    }
+  }
+}
+
+int launch_split_reduce(const float* ws, long long stride, int splits, long long n, void* out, cudaStream_t st) {
+  const long long blocks = (n + 1023) / 1024;
+  split_reduce_kernel<<<(unsigned)blocks, 256, 0, st>>>(ws, stride, splits, n, static_cast<__nv_bfloat16*>(out));
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
 }

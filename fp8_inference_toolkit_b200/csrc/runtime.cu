@@ -29,6 +29,28 @@ int device_info(int device, const DeviceInfo** out) {
   return I4TC_OK;
 }
 
+int split_workspace(int device, size_t bytes, float** out) {
+  const DeviceInfo* cinfo;
+  if (int rc = device_info(device, &cinfo)) return rc;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceInfo& d = g_info[device];
+  if (d.split_ws_bytes < bytes) {
+    DeviceGuard guard(device);
+    I4TC_CUDA(guard.err);
+    if (d.split_ws) {
+      I4TC_CUDA(cudaDeviceSynchronize());  // earlier launches may still read the old buffer
+      I4TC_CUDA(cudaFree(d.split_ws));
+      d.split_ws = nullptr;
+      d.split_ws_bytes = 0;
+    }
+    size_t want = bytes < (16u << 20) ? (16u << 20) : bytes;
+    I4TC_CUDA(cudaMalloc(&d.split_ws, want));
+    d.split_ws_bytes = want;
+  }
+  *out = d.split_ws;
+  return I4TC_OK;
+}
+
 // ---- tensor maps -------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

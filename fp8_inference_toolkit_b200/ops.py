@@ -231,6 +231,11 @@ def set_tuning(tile_n: int = 0, swap: int = -1) -> None:
     check(lib.i4tc_set_tuning(tile_n, swap), "set_tuning")
 
 
+def set_split_k(splits: int = 0) -> None:
+    """Force the number of K ranges of the small-M per-group GEMM (tests); 0 restores automatic."""
+    check(lib.i4tc_set_split_k(splits), "set_split_k")
+
+
 def check_status(device=None) -> None:
     """Raise if any kernel gave up on a bounded wait since the last call (synchronises the stream)."""
     dev = torch.cuda.current_device() if device is None else torch.device(device).index

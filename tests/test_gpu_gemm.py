@@ -153,6 +153,27 @@ def test_grouped_partials_and_output(tc, ops, M, N, G):
         assert (out.cpu() == ref).float().mean() > 0.98
 
 
+@pytest.mark.parametrize("M,N,G", [(1, 256, 8), (16, 4096, 32), (100, 640, 7), (128, 384, 96)])
+def test_split_k_small_m(tc, ops, M, N, G):
+    """Small-M per-group path with the K groups cut into 1..8 ranges: every split count agrees with the
+    oracle, and a forced single range equals the automatic choice within the same tolerance."""
+    rng = np.random.RandomState(M + N + G)
+    a, b = rand_codes(rng, (G, M, 128)), rand_codes(rng, (G, N, 128))
+    sa = (rng.rand(G, M).astype(np.float32) + 0.01) * 0.1
+    sb = (rng.rand(G, N).astype(np.float32) + 0.01) * 0.01
+    ref = O.linear_grouped(a, b, sa, sb)
+    ap, bp = dev_packed(a), dev_packed(b)
+    try:
+        for splits in (0, 1, 2, 3, 8):
+            ops.set_split_k(splits)
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            tc.cutlass_int4_fused_grouped_gemm(ap, bp, dev_f32(sa), dev_f32(sb), out, M, N, 128, G)
+            ops.check_status()
+            assert_close_bf16(out, ref, f"split-K {splits} {M}x{N}x{G}")
+    finally:
+        ops.set_split_k(0)
+
+
 def test_grouped_aliases_and_checks(tc, ops):
     rng = np.random.RandomState(9)
     M, N, G = 10, 64, 2
