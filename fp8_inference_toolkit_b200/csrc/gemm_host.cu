@@ -231,9 +231,9 @@ extern "C" int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, con
   DeviceGuard guard(device);
   I4TC_CUDA(guard.err);
 
-  // Average rows per expert decide the tile width: narrow tiles keep more SMs busy when the
-  // per-expert problems are small.
-  int bn = g_force_bn ? g_force_bn : 128;
+  // 256-column tiles amortise the conversion of the activation tile better; narrow outputs fall
+  // back to 128 columns.
+  int bn = g_force_bn ? g_force_bn : ((N % 256 == 0) ? 256 : 128);
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.P_rows = (int)num_pairs;
