@@ -524,10 +524,55 @@ def run_quant(args) -> None:
     }), flush=True)
 
 
+def run_prefill(args) -> None:
+    """BASELINE configs[4]: Qwen3-8B-architecture prefill, all linears W4A4 group-128, random-init weights,
+    batch 32 x 512 uniform random token ids, attention in bf16 (torch SDPA); tokens/s end to end."""
+    from fp8_inference_toolkit_b200 import ops
+    from fp8_inference_toolkit_b200.qwen3 import Qwen3Config, Qwen3Prefill
+
+    torch.cuda.set_device(0)
+    cfg = Qwen3Config(layers=args.layers)
+    model = Qwen3Prefill(cfg, "cuda")
+    B, S = args.batch, args.seq
+    g = torch.Generator().manual_seed(0)
+    ids_host = torch.randint(0, cfg.vocab, (B, S), generator=g).pin_memory()
+
+    def step():
+        ids = ids_host.to("cuda", non_blocking=True)
+        y = model(ids)
+        return y[:, -1, :8].float().cpu()  # a device->host read of the result
+
+    for _ in range(max(args.warmup, 1)):
+        step()
+    ops.check_status()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_status()
+    ms = e0.elapsed_time(e1) / args.steps
+    lin_ops = 2 * B * S * cfg.layers * sum(N * K for _, K, N in SHAPES)
+    print(json.dumps({
+        "metric": "qwen3_8b_w4a4_prefill_tokens_per_s", "value": B * S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
+        "dtype": "s4*s4->s32 linears, bf16 attention", "data": "synthetic",
+        "config": {"workload": "BASELINE configs[4]: Qwen3-8B-shaped prefill, %d layers, batch %d x %d, W4A4 group-128"
+                               % (cfg.layers, B, S)},
+        "linear_tops": lin_ops / (ms * 1e-3) / 1e12,
+    }), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="linear", choices=["linear", "quant"],
-                    help="linear: the headline W4A4 linears (default); quant: quantise+pack only")
+    ap.add_argument("--workload", default="linear", choices=["linear", "quant", "prefill"],
+                    help="linear: the headline W4A4 linears (default); quant: quantise+pack only; "
+                         "prefill: Qwen3-8B-shaped prefill")
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--seq", type=int, default=512)
     ap.add_argument("--k", type=int, default=12288, help="row length for --workload quant")
     ap.add_argument("--no-sweep", action="store_true", help="skip the kernel-only M x shape sweep")
     ap.add_argument("--gpus", type=int, default=1)
@@ -538,6 +583,8 @@ def main() -> None:
     args = ap.parse_args()
     if args.workload == "quant":
         run_quant(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
