@@ -328,6 +328,8 @@ def run_ours(args) -> None:
     e2e_val = ops_per_step / e2e_s / 1e12
 
     moe_result = bench_moe(args, world, rank, dev, peaks)
+    # the same layer with 4096 tokens per rank (weak scaling), where the exchange is no longer latency-bound
+    moe_weak = bench_moe(args, world, rank, dev, peaks, weak=True) if world > 1 else None
 
     if rank == 0:
         line = {
@@ -347,6 +349,8 @@ def run_ours(args) -> None:
             },
         }
         line["moe"] = moe_result
+        if moe_weak is not None:
+            line["moe_weak"] = moe_weak
         if world == 1 and not args.no_sweep:
             line["sweep"] = bench_sweep(dev, peaks)
         if world == 1:
@@ -416,7 +420,7 @@ def bench_sweep(dev, peaks) -> list:
     return out_rows
 
 
-def bench_moe(args, world, rank, dev, peaks) -> dict:
+def bench_moe(args, world, rank, dev, peaks, weak: bool = False) -> dict:
     """MoE grouped W4A4 layer (BASELINE configs[3]): 128 experts, top-8, 4096 tokens, hidden 2048,
     intermediate 768, group-128; experts and tokens split evenly across ranks, all-to-all dispatch and
     combine.  Timed from (token rows, expert ids, routing weights) to the combined bf16 output."""
@@ -424,7 +428,7 @@ def bench_moe(args, world, rank, dev, peaks) -> dict:
 
     from fp8_inference_toolkit_b200 import moe, moe_ep, ops, synthetic
 
-    T, H, I, E, k = 4096, 2048, 768, 128, 8
+    T, H, I, E, k = (4096 * world if weak else 4096), 2048, 768, 128, 8
     t_loc, e_loc = T // world, E // world
     x, logits = synthetic.moe_inputs(T, H, E, k, seed=0)
     ids, w = moe.moe_route(logits.to(dev), k)
@@ -461,12 +465,13 @@ def bench_moe(args, world, rank, dev, peaks) -> dict:
     ops_layer = T * k * (2 * H * 2 * I + 2 * I * H)
     int8_peak = 2.0 * peaks["bf16_tflops"] * world
     return {
-        "metric": "moe_w4a4_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "metric": "moe_w4a4_tokens_per_s", "scaling": "weak" if weak else "strong",
+        "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "ms_per_layer": ms, "tops": ops_layer / (ms * 1e-3) / 1e12,
         "frac_of_int8_peak": ops_layer / (ms * 1e-3) / 1e12 / int8_peak,
-        "config": {"workload": "BASELINE configs[3]: 128 experts, top-8 of softmax(N(0,1) logits), 4096 tokens, "
+        "config": {"workload": "BASELINE configs[3]: 128 experts, top-8 of softmax(N(0,1) logits), %d tokens, "
                                "hidden 2048, intermediate 768, group-128; %d experts and %d tokens per rank"
-                               % (e_loc, t_loc),
+                               % (T, e_loc, t_loc),
                    "timed": "sort + dispatch + gather-quantise + gate/up GEMM + SwiGLU-quantise + down GEMM + combine"},
     }
 
