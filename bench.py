@@ -342,7 +342,11 @@ def run_ours(args) -> None:
             "gpu_launches": args.steps * 2 * len(SHAPES),
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOPS",
-                "frac": achieved / int8_peak, "traffic": None,
+                "frac": achieved / int8_peak,
+                # ncu (M=1024 capture, profiles/): DRAM reads of a launch = 1.00 x its operand bytes and the
+                # bf16 output is written back after the kernel ends, so a launch moves its algorithmic bytes
+                "traffic": sum(gemm_bytes(M, N // world, K) for _, K, N in SHAPES) / len(SHAPES),
+                "traffic_unit": "bytes per launch (mean of the 4 shapes), algorithmic; ncu-confirmed at M=1024",
                 "kernel": "w4a4_gemm_kernel (per-group-128 epilogue), 4 launches per step",
                 "peak_source": f"2 x bf16 burst of MEASURED_PEAKS.json ({peaks['source']}); int8 dense = 2 x bf16 on B200",
                 "per_shape_us": {SHAPES[i][0]: statistics.mean(v) * 1e6 for i, v in per_shape.items()},
