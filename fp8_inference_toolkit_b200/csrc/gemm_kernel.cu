@@ -35,6 +35,8 @@ constexpr int kThreads = 512;
 constexpr int kConvWarp0 = 4, kConvWarps = 4;
 constexpr int kEpiWarp0 = 8, kEpiWarps = 8;
 constexpr int kNI = 2;               // int8 stages
+constexpr int kNS = 4;               // scale stages (per-group epilogue)
+constexpr int kScaleWarp0 = 2, kScaleWarps = 2;
 // register budgets per role (whole warpgroups): 128*56 + 128*72 + 256*192 = 65536
 constexpr int kRegsWg0 = 56, kRegsConv = 72, kRegsEpi = 192;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
@@ -51,9 +53,14 @@ struct Cfg {
   // shared memory layout (offsets from a 1024-byte aligned base)
   static constexpr int OFF_I8 = 0;
   static constexpr int OFF_PK = OFF_I8 + kNI * (I8_P + I8_Q);
-  static constexpr int OFF_SQ = OFF_PK + NP * (PK_P + PK_Q);          // per-warp column scales, 2 buffers
-  static constexpr int OFF_BAR = OFF_SQ + kEpiWarps * 2 * COLS_PER_WARP * 4;
-  static constexpr int NUM_BARS = 2 * NP + 2 * kNI + 4;
+  // scale stages of the per-group epilogue: kBM row scales then BN column scales of one K group;
+  // the one-flush epilogues use the start of the same region for their per-warp column scales
+  static constexpr int OFF_SQ = OFF_PK + NP * (PK_P + PK_Q);
+  static constexpr int SCALE_STAGE = (kBM + BN) * 4;                  // bytes
+  static constexpr int SQ_BYTES = (kNS * SCALE_STAGE > kEpiWarps * 2 * COLS_PER_WARP * 4) ? kNS * SCALE_STAGE
+                                                                                          : kEpiWarps * 2 * COLS_PER_WARP * 4;
+  static constexpr int OFF_BAR = OFF_SQ + SQ_BYTES;
+  static constexpr int NUM_BARS = 2 * NP + 2 * kNI + 4 + 2 * kNS;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // tmem ptr, abort flag
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;              // + alignment slack
 };
@@ -245,110 +252,132 @@ __device__ __forceinline__ void store_chunk_i(const GemmParams& p, int32_t* out,
 // Epilogue bodies
 // ------------------------------------------------------------------------------------------
 // Per-group accumulate: a flush per K group, fp32 running sums in registers.
-template <int BN, typename OutT>
+//
+// Register layout.  A warp owns 32 TMEM lanes (tile rows) and COLS_PER_WARP columns.  It drains them in
+// "slabs" of 16 rows x 32 columns with tcgen05.ld.16x256b.x4: lane (lr = lane / 4, lq = lane % 4) then holds
+// rows {lr, lr + 8} of the slab and column pairs 8 * kk + 2 * lq + {0, 1}, kk = 0..3.  Over the two slabs of
+// a 32-column chunk a thread therefore owns 4 rows (8 * a + lr, a = 0..3) and, per row, adjacent column
+// pairs: the pair is the unit of the packed f32x2 arithmetic and of the scale reads (one 8-byte shared
+// load per pair, the same address in the 8 lanes that share lq).
+//
+// Scales.  Two otherwise idle warps copy the kBM row scales and BN column scales of each K group from
+// global to shared memory (4-byte cp.async, kNS stages ahead, completion signalled on an mbarrier), so the
+// epilogue warps spend no instructions or registers on global addresses.
+template <int BN, typename OutT, bool SWAP>
 __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
                                                uint32_t bar_tm_full, uint32_t bar_tm_empty,
+                                               uint32_t bar_sc_full, uint32_t bar_sc_empty,
                                                volatile int* abort_flag) {
   using C = Cfg<BN>;
-  constexpr int NCH = C::COLS_PER_WARP / 32;
+  constexpr int CW = C::COLS_PER_WARP;
+  constexpr int NCH = CW / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ew = warp - kEpiWarp0;
   const int quad = warp & 3;         // TMEM lane quarter this warp may access
   const int half = ew >> 2;          // which half of the BN columns
-  const int col_base = half * C::COLS_PER_WARP;
-  float* sq_s = reinterpret_cast<float*>(smem + C::OFF_SQ) + ew * 2 * C::COLS_PER_WARP;
-  // order of the two multiplies: normal (p = m): (acc * sp) * sq ; swapped (p = n): (acc * sq) * sp
-  const bool pq_order = !p.swap;
+  const int col_base = half * CW;
+  const int lq = lane & 3, lr = lane >> 2;
+  const float* sc = reinterpret_cast<const float*>(smem + C::OFF_SQ);
+  // order of the two multiplies: normal (p = m): (acc * sp) * sq ; swapped (p = n): (acc * sq) * sp.
+  // The accumulators are 256 x the integer sums; 2^-8 rides on the row-side scale (exact in both orders).
+  constexpr bool pq_order = !SWAP;
   constexpr float kInv256 = 1.0f / 256.0f;
 
   Sched sched;
   TileInfo ti;
   uint32_t flush = 0;
   while (sched.next<BN>(p, ti)) {
-    float f[C::COLS_PER_WARP];
+    float2 f[CW / 2];   // [a][c][kk]: row 8a + lr, columns c * 32 + kk * 8 + 2 lq + {0, 1}
 #pragma unroll
-    for (int i = 0; i < C::COLS_PER_WARP; ++i) f[i] = 0.f;
-    const int prow = ti.p0 + quad * 32 + lane;
-    const bool prow_ok = prow < ti.p_lim;
-    __syncwarp();  // the previous tile's last reads of sq_s precede this tile's first writes
-    // software-pipelined scale fetch: values for group g+1 are requested while group g is drained
-    float sp_next = 0.f, sq_next[NCH];
-    auto fetch = [&](int g) {
-      sp_next = prow_ok ? __ldg(p.sp + (long long)g * p.sp_gstride + prow) : 0.f;
-#pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        const int q = ti.q0 + col_base + c * 32 + lane;
-        sq_next[c] = (q < ti.q_lim) ? __ldg(p.sq + ti.sq_off + (long long)g * p.sq_gstride + q) : 0.f;
-      }
-    };
-    fetch(ti.g0);
+    for (int i = 0; i < CW / 2; ++i) f[i] = make_float2(0.f, 0.f);
     bool ok = true;
     for (int g = ti.g0; g < ti.g1; ++g) {
-      float* sq_buf = sq_s + (g & 1) * C::COLS_PER_WARP;
-      const float sp = sp_next * (pq_order ? kInv256 : 1.0f);
+      const uint32_t ss = flush % kNS;
+      ok = wait_bar(bar_sc_full + ss * 8, (flush / kNS) & 1u, abort_flag);
+      if (!ok) break;
+      const float* st_p = sc + ss * (C::SCALE_STAGE / 4) + quad * 32;         // this warp's 32 row scales
+      const float* st_q = sc + ss * (C::SCALE_STAGE / 4) + kBM + col_base;    // this warp's CW column scales
+      float2 sp2[4];
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) sq_buf[c * 32 + lane] = sq_next[c] * (pq_order ? 1.0f : kInv256);
-      __syncwarp();
-      if (g + 1 < ti.g1) fetch(g + 1);
+      for (int a = 0; a < 4; ++a) {
+        const float v = st_p[8 * a + lr] * kInv256;
+        sp2[a] = make_float2(v, v);
+      }
       const uint32_t buf = flush & 1u;
       ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
+      for (int u = 0; u < 2 * NCH; ++u) {
+        const int c = u >> 1, sl = u & 1;
+        uint32_t r[16];
+        tmem_ld_16x256b_x4(taddr + ((uint32_t)(sl * 16) << 16) + c * 32, r);
         tmem_ld_wait();
-        if (c == NCH - 1) {
-          // all of this warp's columns of the buffer are in registers: hand it back to the MMA warp
+        if (u == 2 * NCH - 1) {
+          // all of this warp's part of the buffer is in registers: hand it back to the MMA warp
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_tm_empty + buf * 8);
         }
-        if (pq_order) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 s = *reinterpret_cast<const float4*>(sq_buf + c * 32 + i);
-            f[c * 32 + i + 0] = fmaf(__int2float_rn((int32_t)r[i + 0]) * sp, s.x, f[c * 32 + i + 0]);
-            f[c * 32 + i + 1] = fmaf(__int2float_rn((int32_t)r[i + 1]) * sp, s.y, f[c * 32 + i + 1]);
-            f[c * 32 + i + 2] = fmaf(__int2float_rn((int32_t)r[i + 2]) * sp, s.z, f[c * 32 + i + 2]);
-            f[c * 32 + i + 3] = fmaf(__int2float_rn((int32_t)r[i + 3]) * sp, s.w, f[c * 32 + i + 3]);
-          }
-        } else {
+        for (int kk = 0; kk < 4; ++kk) {
+          const float2 sq = *reinterpret_cast<const float2*>(st_q + c * 32 + kk * 8 + lq * 2);
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 s = *reinterpret_cast<const float4*>(sq_buf + c * 32 + i);
-            f[c * 32 + i + 0] = fmaf(__int2float_rn((int32_t)r[i + 0]) * s.x, sp, f[c * 32 + i + 0]);
-            f[c * 32 + i + 1] = fmaf(__int2float_rn((int32_t)r[i + 1]) * s.y, sp, f[c * 32 + i + 1]);
-            f[c * 32 + i + 2] = fmaf(__int2float_rn((int32_t)r[i + 2]) * s.z, sp, f[c * 32 + i + 2]);
-            f[c * 32 + i + 3] = fmaf(__int2float_rn((int32_t)r[i + 3]) * s.w, sp, f[c * 32 + i + 3]);
+          for (int h = 0; h < 2; ++h) {
+            const int a = sl * 2 + h;
+            const float2 d = make_float2(__int2float_rn((int32_t)r[4 * kk + 2 * h]),
+                                         __int2float_rn((int32_t)r[4 * kk + 2 * h + 1]));
+            float2& acc = f[(a * NCH + c) * 4 + kk];
+            if (pq_order) acc = __ffma2_rn(__fmul2_rn(d, sp2[a]), sq, acc);
+            else acc = __ffma2_rn(__fmul2_rn(d, sq), sp2[a], acc);
           }
         }
       }
+      __syncwarp();   // every lane has read its scales of this stage
+      if (lane == 0) mbar_arrive(bar_sc_empty + ss * 8);
       ++flush;
     }
     if (!ok) break;
+    // ---- write the tile: thread owns rows 8a + lr, column pairs c * 32 + kk * 8 + 2 lq ----
+    OutT* out = static_cast<OutT*>(p.out);
+    float* ws = (p.split_ws != nullptr) ? p.split_ws + (long long)ti.split * p.ws_stride : nullptr;
+    const bool pair_ok = ((p.ldc & 1) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
 #pragma unroll
-    for (int c = 0; c < NCH; ++c) {
-      float v[32];
+    for (int a = 0; a < 4; ++a) {
+      const int prow = ti.p0 + quad * 32 + 8 * a + lr;
+      if (prow >= ti.p_lim) continue;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = f[c * 32 + i];
-      if (p.split_ws != nullptr) {
-        // split-K: fp32 partial sums of this K range, element (m, n) at ws[split][m * ldc + n]
-        float* ws = p.split_ws + (long long)ti.split * p.ws_stride;
-        const int qcol0 = ti.q0 + col_base + c * 32;
-        if (prow < ti.p_lim) {
+      for (int c = 0; c < NCH; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (qcol0 + i < ti.q_lim) {
-              if (!p.swap) ws[(long long)prow * p.ldc + qcol0 + i] = v[i];
-              else ws[(long long)(qcol0 + i) * p.ldc + prow] = v[i];
+        for (int kk = 0; kk < 4; ++kk) {
+          const float2 v = f[(a * NCH + c) * 4 + kk];
+          const int q = ti.q0 + col_base + c * 32 + kk * 8 + lq * 2;
+          if (ws != nullptr) {
+            // split-K: fp32 partial sums of this K range, element (m, n) at ws[split][m * ldc + n]
+            if (!SWAP) {
+              float* dst = ws + (long long)prow * p.ldc + q;
+              if (q + 1 < ti.q_lim && (p.ldc & 1) == 0) *reinterpret_cast<float2*>(dst) = v;
+              else { if (q < ti.q_lim) dst[0] = v.x; if (q + 1 < ti.q_lim) dst[1] = v.y; }
+            } else {
+              if (q < ti.q_lim) ws[(long long)q * p.ldc + prow] = v.x;
+              if (q + 1 < ti.q_lim) ws[(long long)(q + 1) * p.ldc + prow] = v.y;
             }
+          } else if (!SWAP) {
+            OutT* dst = out + (long long)prow * p.ldc + q;
+            if (q + 1 < ti.q_lim && pair_ok) {
+              union { OutT h[2]; uint32_t u; } pk;
+              pk.h[0] = cast_out<OutT>(v.x); pk.h[1] = cast_out<OutT>(v.y);
+              *reinterpret_cast<uint32_t*>(dst) = pk.u;
+            } else {
+              if (q < ti.q_lim) dst[0] = cast_out<OutT>(v.x);
+              if (q + 1 < ti.q_lim) dst[1] = cast_out<OutT>(v.y);
+            }
+          } else {
+            if (q < ti.q_lim) out[(long long)q * p.ldc + prow] = cast_out<OutT>(v.x);
+            if (q + 1 < ti.q_lim) out[(long long)(q + 1) * p.ldc + prow] = cast_out<OutT>(v.y);
           }
         }
-      } else {
-        store_chunk_f<OutT>(p, v, prow, ti.q0 + col_base + c * 32, ti);
       }
     }
   }
@@ -449,6 +478,8 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   const uint32_t bar_i8_empty = bar_i8_full + kNI * 8;
   const uint32_t bar_tm_full = bar_i8_empty + kNI * 8;
   const uint32_t bar_tm_empty = bar_tm_full + 2 * 8;
+  const uint32_t bar_sc_full = bar_tm_empty + 2 * 8;
+  const uint32_t bar_sc_empty = bar_sc_full + kNS * 8;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 8);
 
@@ -456,6 +487,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     for (int i = 0; i < C::NP; ++i) { mbar_init(bar_pk_full + i * 8, 1); mbar_init(bar_pk_empty + i * 8, kConvWarps); }
     for (int i = 0; i < kNI; ++i) { mbar_init(bar_i8_full + i * 8, kConvWarps); mbar_init(bar_i8_empty + i * 8, 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(bar_tm_full + i * 8, 1); mbar_init(bar_tm_empty + i * 8, kEpiWarps); }
+    for (int i = 0; i < kNS; ++i) { mbar_init(bar_sc_full + i * 8, 32); mbar_init(bar_sc_empty + i * 8, kEpiWarps); }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tmP);
@@ -549,6 +581,38 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         if (last) ++flush;
       }
     }
+  } else if (p.epi_mode == EPI_GROUP) {
+    // ---------------- scale loaders (warps 2 and 3 take alternate K groups) ----------------
+    const uint32_t w = (uint32_t)(warp - kScaleWarp0);
+    Sched sched;
+    TileInfo ti;
+    uint32_t it = 0;
+    bool ok = true;
+    while (ok && sched.next<BN>(p, ti)) {
+      for (int g = ti.g0; g < ti.g1; ++g, ++it) {
+        if ((it % kScaleWarps) != w) continue;
+        const uint32_t ss = it % kNS;
+        ok = wait_bar(bar_sc_empty + ss * 8, ((it / kNS) & 1u) ^ 1u, abort_flag);
+        if (!ok) break;
+        const uint32_t dst = sbase + C::OFF_SQ + ss * C::SCALE_STAGE;
+        const float* src_p = p.sp + (long long)g * p.sp_gstride;
+#pragma unroll
+        for (int j = 0; j < kBM / 32; ++j) {
+          const int row = ti.p0 + j * 32 + lane;
+          const bool v = row < ti.p_lim;
+          cp_async_4_zfill(dst + (uint32_t)(j * 32 + lane) * 4u, v ? src_p + row : p.sp, v);
+        }
+        const float* src_q = p.sq + ti.sq_off + (long long)g * p.sq_gstride;
+#pragma unroll
+        for (int j = 0; j < BN / 32; ++j) {
+          const int q = ti.q0 + j * 32 + lane;
+          const bool v = q < ti.q_lim;
+          cp_async_4_zfill(dst + (uint32_t)(kBM + j * 32 + lane) * 4u, v ? src_q + q : p.sq, v);
+        }
+        cp_async_mbar_arrive_noinc(bar_sc_full + ss * 8);   // fires when this lane's copies have landed
+      }
+    }
+    cp_async_wait_all();   // nothing of this warp is in flight into shared memory at teardown
   }
   } else if (warp < kConvWarp0 + kConvWarps) {
     // ---------------- converters ----------------
@@ -582,7 +646,8 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     // ---------------- epilogue ----------------
     setmaxnreg_inc<kRegsEpi>();
     if (p.epi_mode == EPI_GROUP) {
-      epilogue_group<BN, __nv_bfloat16>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+      if (p.swap) epilogue_group<BN, __nv_bfloat16, true>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
+      else epilogue_group<BN, __nv_bfloat16, false>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
     } else if (p.epi_mode == EPI_CHANNEL && p.out_dtype == I4TC_FP16) {
       epilogue_simple<BN, __half>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
     } else {

@@ -221,6 +221,16 @@ __device__ __forceinline__ uint64_t lds64(uint32_t addr) {
 __device__ __forceinline__ void cp_async_4(uint32_t dst_smem, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
 }
+// The same copy, writing zero instead when `valid` is false (nothing is read from `src` then).
+__device__ __forceinline__ void cp_async_4_zfill(uint32_t dst_smem, const void* src, bool valid) {
+  const uint32_t n = valid ? 4u : 0u;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst_smem), "l"(src), "r"(n) : "memory");
+}
+// Makes the mbarrier receive one arrival (not added to its expected count) once all cp.async copies this
+// thread issued before have completed.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.wait_all;" ::: "memory");
 }
