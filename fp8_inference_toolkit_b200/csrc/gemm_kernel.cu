@@ -342,40 +342,80 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
     // ---- write the tile: thread owns rows 8a + lr, column pairs c * 32 + kk * 8 + 2 lq ----
     OutT* out = static_cast<OutT*>(p.out);
     float* ws = (p.split_ws != nullptr) ? p.split_ws + (long long)ti.split * p.ws_stride : nullptr;
-    const bool pair_ok = ((p.ldc & 1) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
+    const bool vec_ok = !SWAP && ws == nullptr && ((p.ldc & 7) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) && (ti.q0 + col_base + CW <= ti.q_lim);
+    if (vec_ok) {
+      // The four lanes of a quad hold, per row and 32-column chunk, four column pairs each (kk = 0..3).
+      // A 4 x 4 transpose inside the quad (two butterfly exchanges) gives every lane 8 consecutive
+      // columns, written with one 16-byte store; a quad then covers 64 contiguous bytes of the row.
+      const bool odd = (lq & 1) != 0, hi = (lq & 2) != 0;
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const int prow = ti.p0 + quad * 32 + 8 * a + lr;
-      if (prow >= ti.p_lim) continue;
+      for (int a = 0; a < 4; ++a) {
+        const int prow = ti.p0 + quad * 32 + 8 * a + lr;
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
+        for (int c = 0; c < NCH; ++c) {
+          uint32_t x[4];
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const float2 v = f[(a * NCH + c) * 4 + kk];
-          const int q = ti.q0 + col_base + c * 32 + kk * 8 + lq * 2;
-          if (ws != nullptr) {
-            // split-K: fp32 partial sums of this K range, element (m, n) at ws[split][m * ldc + n]
-            if (!SWAP) {
-              float* dst = ws + (long long)prow * p.ldc + q;
-              if (q + 1 < ti.q_lim && (p.ldc & 1) == 0) *reinterpret_cast<float2*>(dst) = v;
-              else { if (q < ti.q_lim) dst[0] = v.x; if (q + 1 < ti.q_lim) dst[1] = v.y; }
+          for (int kk = 0; kk < 4; ++kk) {
+            const float2 v = f[(a * NCH + c) * 4 + kk];
+            union { OutT h[2]; uint32_t u; } pk;
+            pk.h[0] = cast_out<OutT>(v.x); pk.h[1] = cast_out<OutT>(v.y);
+            x[kk] = pk.u;
+          }
+          // exchange with lane ^ 1: keep the pairs whose kk has my low bit, receive the partner's
+          const uint32_t r0 = __shfl_xor_sync(0xffffffffu, odd ? x[0] : x[1], 1);
+          const uint32_t r1 = __shfl_xor_sync(0xffffffffu, odd ? x[2] : x[3], 1);
+          // u[kkhi][src]: src 0 = even lane of the lane pair, 1 = odd lane
+          const uint32_t own0 = odd ? x[1] : x[0], own1 = odd ? x[3] : x[2];
+          const uint32_t u00 = odd ? r0 : own0, u01 = odd ? own0 : r0;   // kk = (lq & 1)
+          const uint32_t u10 = odd ? r1 : own1, u11 = odd ? own1 : r1;   // kk = (lq & 1) + 2
+          // exchange with lane ^ 2: keep kkhi == (lq >> 1)
+          const uint32_t t0 = __shfl_xor_sync(0xffffffffu, hi ? u00 : u10, 2);
+          const uint32_t t1 = __shfl_xor_sync(0xffffffffu, hi ? u01 : u11, 2);
+          const uint32_t k0 = hi ? u10 : u00, k1 = hi ? u11 : u01;       // from lanes (lq & 2) + {0, 1}
+          // sources in lane order 0..3 of the quad
+          uint4 y;
+          y.x = hi ? t0 : k0; y.y = hi ? t1 : k1; y.z = hi ? k0 : t0; y.w = hi ? k1 : t1;
+          if (prow < ti.p_lim)
+            *reinterpret_cast<uint4*>(out + (long long)prow * p.ldc + ti.q0 + col_base + c * 32 + lq * 8) = y;
+        }
+      }
+    } else {
+      const bool pair_ok = ((p.ldc & 1) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const int prow = ti.p0 + quad * 32 + 8 * a + lr;
+        if (prow >= ti.p_lim) continue;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const float2 v = f[(a * NCH + c) * 4 + kk];
+            const int q = ti.q0 + col_base + c * 32 + kk * 8 + lq * 2;
+            if (ws != nullptr) {
+              // split-K: fp32 partial sums of this K range, element (m, n) at ws[split][m * ldc + n]
+              if (!SWAP) {
+                float* dst = ws + (long long)prow * p.ldc + q;
+                if (q + 1 < ti.q_lim && (p.ldc & 1) == 0) *reinterpret_cast<float2*>(dst) = v;
+                else { if (q < ti.q_lim) dst[0] = v.x; if (q + 1 < ti.q_lim) dst[1] = v.y; }
+              } else {
+                if (q < ti.q_lim) ws[(long long)q * p.ldc + prow] = v.x;
+                if (q + 1 < ti.q_lim) ws[(long long)(q + 1) * p.ldc + prow] = v.y;
+              }
+            } else if (!SWAP) {
+              OutT* dst = out + (long long)prow * p.ldc + q;
+              if (q + 1 < ti.q_lim && pair_ok) {
+                union { OutT h[2]; uint32_t u; } pk;
+                pk.h[0] = cast_out<OutT>(v.x); pk.h[1] = cast_out<OutT>(v.y);
+                *reinterpret_cast<uint32_t*>(dst) = pk.u;
+              } else {
+                if (q < ti.q_lim) dst[0] = cast_out<OutT>(v.x);
+                if (q + 1 < ti.q_lim) dst[1] = cast_out<OutT>(v.y);
+              }
             } else {
-              if (q < ti.q_lim) ws[(long long)q * p.ldc + prow] = v.x;
-              if (q + 1 < ti.q_lim) ws[(long long)(q + 1) * p.ldc + prow] = v.y;
+              if (q < ti.q_lim) out[(long long)q * p.ldc + prow] = cast_out<OutT>(v.x);
+              if (q + 1 < ti.q_lim) out[(long long)(q + 1) * p.ldc + prow] = cast_out<OutT>(v.y);
             }
-          } else if (!SWAP) {
-            OutT* dst = out + (long long)prow * p.ldc + q;
-            if (q + 1 < ti.q_lim && pair_ok) {
-              union { OutT h[2]; uint32_t u; } pk;
-              pk.h[0] = cast_out<OutT>(v.x); pk.h[1] = cast_out<OutT>(v.y);
-              *reinterpret_cast<uint32_t*>(dst) = pk.u;
-            } else {
-              if (q < ti.q_lim) dst[0] = cast_out<OutT>(v.x);
-              if (q + 1 < ti.q_lim) dst[1] = cast_out<OutT>(v.y);
-            }
-          } else {
-            if (q < ti.q_lim) out[(long long)q * p.ldc + prow] = cast_out<OutT>(v.x);
-            if (q + 1 < ti.q_lim) out[(long long)(q + 1) * p.ldc + prow] = cast_out<OutT>(v.y);
           }
         }
       }
