@@ -114,12 +114,10 @@ struct Sched {
 };
 
 // Bounded mbarrier wait, uniform across the warp.  Returns false (and raises the abort flag)
-// when the limit expires or another role has already aborted.
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  // a non-blocking probe first: when the phase has already completed it is much cheaper than the
-  // potentially-suspending try_wait
-  bool ok = mbar_test_wait(bar, parity);
-  if (!ok) ok = mbar_try_wait(bar, parity);
+// when the limit expires or another role has already aborted.  The common case -- the phase has
+// already completed -- is one non-blocking probe; everything else is the rare path.
+__device__ __forceinline__ bool wait_bar_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  bool ok = mbar_try_wait(bar, parity);
   if (!ok) {
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
@@ -135,6 +133,10 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   ok = __all_sync(0xffffffffu, ok);
   if (!ok) *abort_flag = 1;
   return ok;
+}
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
+  return wait_bar_slow(bar, parity, abort_flag);
 }
 
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
@@ -265,8 +267,7 @@ __device__ __forceinline__ void store_chunk_i(const GemmParams& p, int32_t* out,
 // epilogue warps spend no instructions or registers on global addresses.
 template <int BN, typename OutT, bool SWAP>
 __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
-                                               uint32_t bar_tm_full, uint32_t bar_tm_empty,
-                                               uint32_t bar_sc_full, uint32_t bar_sc_empty,
+                                               uint32_t bar_tm_full, uint32_t bar_tm_empty, uint32_t bar_sc_empty,
                                                volatile int* abort_flag) {
   using C = Cfg<BN>;
   constexpr int CW = C::COLS_PER_WARP;
@@ -292,9 +293,13 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
     for (int i = 0; i < CW / 2; ++i) f[i] = make_float2(0.f, 0.f);
     bool ok = true;
     for (int g = ti.g0; g < ti.g1; ++g) {
+      // the MMA warp waited for this scale stage before it issued the group, so an accumulator that is
+      // full implies scales that have landed
       const uint32_t ss = flush % kNS;
-      ok = wait_bar(bar_sc_full + ss * 8, (flush / kNS) & 1u, abort_flag);
+      const uint32_t buf = flush & 1u;
+      ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
       if (!ok) break;
+      tc_fence_after_sync();
       const float* st_p = sc + ss * (C::SCALE_STAGE / 4) + quad * 32;         // this warp's 32 row scales
       const float* st_q = sc + ss * (C::SCALE_STAGE / 4) + kBM + col_base;    // this warp's CW column scales
       float2 sp2[4];
@@ -303,10 +308,6 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
         const float v = st_p[8 * a + lr] * kInv256;
         sp2[a] = make_float2(v, v);
       }
-      const uint32_t buf = flush & 1u;
-      ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
-      if (!ok) break;
-      tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
 #pragma unroll
       for (int u = 0; u < 2 * NCH; ++u) {
@@ -603,6 +604,10 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         const uint32_t s = it % kNI, ph = (it / kNI) & 1u;
         ok = wait_bar(bar_i8_full + s * 8, ph, abort_flag);
         if (!ok) break;
+        if (p.epi_mode == EPI_GROUP) {
+          ok = wait_bar(bar_sc_full + (flush % kNS) * 8, (flush / kNS) & 1u, abort_flag);
+          if (!ok) break;
+        }
         tc_fence_after_sync();
         if (lane == 0) {
           const uint32_t aP = sbase + C::OFF_I8 + s * (C::I8_P + C::I8_Q);
@@ -686,8 +691,8 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     // ---------------- epilogue ----------------
     setmaxnreg_inc<kRegsEpi>();
     if (p.epi_mode == EPI_GROUP) {
-      if (p.swap) epilogue_group<BN, __nv_bfloat16, true>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
-      else epilogue_group<BN, __nv_bfloat16, false>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
+      if (p.swap) epilogue_group<BN, __nv_bfloat16, true>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, bar_sc_empty, abort_flag);
+      else epilogue_group<BN, __nv_bfloat16, false>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, bar_sc_empty, abort_flag);
     } else if (p.epi_mode == EPI_CHANNEL && p.out_dtype == I4TC_FP16) {
       epilogue_simple<BN, __half>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
     } else {
