@@ -195,36 +195,8 @@ __device__ __forceinline__ __nv_bfloat16 cast_out<__nv_bfloat16>(float v) { retu
 template <>
 __device__ __forceinline__ __half cast_out<__half>(float v) { return __float2half_rn(v); }
 
-// Stores 32 consecutive output values of one tile row (normal) or 32 values of one tile column
-// spread over 32 rows (swap).  `vals` are fp32 (cast to OutT) or raw int32.
-template <typename OutT>
-__device__ __forceinline__ void store_chunk_f(const GemmParams& p, const float (&v)[32], int prow, int qcol0,
-                                              const TileInfo& ti) {
-  OutT* out = static_cast<OutT*>(p.out);
-  if (prow >= ti.p_lim) return;
-  if (!p.swap) {
-    OutT* dst = out + (long long)prow * p.ldc + qcol0;
-    const bool vec = (qcol0 + 32 <= ti.q_lim) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-    if (vec) {
-#pragma unroll
-      for (int i = 0; i < 32; i += 8) {
-        union { OutT h[8]; uint4 u; } pk;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) pk.h[k] = cast_out<OutT>(v[i + k]);
-        *reinterpret_cast<uint4*>(dst + i) = pk.u;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (qcol0 + i < ti.q_lim) dst[i] = cast_out<OutT>(v[i]);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (qcol0 + i < ti.q_lim) out[(long long)(qcol0 + i) * p.ldc + prow] = cast_out<OutT>(v[i]);
-  }
-}
-
+// Stores 32 consecutive int32 values of one tile row (normal) or of one tile column spread over 32 rows
+// (swap); the accumulators are 256 x the integer sums.
 __device__ __forceinline__ void store_chunk_i(const GemmParams& p, int32_t* out, const uint32_t (&r)[32], int prow,
                                               int qcol0, const TileInfo& ti) {
   if (prow >= ti.p_lim) return;
@@ -247,6 +219,51 @@ __device__ __forceinline__ void store_chunk_i(const GemmParams& p, int32_t* out,
 #pragma unroll
     for (int i = 0; i < 32; ++i)
       if (qcol0 + i < ti.q_lim) out[(long long)(qcol0 + i) * p.ldc + prow] = ((int32_t)r[i]) >> 8;
+  }
+}
+
+// 4 x 4 transpose inside a quad of lanes (two butterfly exchanges).  On entry lane lq of the quad holds
+// x[kk], kk = 0..3; on return it holds { x of lane 0, 1, 2, 3 }[kk = lq].  With x[kk] = the packed pair of
+// columns 8 kk + 2 lq + {0, 1} this gives every lane 8 consecutive 16-bit columns (8 lq .. 8 lq + 7).
+__device__ __forceinline__ uint4 quad_transpose(const uint32_t (&x)[4], int lq) {
+  const bool odd = (lq & 1) != 0, hi = (lq & 2) != 0;
+  // exchange with lane ^ 1: keep the pairs whose kk has my low bit, receive the partner's
+  const uint32_t r0 = __shfl_xor_sync(0xffffffffu, odd ? x[0] : x[1], 1);
+  const uint32_t r1 = __shfl_xor_sync(0xffffffffu, odd ? x[2] : x[3], 1);
+  const uint32_t own0 = odd ? x[1] : x[0], own1 = odd ? x[3] : x[2];
+  const uint32_t u00 = odd ? r0 : own0, u01 = odd ? own0 : r0;   // kk = (lq & 1), from the even / odd lane
+  const uint32_t u10 = odd ? r1 : own1, u11 = odd ? own1 : r1;   // kk = (lq & 1) + 2
+  // exchange with lane ^ 2: keep kk's high bit == (lq >> 1)
+  const uint32_t t0 = __shfl_xor_sync(0xffffffffu, hi ? u00 : u10, 2);
+  const uint32_t t1 = __shfl_xor_sync(0xffffffffu, hi ? u01 : u11, 2);
+  const uint32_t k0 = hi ? u10 : u00, k1 = hi ? u11 : u01;
+  uint4 y;
+  y.x = hi ? t0 : k0; y.y = hi ? t1 : k1; y.z = hi ? k0 : t0; y.w = hi ? k1 : t1;
+  return y;
+}
+
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack_pair(float2 v) {
+  union { OutT h[2]; uint32_t u; } pk;
+  pk.h[0] = cast_out<OutT>(v.x); pk.h[1] = cast_out<OutT>(v.y);
+  return pk.u;
+}
+
+// Writes the column pair (q, q + 1) of tile row prow without any alignment assumption beyond what
+// `pair_ok` promises (even ldc, 4-byte aligned base): 16-bit output, normal or swapped orientation.
+template <typename OutT, bool SWAP>
+__device__ __forceinline__ void store_pair(OutT* out, long long ldc, int prow, int q, int q_lim, float2 v, bool pair_ok) {
+  if (!SWAP) {
+    OutT* dst = out + (long long)prow * ldc + q;
+    if (q + 1 < q_lim && pair_ok) {
+      *reinterpret_cast<uint32_t*>(dst) = pack_pair<OutT>(v);
+    } else {
+      if (q < q_lim) dst[0] = cast_out<OutT>(v.x);
+      if (q + 1 < q_lim) dst[1] = cast_out<OutT>(v.y);
+    }
+  } else {
+    if (q < q_lim) out[(long long)q * ldc + prow] = cast_out<OutT>(v.x);
+    if (q + 1 < q_lim) out[(long long)(q + 1) * ldc + prow] = cast_out<OutT>(v.y);
   }
 }
 
@@ -346,10 +363,8 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
     const bool vec_ok = !SWAP && ws == nullptr && ((p.ldc & 7) == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) && (ti.q0 + col_base + CW <= ti.q_lim);
     if (vec_ok) {
-      // The four lanes of a quad hold, per row and 32-column chunk, four column pairs each (kk = 0..3).
-      // A 4 x 4 transpose inside the quad (two butterfly exchanges) gives every lane 8 consecutive
-      // columns, written with one 16-byte store; a quad then covers 64 contiguous bytes of the row.
-      const bool odd = (lq & 1) != 0, hi = (lq & 2) != 0;
+      // per row and 32-column chunk the quad holds four column pairs per lane; after the quad transpose
+      // each lane writes 8 consecutive columns with one 16-byte store (64 contiguous bytes per quad)
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
         const int prow = ti.p0 + quad * 32 + 8 * a + lr;
@@ -357,26 +372,8 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
         for (int c = 0; c < NCH; ++c) {
           uint32_t x[4];
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const float2 v = f[(a * NCH + c) * 4 + kk];
-            union { OutT h[2]; uint32_t u; } pk;
-            pk.h[0] = cast_out<OutT>(v.x); pk.h[1] = cast_out<OutT>(v.y);
-            x[kk] = pk.u;
-          }
-          // exchange with lane ^ 1: keep the pairs whose kk has my low bit, receive the partner's
-          const uint32_t r0 = __shfl_xor_sync(0xffffffffu, odd ? x[0] : x[1], 1);
-          const uint32_t r1 = __shfl_xor_sync(0xffffffffu, odd ? x[2] : x[3], 1);
-          // u[kkhi][src]: src 0 = even lane of the lane pair, 1 = odd lane
-          const uint32_t own0 = odd ? x[1] : x[0], own1 = odd ? x[3] : x[2];
-          const uint32_t u00 = odd ? r0 : own0, u01 = odd ? own0 : r0;   // kk = (lq & 1)
-          const uint32_t u10 = odd ? r1 : own1, u11 = odd ? own1 : r1;   // kk = (lq & 1) + 2
-          // exchange with lane ^ 2: keep kkhi == (lq >> 1)
-          const uint32_t t0 = __shfl_xor_sync(0xffffffffu, hi ? u00 : u10, 2);
-          const uint32_t t1 = __shfl_xor_sync(0xffffffffu, hi ? u01 : u11, 2);
-          const uint32_t k0 = hi ? u10 : u00, k1 = hi ? u11 : u01;       // from lanes (lq & 2) + {0, 1}
-          // sources in lane order 0..3 of the quad
-          uint4 y;
-          y.x = hi ? t0 : k0; y.y = hi ? t1 : k1; y.z = hi ? k0 : t0; y.w = hi ? k1 : t1;
+          for (int kk = 0; kk < 4; ++kk) x[kk] = pack_pair<OutT>(f[(a * NCH + c) * 4 + kk]);
+          const uint4 y = quad_transpose(x, lq);
           if (prow < ti.p_lim)
             *reinterpret_cast<uint4*>(out + (long long)prow * p.ldc + ti.q0 + col_base + c * 32 + lq * 8) = y;
         }
@@ -403,19 +400,8 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
                 if (q < ti.q_lim) ws[(long long)q * p.ldc + prow] = v.x;
                 if (q + 1 < ti.q_lim) ws[(long long)(q + 1) * p.ldc + prow] = v.y;
               }
-            } else if (!SWAP) {
-              OutT* dst = out + (long long)prow * p.ldc + q;
-              if (q + 1 < ti.q_lim && pair_ok) {
-                union { OutT h[2]; uint32_t u; } pk;
-                pk.h[0] = cast_out<OutT>(v.x); pk.h[1] = cast_out<OutT>(v.y);
-                *reinterpret_cast<uint32_t*>(dst) = pk.u;
-              } else {
-                if (q < ti.q_lim) dst[0] = cast_out<OutT>(v.x);
-                if (q + 1 < ti.q_lim) dst[1] = cast_out<OutT>(v.y);
-              }
             } else {
-              if (q < ti.q_lim) out[(long long)q * p.ldc + prow] = cast_out<OutT>(v.x);
-              if (q + 1 < ti.q_lim) out[(long long)(q + 1) * p.ldc + prow] = cast_out<OutT>(v.y);
+              store_pair<OutT, SWAP>(out, p.ldc, prow, q, ti.q_lim, v, pair_ok);
             }
           }
         }
@@ -424,11 +410,108 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
   }
 }
 
-// One flush per tile (EPI_INT32, EPI_CHANNEL) or raw per-group dumps (EPI_GROUP_INT32).
-template <int BN, typename OutT>
-__device__ __forceinline__ void epilogue_simple(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
-                                                uint32_t bar_tm_full, uint32_t bar_tm_empty,
-                                                volatile int* abort_flag) {
+// One flush per tile with per-channel scales: out = cast((acc * scale_b[n]) * scale_a[m]), the
+// reference's order.  Same slab register layout and quad-transposed stores as the per-group epilogue.
+template <int BN, typename OutT, bool SWAP>
+__device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
+                                                 uint32_t bar_tm_full, uint32_t bar_tm_empty,
+                                                 volatile int* abort_flag) {
+  using C = Cfg<BN>;
+  constexpr int CW = C::COLS_PER_WARP;
+  constexpr int NCH = CW / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ew = warp - kEpiWarp0;
+  const int quad = warp & 3;
+  const int half = ew >> 2;
+  const int col_base = half * CW;
+  const int lq = lane & 3, lr = lane >> 2;
+  float* sq_s = reinterpret_cast<float*>(smem + C::OFF_SQ) + ew * CW;
+  constexpr float kInv256 = 1.0f / 256.0f;
+  // normal: columns are n, so the column scale (scale_b) multiplies first; swapped: rows are n.
+  // The first multiplier also carries the 2^-8 that undoes the x16 operand scaling (exact).
+  constexpr bool q_first = !SWAP;
+  OutT* out = static_cast<OutT*>(p.out);
+
+  Sched sched;
+  TileInfo ti;
+  uint32_t flush = 0;
+  bool ok = true;
+  while (ok && sched.next<BN>(p, ti)) {
+    __syncwarp();  // the previous tile's reads of sq_s are done
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int q = ti.q0 + col_base + c * 32 + lane;
+      const float sv = (q < ti.q_lim) ? __ldg(p.sq + ti.sq_off + q) : 0.f;
+      sq_s[c * 32 + lane] = q_first ? sv * kInv256 : sv;
+    }
+    float spv[4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const int prow = ti.p0 + quad * 32 + 8 * a + lr;
+      const float sv = (prow < ti.p_lim) ? __ldg(p.sp + prow) : 0.f;
+      spv[a] = q_first ? sv : sv * kInv256;
+    }
+    __syncwarp();
+    const bool vec_ok = !SWAP && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                        (ti.q0 + col_base + CW <= ti.q_lim);
+    const bool pair_ok = ((p.ldc & 1) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
+    const uint32_t buf = flush & 1u;
+    ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
+    if (!ok) break;
+    tc_fence_after_sync();
+    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
+#pragma unroll
+    for (int u = 0; u < 2 * NCH; ++u) {
+      const int c = u >> 1, sl = u & 1;
+      uint32_t r[16];
+      tmem_ld_16x256b_x4(taddr + ((uint32_t)(sl * 16) << 16) + c * 32, r);
+      tmem_ld_wait();
+      if (u == 2 * NCH - 1) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tm_empty + buf * 8);
+      }
+      float2 v[2][4];
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const float2 sq = *reinterpret_cast<const float2*>(sq_s + c * 32 + kk * 8 + lq * 2);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float sp = spv[sl * 2 + h];
+          const float d0 = __int2float_rn((int32_t)r[4 * kk + 2 * h]);
+          const float d1 = __int2float_rn((int32_t)r[4 * kk + 2 * h + 1]);
+          v[h][kk] = q_first ? make_float2((d0 * sq.x) * sp, (d1 * sq.y) * sp)
+                             : make_float2((d0 * sp) * sq.x, (d1 * sp) * sq.y);
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int prow = ti.p0 + quad * 32 + 8 * (sl * 2 + h) + lr;
+        if (vec_ok) {
+          uint32_t x[4];
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) x[kk] = pack_pair<OutT>(v[h][kk]);
+          const uint4 y = quad_transpose(x, lq);
+          if (prow < ti.p_lim)
+            *reinterpret_cast<uint4*>(out + (long long)prow * p.ldc + ti.q0 + col_base + c * 32 + lq * 8) = y;
+        } else if (prow < ti.p_lim) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            store_pair<OutT, SWAP>(out, p.ldc, prow, ti.q0 + col_base + c * 32 + kk * 8 + lq * 2, ti.q_lim,
+                                   v[h][kk], pair_ok);
+        }
+      }
+    }
+    ++flush;
+  }
+}
+
+// One flush per tile (EPI_INT32) or raw per-group dumps (EPI_GROUP_INT32): int32 out = acc >> 8.
+// Thread = tile row here (32x32b loads): these are the verification paths, not the fast ones.
+template <int BN>
+__device__ __forceinline__ void epilogue_int32(const GemmParams& p, uint32_t tmem_base,
+                                               uint32_t bar_tm_full, uint32_t bar_tm_empty,
+                                               volatile int* abort_flag) {
   using C = Cfg<BN>;
   constexpr int NCH = C::COLS_PER_WARP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -436,12 +519,7 @@ __device__ __forceinline__ void epilogue_simple(const GemmParams& p, uint8_t* sm
   const int quad = warp & 3;
   const int half = ew >> 2;
   const int col_base = half * C::COLS_PER_WARP;
-  float* sq_s = reinterpret_cast<float*>(smem + C::OFF_SQ) + ew * 2 * C::COLS_PER_WARP;
   const bool per_group = p.epi_mode == EPI_GROUP_INT32;
-
-  constexpr float kInv256 = 1.0f / 256.0f;
-  // reference order (acc * scale_b[n]) * scale_a[m]: normal -> column scale first; swapped -> row scale first
-  const bool q_first = !p.swap;
 
   Sched sched;
   TileInfo ti;
@@ -449,18 +527,6 @@ __device__ __forceinline__ void epilogue_simple(const GemmParams& p, uint8_t* sm
   bool ok = true;
   while (ok && sched.next<BN>(p, ti)) {
     const int prow = ti.p0 + quad * 32 + lane;
-    float sp = 0.f;
-    if (p.epi_mode == EPI_CHANNEL) {
-      sp = (prow < ti.p_lim) ? __ldg(p.sp + prow) : 0.f;
-      if (!q_first) sp *= kInv256;
-#pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        const int q = ti.q0 + col_base + c * 32 + lane;
-        const float s = (q < ti.q_lim) ? __ldg(p.sq + ti.sq_off + q) : 0.f;
-        sq_s[c * 32 + lane] = q_first ? s * kInv256 : s;
-      }
-      __syncwarp();
-    }
     const int nflush = per_group ? (ti.g1 - ti.g0) : 1;
     for (int fl = 0; fl < nflush; ++fl) {
       const uint32_t buf = flush & 1u;
@@ -478,24 +544,11 @@ __device__ __forceinline__ void epilogue_simple(const GemmParams& p, uint8_t* sm
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_tm_empty + buf * 8);
         }
-        const int qcol0 = ti.q0 + col_base + c * 32;
-        if (p.epi_mode == EPI_CHANNEL) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float a = __int2float_rn((int32_t)r[i]);
-            const float s = sq_s[c * 32 + i];
-            v[i] = q_first ? (a * s) * sp : (a * sp) * s;
-          }
-          store_chunk_f<OutT>(p, v, prow, qcol0, ti);
-        } else {
-          int32_t* out = static_cast<int32_t*>(p.out) + (per_group ? (long long)(ti.g0 + fl) * p.out_gstride : 0ll);
-          store_chunk_i(p, out, r, prow, qcol0, ti);
-        }
+        int32_t* out = static_cast<int32_t*>(p.out) + (per_group ? (long long)(ti.g0 + fl) * p.out_gstride : 0ll);
+        store_chunk_i(p, out, r, prow, ti.q0 + col_base + c * 32, ti);
       }
       ++flush;
     }
-    __syncwarp();  // sq_s is rewritten at the next tile
   }
 }
 
@@ -693,10 +746,16 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     if (p.epi_mode == EPI_GROUP) {
       if (p.swap) epilogue_group<BN, __nv_bfloat16, true>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, bar_sc_empty, abort_flag);
       else epilogue_group<BN, __nv_bfloat16, false>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, bar_sc_empty, abort_flag);
-    } else if (p.epi_mode == EPI_CHANNEL && p.out_dtype == I4TC_FP16) {
-      epilogue_simple<BN, __half>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+    } else if (p.epi_mode == EPI_CHANNEL) {
+      if (p.out_dtype == I4TC_FP16) {
+        if (p.swap) epilogue_channel<BN, __half, true>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+        else epilogue_channel<BN, __half, false>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+      } else {
+        if (p.swap) epilogue_channel<BN, __nv_bfloat16, true>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+        else epilogue_channel<BN, __nv_bfloat16, false>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+      }
     } else {
-      epilogue_simple<BN, __nv_bfloat16>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+      epilogue_int32<BN>(p, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
     }
   }
 
