@@ -51,8 +51,10 @@ struct GemmParams {
 // out[i] = bf16(sum_s ws[s * stride + i]), s ascending.
 int launch_split_reduce(const float* ws, long long stride, int splits, long long n, void* out, cudaStream_t st);
 
+// cta_pair: pairs of CTAs compute 256 x 256 tiles (dense, unswapped, bn = 256, even grid; p.num_p_tiles counts
+// 256-row tiles and tmQ has 128-row boxes).
 int launch_w4a4_gemm(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int bn, int grid,
-                     cudaStream_t st);
+                     bool cta_pair, cudaStream_t st);
 
 // Builds (or fetches from a small per-device cache) a tensor map over packed int4 data.
 // rowmajor: 2-D view [rows, row_bytes]; otherwise 3-D view [slabs, rows, 64].

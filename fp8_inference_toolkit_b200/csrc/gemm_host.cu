@@ -8,6 +8,7 @@ namespace i4tc {
 static int g_force_bn = 0;    // 0 = choose automatically
 static int g_force_swap = -1; // -1 = choose automatically
 static int g_force_splits = 0; // 0 = choose automatically, 1 = never split, n = n K ranges
+static int g_cta_pairs = -1;   // -1 = choose automatically, 0 = never, 1 = whenever the problem allows it
 
 struct Shape {
   int bn;
@@ -132,13 +133,34 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
     }
   }
 
+  // CTA pairs (256 x 256 tiles on two SMs): each SM converts and stages a third less per unit of MMA work.
+  // Worth it once the 256-row tiles fill the SM pairs about as well as the 128-row tiles fill the SMs.
+  bool pair = false;
+  const int clusters_max = info->sm_count / 2;
+  const long long pair_tiles = ((prow + 255) / 256) * p.num_q_tiles;
+  if (!sh.swap && sh.bn == 256 && p.splits == 1 && clusters_max > 0 &&
+      (d.epi_mode == EPI_CHANNEL || d.epi_mode == EPI_GROUP)) {
+    const double eff1 = (double)tiles / (double)(((tiles + info->sm_count - 1) / info->sm_count) * info->sm_count);
+    const double eff2 = (double)pair_tiles / (double)(((pair_tiles + clusters_max - 1) / clusters_max) * clusters_max);
+    // measured: +18-21 % for the one-flush per-channel epilogue; the per-group epilogue (which bounds that mode)
+    // gains nothing from it, so it stays on single CTAs unless forced
+    pair = d.epi_mode == EPI_CHANNEL && prow >= 512 && eff2 >= 0.9 * eff1;
+    if (g_cta_pairs == 0) pair = false;
+    if (g_cta_pairs == 1) pair = true;
+  }
   CUtensorMap tmP, tmQ;
   const long long extent = d.rowmajor ? d.K / 2 : (long long)d.G;
   if (int rc = get_tensor_map(device, pbase, d.rowmajor, prow, extent, 128, &tmP)) return rc;
-  if (int rc = get_tensor_map(device, qbase, d.rowmajor, qrow, extent, sh.bn, &tmQ)) return rc;
-  const long long items = tiles * p.splits;
-  const int grid = (int)(items < info->sm_count ? items : info->sm_count);
-  if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, static_cast<cudaStream_t>(stream))) return rc;
+  if (int rc = get_tensor_map(device, qbase, d.rowmajor, qrow, extent, pair ? 128 : sh.bn, &tmQ)) return rc;
+  int grid;
+  if (pair) {
+    p.num_p_tiles = (int)((prow + 255) / 256);
+    grid = 2 * (int)(pair_tiles < clusters_max ? pair_tiles : clusters_max);
+  } else {
+    const long long items = tiles * p.splits;
+    grid = (int)(items < info->sm_count ? items : info->sm_count);
+  }
+  if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, pair, static_cast<cudaStream_t>(stream))) return rc;
   if (p.splits > 1)
     return launch_split_reduce(p.split_ws, p.ws_stride, p.splits, d.M * d.N, d.out, static_cast<cudaStream_t>(stream));
   return I4TC_OK;
@@ -167,6 +189,12 @@ extern "C" int i4tc_set_tuning(int tile_n, int swap) {
 extern "C" int i4tc_set_split_k(int splits) {
   I4TC_REQUIRE(splits >= 0 && splits <= 8, I4TC_EINVAL, "splits must be 0 (automatic) or 1..8");
   g_force_splits = splits;
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_set_cta_pairs(int mode) {
+  I4TC_REQUIRE(mode >= -1 && mode <= 1, I4TC_EINVAL, "mode must be -1 (automatic), 0 or 1");
+  g_cta_pairs = mode;
   return I4TC_OK;
 }
 
@@ -261,5 +289,5 @@ extern "C" int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, con
   // upper bound on tiles: every expert may add one partial row tile
   const long long max_tiles = ((num_pairs + 127) / 128 + num_experts) * p.num_q_tiles;
   const int grid = (int)(max_tiles < info->sm_count ? max_tiles : info->sm_count);
-  return launch_w4a4_gemm(p, tmP, tmQ, bn, grid, static_cast<cudaStream_t>(stream));
+  return launch_w4a4_gemm(p, tmP, tmQ, bn, grid, false, static_cast<cudaStream_t>(stream));
 }

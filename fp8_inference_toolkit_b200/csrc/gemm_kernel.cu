@@ -34,25 +34,29 @@ constexpr int kI8Row = 128;          // bytes of one int8 row of one group (the 
 constexpr int kThreads = 512;
 constexpr int kConvWarp0 = 4, kConvWarps = 4;
 constexpr int kEpiWarp0 = 8, kEpiWarps = 8;
-constexpr int kNI = 2;               // int8 stages
 constexpr int kNS = 4;               // scale stages (per-group epilogue)
 constexpr int kScaleWarp0 = 2, kScaleWarps = 2;
 // register budgets per role (whole warpgroups): 128*56 + 128*72 + 256*192 = 65536
 constexpr int kRegsWg0 = 56, kRegsConv = 72, kRegsEpi = 192;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
-template <int BN>
+// CG = 1: one CTA computes a 128 x BN tile.  CG = 2: a pair of CTAs (a cluster of two SMs) computes a
+// 256 x BN tile with tcgen05.mma.cta_group::2; each CTA stages its own 128 P rows and only BN / 2 rows of
+// the Q operand, so a third less is converted and moved through shared memory per unit of MMA work.
+template <int BN, int CG = 1>
 struct Cfg {
-  static constexpr int NP = (BN >= 256) ? 5 : 6;                       // packed stages
+  static constexpr int QR = BN / CG;                                   // Q rows staged by this CTA
+  static constexpr int NP = (CG == 2) ? 4 : ((BN >= 256) ? 5 : 6);     // packed stages
+  static constexpr int NI = (CG == 2) ? 4 : 2;                         // int8 stages
   static constexpr int PK_P = kBM * kPackedRow;                        // 8 KB
-  static constexpr int PK_Q = BN * kPackedRow;
+  static constexpr int PK_Q = QR * kPackedRow;
   static constexpr int I8_P = kBM * kI8Row;                            // 16 KB
-  static constexpr int I8_Q = BN * kI8Row;
+  static constexpr int I8_Q = QR * kI8Row;
   static constexpr int COLS_PER_WARP = BN / 2;                         // epilogue columns per thread
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;        // power of two for BN in {16..256}
   // shared memory layout (offsets from a 1024-byte aligned base)
   static constexpr int OFF_I8 = 0;
-  static constexpr int OFF_PK = OFF_I8 + kNI * (I8_P + I8_Q);
+  static constexpr int OFF_PK = OFF_I8 + NI * (I8_P + I8_Q);
   // scale stages of the per-group epilogue: kBM row scales then BN column scales of one K group;
   // the one-flush epilogues use the start of the same region for their per-warp column scales
   static constexpr int OFF_SQ = OFF_PK + NP * (PK_P + PK_Q);
@@ -60,7 +64,7 @@ struct Cfg {
   static constexpr int SQ_BYTES = (kNS * SCALE_STAGE > kEpiWarps * 2 * COLS_PER_WARP * 4) ? kNS * SCALE_STAGE
                                                                                           : kEpiWarps * 2 * COLS_PER_WARP * 4;
   static constexpr int OFF_BAR = OFF_SQ + SQ_BYTES;
-  static constexpr int NUM_BARS = 2 * NP + 2 * kNI + 4 + 2 * kNS;
+  static constexpr int NUM_BARS = 2 * NP + 2 * NI + 4 + 2 * kNS;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // tmem ptr, abort flag
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;              // + alignment slack
 };
@@ -76,11 +80,15 @@ struct TileInfo {
 
 // Static persistent schedule: CTA b takes tiles b, b + grid, ...  P tiles vary fastest so that
 // CTAs running together share Q (weight) tiles in L2.
-struct Sched {
+// With CG = 2 a work item is a 256-row P tile of a CTA pair; rank r of the pair owns rows 128 r .. 128 r + 127
+// of it (p.num_p_tiles then counts 256-row tiles).
+template <int CG = 1>
+struct SchedT {
   int tile;
   int e;
   int tile_base;
-  __device__ Sched() : tile(blockIdx.x), e(0), tile_base(0) {}
+  int rank;
+  __device__ SchedT() : tile(blockIdx.x / CG), e(0), tile_base(0), rank(CG == 2 ? (int)cluster_ctarank() : 0) {}
   template <int BN>
   __device__ bool next(const GemmParams& p, TileInfo& ti) {
     if (p.expert_offsets == nullptr) {
@@ -88,7 +96,7 @@ struct Sched {
       if (tile >= per_split * p.splits) return false;
       const int sp = tile / per_split, local = tile - sp * per_split;
       const int pt = local % p.num_p_tiles, qt = local / p.num_p_tiles;
-      ti.p0 = pt * kBM; ti.q0 = qt * BN; ti.p_lim = p.P_rows; ti.q_lim = p.Q_rows; ti.zq = 0; ti.sq_off = 0;
+      ti.p0 = pt * (kBM * CG) + rank * kBM; ti.q0 = qt * BN; ti.p_lim = p.P_rows; ti.q_lim = p.Q_rows; ti.zq = 0; ti.sq_off = 0;
       ti.split = sp; ti.g0 = sp * p.groups_per_split;
       ti.g1 = min(p.G, ti.g0 + p.groups_per_split);
     } else {
@@ -108,10 +116,11 @@ struct Sched {
         tile_base += nt; ++e;
       }
     }
-    tile += gridDim.x;
+    tile += gridDim.x / CG;
     return true;
   }
 };
+using Sched = SchedT<1>;
 
 // Bounded mbarrier wait, uniform across the warp.  Returns false (and raises the abort flag)
 // when the limit expires or another role has already aborted.  The common case -- the phase has
@@ -139,6 +148,13 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   return wait_bar_slow(bar, parity, abort_flag);
 }
 
+// Arrival on a barrier that, for CG = 2, may live in the peer CTA (`bar` is then a shared::cluster address).
+template <int CG>
+__device__ __forceinline__ void arrive_bar(uint32_t bar) {
+  if (CG == 2) mbar_arrive_cluster(bar);
+  else mbar_arrive(bar);
+}
+
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
   // K-major, 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart (SBO), LBO unused (1),
   // descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
@@ -150,10 +166,10 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
   return d;
 }
 
-template <int BN>
+template <int BN, int CG>
 __device__ __forceinline__ constexpr uint32_t make_idesc() {
   // D = S32 (2 << 4), A = B = signed int8 (1 << 7, 1 << 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
-  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((kBM * CG) >> 4) << 24);
 }
 
 // Expand one packed tile (rows x 64 B, dense) into a swizzled int8 tile (rows x 128 B).
@@ -282,11 +298,12 @@ __device__ __forceinline__ void store_pair(OutT* out, long long ldc, int prow, i
 // Scales.  Two otherwise idle warps copy the kBM row scales and BN column scales of each K group from
 // global to shared memory (4-byte cp.async, kNS stages ahead, completion signalled on an mbarrier), so the
 // epilogue warps spend no instructions or registers on global addresses.
-template <int BN, typename OutT, bool SWAP>
+template <int BN, typename OutT, bool SWAP, int CG>
 __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
-                                               uint32_t bar_tm_full, uint32_t bar_tm_empty, uint32_t bar_sc_empty,
+                                               uint32_t bar_tm_full, uint32_t bar_tm_empty, uint32_t bar_sc_full,
+                                               uint32_t bar_sc_empty,
                                                volatile int* abort_flag) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CG>;
   constexpr int CW = C::COLS_PER_WARP;
   constexpr int NCH = CW / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -301,19 +318,24 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
   constexpr bool pq_order = !SWAP;
   constexpr float kInv256 = 1.0f / 256.0f;
 
-  Sched sched;
+  SchedT<CG> sched;
   TileInfo ti;
   uint32_t flush = 0;
-  while (sched.next<BN>(p, ti)) {
+  while (sched.template next<BN>(p, ti)) {
     float2 f[CW / 2];   // [a][c][kk]: row 8a + lr, columns c * 32 + kk * 8 + 2 lq + {0, 1}
 #pragma unroll
     for (int i = 0; i < CW / 2; ++i) f[i] = make_float2(0.f, 0.f);
     bool ok = true;
     for (int g = ti.g0; g < ti.g1; ++g) {
-      // the MMA warp waited for this scale stage before it issued the group, so an accumulator that is
-      // full implies scales that have landed
+      // CG = 1: the MMA warp waited for this scale stage before it issued the group, so an accumulator
+      // that is full implies scales that have landed
       const uint32_t ss = flush % kNS;
       const uint32_t buf = flush & 1u;
+      if (CG == 2) {
+        // in a CTA pair only the leader issues MMAs, so each CTA checks its own scale stage
+        ok = wait_bar(bar_sc_full + ss * 8, (flush / kNS) & 1u, abort_flag);
+        if (!ok) break;
+      }
       ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
@@ -336,7 +358,7 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
           // all of this warp's part of the buffer is in registers: hand it back to the MMA warp
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_tm_empty + buf * 8);
+          if (lane == 0) arrive_bar<CG>(bar_tm_empty + buf * 8);
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
@@ -412,11 +434,11 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
 
 // One flush per tile with per-channel scales: out = cast((acc * scale_b[n]) * scale_a[m]), the
 // reference's order.  Same slab register layout and quad-transposed stores as the per-group epilogue.
-template <int BN, typename OutT, bool SWAP>
+template <int BN, typename OutT, bool SWAP, int CG>
 __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
                                                  uint32_t bar_tm_full, uint32_t bar_tm_empty,
                                                  volatile int* abort_flag) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CG>;
   constexpr int CW = C::COLS_PER_WARP;
   constexpr int NCH = CW / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -432,11 +454,11 @@ __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* s
   constexpr bool q_first = !SWAP;
   OutT* out = static_cast<OutT*>(p.out);
 
-  Sched sched;
+  SchedT<CG> sched;
   TileInfo ti;
   uint32_t flush = 0;
   bool ok = true;
-  while (ok && sched.next<BN>(p, ti)) {
+  while (ok && sched.template next<BN>(p, ti)) {
     __syncwarp();  // the previous tile's reads of sq_s are done
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
@@ -469,7 +491,7 @@ __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* s
       if (u == 2 * NCH - 1) {
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tm_empty + buf * 8);
+        if (lane == 0) arrive_bar<CG>(bar_tm_empty + buf * 8);
       }
       float2 v[2][4];
 #pragma unroll
@@ -525,7 +547,7 @@ __device__ __forceinline__ void epilogue_int32(const GemmParams& p, uint32_t tme
   TileInfo ti;
   uint32_t flush = 0;
   bool ok = true;
-  while (ok && sched.next<BN>(p, ti)) {
+  while (ok && sched.template next<BN>(p, ti)) {
     const int prow = ti.p0 + quad * 32 + lane;
     const int nflush = per_group ? (ti.g1 - ti.g0) : 1;
     for (int fl = 0; fl < nflush; ++fl) {
@@ -555,32 +577,38 @@ __device__ __forceinline__ void epilogue_int32(const GemmParams& p, uint32_t tme
 // ------------------------------------------------------------------------------------------
 // The kernel
 // ------------------------------------------------------------------------------------------
-template <int BN>
+template <int BN, int CG>
 __global__ void __launch_bounds__(kThreads, 1)
 w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmP,
                  const __grid_constant__ CUtensorMap tmQ) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CG>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // CTA pair: rank 0 (the leader) issues the MMAs for both CTAs and owns the barriers both CTAs arrive on
+  const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
 
   const uint32_t bar0 = sbase + C::OFF_BAR;
   const uint32_t bar_pk_full = bar0;
   const uint32_t bar_pk_empty = bar_pk_full + C::NP * 8;
   const uint32_t bar_i8_full = bar_pk_empty + C::NP * 8;
-  const uint32_t bar_i8_empty = bar_i8_full + kNI * 8;
-  const uint32_t bar_tm_full = bar_i8_empty + kNI * 8;
+  const uint32_t bar_i8_empty = bar_i8_full + C::NI * 8;
+  const uint32_t bar_tm_full = bar_i8_empty + C::NI * 8;
   const uint32_t bar_tm_empty = bar_tm_full + 2 * 8;
   const uint32_t bar_sc_full = bar_tm_empty + 2 * 8;
   const uint32_t bar_sc_empty = bar_sc_full + kNS * 8;
+  // where converters and epilogue warps arrive: the leader's barriers (shared::cluster addresses for CG = 2)
+  const uint32_t arr_i8_full = (CG == 2) ? mapa_shared(bar_i8_full, 0) : bar_i8_full;
+  const uint32_t arr_tm_empty = (CG == 2) ? mapa_shared(bar_tm_empty, 0) : bar_tm_empty;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 8);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::NP; ++i) { mbar_init(bar_pk_full + i * 8, 1); mbar_init(bar_pk_empty + i * 8, kConvWarps); }
-    for (int i = 0; i < kNI; ++i) { mbar_init(bar_i8_full + i * 8, kConvWarps); mbar_init(bar_i8_empty + i * 8, 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_tm_full + i * 8, 1); mbar_init(bar_tm_empty + i * 8, kEpiWarps); }
+    for (int i = 0; i < C::NI; ++i) { mbar_init(bar_i8_full + i * 8, kConvWarps * CG); mbar_init(bar_i8_empty + i * 8, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_tm_full + i * 8, 1); mbar_init(bar_tm_empty + i * 8, kEpiWarps * CG); }
     for (int i = 0; i < kNS; ++i) { mbar_init(bar_sc_full + i * 8, 32); mbar_init(bar_sc_empty + i * 8, kEpiWarps); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -588,11 +616,12 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     prefetch_tensormap(&tmQ);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
-    tmem_relinquish();
+    if (CG == 2) { tmem_alloc_cg2(smem_u32(tmem_slot), C::TMEM_COLS); tmem_relinquish_cg2(); }
+    else { tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS); tmem_relinquish(); }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if (CG == 2) cluster_sync();   // the peer's barriers are initialised before anything arrives on them
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -606,11 +635,11 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   setmaxnreg_dec<kRegsWg0>();
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    Sched sched;
+    SchedT<CG> sched;
     TileInfo ti;
     uint32_t it = 0;
     bool ok = true;
-    while (ok && sched.next<BN>(p, ti)) {
+    while (ok && sched.template next<BN>(p, ti)) {
       for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         const uint32_t s = it % C::NP, ph = (it / C::NP) & 1u;
         ok = wait_bar(bar_pk_empty + s * 8, ph ^ 1u, abort_flag);
@@ -622,8 +651,9 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
           mbar_arrive_expect_tx(full, C::PK_P + C::PK_Q);
           if (p.p_rowmajor) tma_load_2d(dstP, &tmP, full, g * kPackedRow, ti.p0);
           else tma_load_3d(dstP, &tmP, full, 0, ti.p0, g);
-          if (p.q_rowmajor) tma_load_2d(dstQ, &tmQ, full, g * kPackedRow, ti.q0);
-          else tma_load_3d(dstQ, &tmQ, full, 0, ti.q0, ti.zq + g);
+          const int qrow = ti.q0 + (int)rank * C::QR;   // CG = 2: this CTA stages half of the Q tile
+          if (p.q_rowmajor) tma_load_2d(dstQ, &tmQ, full, g * kPackedRow, qrow);
+          else tma_load_3d(dstQ, &tmQ, full, 0, qrow, ti.zq + g);
         }
         __syncwarp();
       }
@@ -639,13 +669,16 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    constexpr uint32_t idesc = make_idesc<BN>();
-    Sched sched;
+    // ---------------- MMA issuer (CG = 2: the leader CTA only) ----------------
+    if (leader) {
+    constexpr uint32_t idesc = make_idesc<BN, CG>();
+    const uint32_t peer_i8_empty = (CG == 2) ? mapa_shared(bar_i8_empty, 1) : 0u;
+    const uint32_t peer_tm_full = (CG == 2) ? mapa_shared(bar_tm_full, 1) : 0u;
+    SchedT<CG> sched;
     TileInfo ti;
     uint32_t it = 0, flush = 0;
     bool ok = true;
-    while (ok && sched.next<BN>(p, ti)) {
+    while (ok && sched.template next<BN>(p, ti)) {
       for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         const bool first = per_group_flush || g == ti.g0;
         const bool last = per_group_flush || g == ti.g1 - 1;
@@ -654,10 +687,10 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
           ok = wait_bar(bar_tm_empty + buf * 8, ((flush >> 1) & 1u) ^ 1u, abort_flag);
           if (!ok) break;
         }
-        const uint32_t s = it % kNI, ph = (it / kNI) & 1u;
+        const uint32_t s = it % C::NI, ph = (it / C::NI) & 1u;
         ok = wait_bar(bar_i8_full + s * 8, ph, abort_flag);
         if (!ok) break;
-        if (p.epi_mode == EPI_GROUP) {
+        if (CG == 1 && p.epi_mode == EPI_GROUP) {
           ok = wait_bar(bar_sc_full + (flush % kNS) * 8, (flush / kNS) & 1u, abort_flag);
           if (!ok) break;
         }
@@ -670,23 +703,32 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // 32 bytes of K per MMA: advance the start-address field by 32 >> 4
-            mma_i8(d_tmem, dP + (uint64_t)(2 * k), dQ + (uint64_t)(2 * k), idesc, (first && k == 0) ? 0u : 1u);
+            if (CG == 2) mma_i8_cg2(d_tmem, dP + (uint64_t)(2 * k), dQ + (uint64_t)(2 * k), idesc, (first && k == 0) ? 0u : 1u);
+            else mma_i8(d_tmem, dP + (uint64_t)(2 * k), dQ + (uint64_t)(2 * k), idesc, (first && k == 0) ? 0u : 1u);
           }
-          tc_commit(bar_i8_empty + s * 8);
-          if (last) tc_commit(bar_tm_full + buf * 8);
+          if (CG == 2) {
+            // one arrival per CTA: the stage is free for both converters, the accumulator full for both epilogues
+            tc_commit_cg2(bar_i8_empty + s * 8);
+            tc_commit_cg2(peer_i8_empty + s * 8);
+            if (last) { tc_commit_cg2(bar_tm_full + buf * 8); tc_commit_cg2(peer_tm_full + buf * 8); }
+          } else {
+            tc_commit(bar_i8_empty + s * 8);
+            if (last) tc_commit(bar_tm_full + buf * 8);
+          }
         }
         __syncwarp();
         if (last) ++flush;
       }
     }
+    }
   } else if (p.epi_mode == EPI_GROUP) {
     // ---------------- scale loaders (warps 2 and 3 take alternate K groups) ----------------
     const uint32_t w = (uint32_t)(warp - kScaleWarp0);
-    Sched sched;
+    SchedT<CG> sched;
     TileInfo ti;
     uint32_t it = 0;
     bool ok = true;
-    while (ok && sched.next<BN>(p, ti)) {
+    while (ok && sched.template next<BN>(p, ti)) {
       for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         if ((it % kScaleWarps) != w) continue;
         const uint32_t ss = it % kNS;
@@ -716,14 +758,14 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     // ---------------- converters ----------------
     setmaxnreg_dec<kRegsConv>();
     const int tid = threadIdx.x - kConvWarp0 * 32;
-    Sched sched;
+    SchedT<CG> sched;
     TileInfo ti;
     uint32_t it = 0;
     bool ok = true;
-    while (ok && sched.next<BN>(p, ti)) {
+    while (ok && sched.template next<BN>(p, ti)) {
       for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         const uint32_t sp_ = it % C::NP, php = (it / C::NP) & 1u;
-        const uint32_t si = it % kNI, phi = (it / kNI) & 1u;
+        const uint32_t si = it % C::NI, phi = (it / C::NI) & 1u;
         ok = wait_bar(bar_pk_full + sp_ * 8, php, abort_flag);
         if (!ok) break;
         ok = wait_bar(bar_i8_empty + si * 8, phi ^ 1u, abort_flag);
@@ -731,11 +773,11 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         const uint32_t pkP = sbase + C::OFF_PK + sp_ * (C::PK_P + C::PK_Q);
         const uint32_t i8P = sbase + C::OFF_I8 + si * (C::I8_P + C::I8_Q);
         convert_tile<kBM>(pkP, i8P, tid);
-        convert_tile<BN>(pkP + C::PK_P, i8P + C::I8_P, tid);
+        convert_tile<C::QR>(pkP + C::PK_P, i8P + C::I8_P, tid);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(bar_i8_full + si * 8);
+          arrive_bar<CG>(arr_i8_full + si * 8);
           mbar_arrive(bar_pk_empty + sp_ * 8);
         }
       }
@@ -744,40 +786,61 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     // ---------------- epilogue ----------------
     setmaxnreg_inc<kRegsEpi>();
     if (p.epi_mode == EPI_GROUP) {
-      if (p.swap) epilogue_group<BN, __nv_bfloat16, true>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, bar_sc_empty, abort_flag);
-      else epilogue_group<BN, __nv_bfloat16, false>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, bar_sc_empty, abort_flag);
+      if (p.swap) epilogue_group<BN, __nv_bfloat16, true, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
+      else epilogue_group<BN, __nv_bfloat16, false, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
     } else if (p.epi_mode == EPI_CHANNEL) {
       if (p.out_dtype == I4TC_FP16) {
-        if (p.swap) epilogue_channel<BN, __half, true>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
-        else epilogue_channel<BN, __half, false>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+        if (p.swap) epilogue_channel<BN, __half, true, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        else epilogue_channel<BN, __half, false, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
       } else {
-        if (p.swap) epilogue_channel<BN, __nv_bfloat16, true>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
-        else epilogue_channel<BN, __nv_bfloat16, false>(p, smem, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+        if (p.swap) epilogue_channel<BN, __nv_bfloat16, true, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        else epilogue_channel<BN, __nv_bfloat16, false, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
       }
     } else {
-      epilogue_int32<BN>(p, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);
+      epilogue_int32<BN>(p, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);   // CG = 1 only
     }
   }
 
   // ---------------- teardown ----------------
   tc_fence_before_sync();
-  __syncthreads();
+  if (CG == 2) cluster_sync();   // neither CTA leaves while the other may still read its shared memory or arrive on its barriers
+  else __syncthreads();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+  if (warp == 1) {
+    if (CG == 2) tmem_dealloc_cg2(tmem_base, C::TMEM_COLS);
+    else tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, 1u);
 }
 
-template <int BN>
+template <int BN, int CG>
 static int launch_bn(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int grid, cudaStream_t st) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CG>;
+  static_assert(C::SMEM_BYTES <= 232448, "shared memory layout exceeds the 227 KB a CTA may use");
   static bool configured[64] = {false};
   int dev = 0;
   I4TC_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    I4TC_CUDA(cudaFuncSetAttribute(w4a4_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    I4TC_CUDA(cudaFuncSetAttribute(w4a4_gemm_kernel<BN, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured[dev] = true;
   }
-  w4a4_gemm_kernel<BN><<<grid, kThreads, C::SMEM_BYTES, st>>>(p, tmP, tmQ);
+  if (CG == 1) {
+    w4a4_gemm_kernel<BN, CG><<<grid, kThreads, C::SMEM_BYTES, st>>>(p, tmP, tmQ);
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    I4TC_CUDA(cudaLaunchKernelEx(&cfg, w4a4_gemm_kernel<BN, CG>, p, tmP, tmQ));
+  }
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
 }
@@ -812,11 +875,17 @@ int launch_split_reduce(const float* ws, long long stride, int splits, long long
 }
 
 int launch_w4a4_gemm(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int bn, int grid,
-                     cudaStream_t st) {
+                     bool cta_pair, cudaStream_t st) {
+  if (cta_pair) {
+    I4TC_REQUIRE(bn == 256 && (grid % 2) == 0 && p.expert_offsets == nullptr && !p.swap && p.splits == 1 &&
+                     (p.epi_mode == EPI_CHANNEL || p.epi_mode == EPI_GROUP),
+                 I4TC_EINVAL, "CTA-pair launch needs a dense, unswapped 256-wide problem and an even grid");
+    return launch_bn<256, 2>(p, tmP, tmQ, grid, st);
+  }
   switch (bn) {
-    case 64: return launch_bn<64>(p, tmP, tmQ, grid, st);
-    case 128: return launch_bn<128>(p, tmP, tmQ, grid, st);
-    case 256: return launch_bn<256>(p, tmP, tmQ, grid, st);
+    case 64: return launch_bn<64, 1>(p, tmP, tmQ, grid, st);
+    case 128: return launch_bn<128, 1>(p, tmP, tmQ, grid, st);
+    case 256: return launch_bn<256, 1>(p, tmP, tmQ, grid, st);
     default: return fail(I4TC_EINVAL, "unsupported tile width %d", bn);
   }
 }

@@ -236,6 +236,11 @@ def set_split_k(splits: int = 0) -> None:
     check(lib.i4tc_set_split_k(splits), "set_split_k")
 
 
+def set_cta_pairs(mode: int = -1) -> None:
+    """Force (1) or forbid (0) 256 x 256 tiles on SM pairs for large dense GEMMs (tests); -1 restores automatic."""
+    check(lib.i4tc_set_cta_pairs(mode), "set_cta_pairs")
+
+
 def check_status(device=None) -> None:
     """Raise if any kernel gave up on a bounded wait since the last call (synchronises the stream)."""
     dev = torch.cuda.current_device() if device is None else torch.device(device).index

@@ -63,6 +63,11 @@ int i4tc_set_tuning(int tile_n, int swap);
  * different streams of one device that both split must not overlap. */
 int i4tc_set_split_k(int splits);
 
+/* Test / tuning hook for large dense problems: whether pairs of thread blocks on two SMs share 256 x 256
+ * tiles (-1 = automatic, 0 = never, 1 = whenever the problem allows it: 256-wide tiles, activations on the
+ * row side, scaled outputs).  Process-wide.  Results do not depend on it.  No reference counterpart. */
+int i4tc_set_cta_pairs(int mode);
+
 /* ---- quantise + pack ------------------------------------------------------- */
 
 /* Per-row symmetric int4 quantise + pack, one pass over the input.

@@ -107,6 +107,53 @@ def test_scaled_bit_exact(tc, ops, M, N, K, dtype):
         assert torch.equal(out.cpu(), ref), (tile_n, swap)
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (600, 1000, 1024), (1024, 264, 4096), (257, 256, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_cta_pairs_scaled_bit_exact(tc, ops, M, N, K, dtype):
+    """Per-channel GEMM on SM pairs (256 x 256 tiles, forced on): bit-identical to the oracle, ragged M and N
+    included (a pair's second thread block may own no valid row at all)."""
+    rng = np.random.RandomState(M + N + K + 1)
+    a, b = rand_codes(rng, (M, K)), rand_codes(rng, (N, K))
+    sa = (rng.rand(M).astype(np.float32) + 0.01) * 0.1
+    sb = (rng.rand(N).astype(np.float32) + 0.01) * 0.01
+    ref = torch.from_numpy(O.dequant_per_channel(O.int_gemm(a, b), sa, sb)).to(dtype)
+    try:
+        ops.set_cta_pairs(1)
+        ops.set_tuning(256, 0)
+        out = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+        tc.cutlass_int4_scaled_mm(dev_packed(a), dev_packed(b), dev_f32(sa), dev_f32(sb), out, M, N, K)
+        ops.check_status()
+        assert torch.equal(out.cpu(), ref)
+    finally:
+        ops.set_cta_pairs(-1)
+        ops.set_tuning(0, -1)
+
+
+@pytest.mark.parametrize("M,N,G", [(512, 256, 3), (700, 520, 8), (1024, 1024, 32)])
+def test_cta_pairs_grouped(tc, ops, M, N, G):
+    """Per-group GEMM on SM pairs (forced on) against the oracle, and bit-identical to the single-block path."""
+    rng = np.random.RandomState(M + N + G + 2)
+    a, b = rand_codes(rng, (G, M, 128)), rand_codes(rng, (G, N, 128))
+    sa = (rng.rand(G, M).astype(np.float32) + 0.01) * 0.1
+    sb = (rng.rand(G, N).astype(np.float32) + 0.01) * 0.01
+    ref = O.linear_grouped(a, b, sa, sb)
+    ap, bp = dev_packed(a), dev_packed(b)
+    outs = {}
+    try:
+        ops.set_tuning(256, 0)
+        for mode in (0, 1):
+            ops.set_cta_pairs(mode)
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            tc.cutlass_int4_fused_grouped_gemm(ap, bp, dev_f32(sa), dev_f32(sb), out, M, N, 128, G)
+            ops.check_status()
+            assert_close_bf16(out, ref, f"pairs={mode} {M}x{N}x{G}")
+            outs[mode] = out.cpu()
+    finally:
+        ops.set_cta_pairs(-1)
+        ops.set_tuning(0, -1)
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_config0_end_to_end(tc, ops):
     """x [16,4096] with outlier channels, W [4096,4096]: quantise on the GPU, per-channel linear,
     compare codes, scales and bf16 output with the oracle bit for bit."""
