@@ -56,6 +56,12 @@ int launch_split_reduce(const float* ws, long long stride, int splits, long long
 int launch_w4a4_gemm(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int bn, int grid,
                      bool cta_pair, cudaStream_t st);
 
+// CUDA-core weight-streaming kernel for M <= 8 tokens (per-group or per-channel scales, 16-bit output).
+// x / w are the packed operands in either layout (rowmajor: [rows, G * 64]; else [G, rows, 64]).
+bool gemv_applicable(long long M, long long N, long long K, int epi_mode);
+int launch_w4a4_gemv(const uint8_t* x, const uint8_t* w, const float* sx, const float* sw, void* out, int out_dtype,
+                     long long M, long long N, int G, bool rowmajor, int epi_mode, int sm_count, cudaStream_t st);
+
 // Builds (or fetches from a small per-device cache) a tensor map over packed int4 data.
 // rowmajor: 2-D view [rows, row_bytes]; otherwise 3-D view [slabs, rows, 64].
 int get_tensor_map(int device, const void* base, bool rowmajor, long long rows, long long row_bytes_or_slabs,

@@ -71,6 +71,12 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   I4TC_CUDA(guard.err);
   I4TC_REQUIRE(d.M < (1ll << 31) - 256 && d.N < (1ll << 31) - 256, I4TC_EINVAL, "M or N too large");
 
+  // a handful of tokens: stream the weights through the CUDA cores instead (unless a test pins the tile shape)
+  if (g_force_bn == 0 && g_force_swap < 0 && g_force_splits == 0 &&
+      gemv_applicable(d.M, d.N, (long long)d.G * 128, d.epi_mode) && (!d.rowmajor || d.K == (long long)d.G * 128))
+    return launch_w4a4_gemv(d.a, d.b, d.sa, d.sb, d.out, d.out_dtype, d.M, d.N, d.G, d.rowmajor, d.epi_mode,
+                            info->sm_count, static_cast<cudaStream_t>(stream));
+
   const bool group_mode = d.epi_mode == EPI_GROUP || d.epi_mode == EPI_GROUP_INT32;
   const Shape sh = choose_shape(d.M, d.N, info->sm_count, true, group_mode);
   GemmParams p;
@@ -126,9 +132,9 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
       p.splits = best_s;
       p.groups_per_split = (d.G + best_s - 1) / best_s;
       p.splits = (d.G + p.groups_per_split - 1) / p.groups_per_split;  // no empty range
-      p.ws_stride = d.M * d.N;
+      p.ws_stride = (d.M * d.N + 3) & ~3ll;   // every range starts on a 16-byte boundary
       float* ws = nullptr;
-      if (int rc = split_workspace(device, (size_t)p.splits * d.M * d.N * sizeof(float), &ws)) return rc;
+      if (int rc = split_workspace(device, (size_t)p.splits * p.ws_stride * sizeof(float), &ws)) return rc;
       p.split_ws = ws;
     }
   }

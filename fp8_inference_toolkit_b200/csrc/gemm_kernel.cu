@@ -848,7 +848,10 @@ static int launch_bn(const GemmParams& p, const CUtensorMap& tmP, const CUtensor
 __global__ void __launch_bounds__(256) split_reduce_kernel(const float* __restrict__ ws, long long stride, int splits,
                                                           long long n, __nv_bfloat16* __restrict__ out) {
   const long long i = ((long long)blockIdx.x * 256 + threadIdx.x) * 4;
-  if (i + 3 < n) {
+  // 16-byte loads need every range to start on a 16-byte boundary, the 8-byte store an 8-byte aligned output
+  const bool vec = ((stride & 3) == 0) && ((reinterpret_cast<uintptr_t>(ws) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(out) & 7) == 0);
+  if (vec && i + 3 < n) {
     float4 acc = *reinterpret_cast<const float4*>(ws + i);
     for (int s = 1; s < splits; ++s) {
       const float4 v = *reinterpret_cast<const float4*>(ws + (long long)s * stride + i);
@@ -859,7 +862,7 @@ __global__ void __launch_bounds__(256) split_reduce_kernel(const float* __restri
     pk.h[2] = __float2bfloat16_rn(acc.z); pk.h[3] = __float2bfloat16_rn(acc.w);
     *reinterpret_cast<uint2*>(out + i) = pk.u;
   } else {
-    for (long long j = i; j < n; ++j) {
+    for (long long j = i; j < n && j < i + 4; ++j) {
       float acc = ws[j];
       for (int s = 1; s < splits; ++s) acc += ws[(long long)s * stride + j];
       out[j] = __float2bfloat16_rn(acc);

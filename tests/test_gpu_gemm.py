@@ -154,6 +154,40 @@ def test_cta_pairs_grouped(tc, ops, M, N, G):
     assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 13, 16])
+@pytest.mark.parametrize("N,G", [(100, 3), (4096, 32), (257, 96)])
+def test_small_m_weight_streaming(tc, ops, M, N, G):
+    """A handful of tokens take the CUDA-core weight-streaming kernel (automatic choice): per-channel results are
+    bit-identical to the oracle, per-group results within the tolerance, and both agree with the tensor-core path."""
+    rng = np.random.RandomState(M * 7 + N + G)
+    K = G * 128
+    a, b = rand_codes(rng, (G, M, 128)), rand_codes(rng, (G, N, 128))
+    sa = (rng.rand(G, M).astype(np.float32) + 0.01) * 0.1
+    sb = (rng.rand(G, N).astype(np.float32) + 0.01) * 0.01
+    ref_g = O.linear_grouped(a, b, sa, sb)
+    ar, br = a.transpose(1, 0, 2).reshape(M, K), b.transpose(1, 0, 2).reshape(N, K)
+    ref_c = torch.from_numpy(O.dequant_per_channel(O.int_gemm(ar, br), sa[0], sb[0]))
+    ap, bp, arp, brp = dev_packed(a), dev_packed(b), dev_packed(ar), dev_packed(br)
+    outs = []
+    try:
+        for tile_n, swap in [(0, -1), (64, 1)]:   # automatic (weight streaming), then the tensor-core kernel
+            ops.set_tuning(tile_n, swap)
+            og = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            tc.cutlass_int4_fused_grouped_gemm(ap, bp, dev_f32(sa), dev_f32(sb), og, M, N, 128, G)
+            ops.check_status()
+            assert_close_bf16(og, ref_g, f"grouped M={M} N={N} G={G} tuning={tile_n}")
+            for dtype in (torch.bfloat16, torch.float16):
+                oc = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+                tc.cutlass_int4_scaled_mm(arp, brp, dev_f32(sa[0]), dev_f32(sb[0]), oc, M, N, K)
+                ops.check_status()
+                assert torch.equal(oc.cpu(), ref_c.to(dtype)), (M, N, G, tile_n, dtype)
+            outs.append(og.float().cpu())
+    finally:
+        ops.set_tuning(0, -1)
+    # two summation orders of the same fp32 terms: a couple of bf16 ulps at most
+    assert (outs[0] - outs[1]).abs().max() <= 2e-2 * outs[1].abs().max() + 1e-6
+
+
 def test_config0_end_to_end(tc, ops):
     """x [16,4096] with outlier channels, W [4096,4096]: quantise on the GPU, per-channel linear,
     compare codes, scales and bf16 output with the oracle bit for bit."""
