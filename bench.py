@@ -31,6 +31,7 @@ import torch  # noqa: E402
 
 SHAPES = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 24576), ("down", 12288, 4096)]
 METRIC = "w4a4_gemm_tops_qwen3_8b_shapes_g128"
+METRIC_CHANNEL = "w4a4_gemm_tops_qwen3_8b_shapes_per_channel"
 UNIT = "TOPS"
 GROUP = 128
 
@@ -168,12 +169,13 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
-def workload_config(M: int, n_gpus: int) -> dict:
+def workload_config(M: int, n_gpus: int, per_channel: bool = False) -> dict:
+    scales = "per-token / per-channel" if per_channel else "per-group-128"
     return {
-        "workload": f"BASELINE configs[1]: dense W4A4 per-group-128 linears at Qwen3-8B shapes "
+        "workload": f"BASELINE configs[1]: dense W4A4 {scales} linears at Qwen3-8B shapes "
                     f"(K,N) in (4096,6144),(4096,4096),(4096,24576),(12288,4096), M={M} tokens; "
                     f"step = quantise+pack of the activations then the fused GEMM, for each shape",
-        "M": M, "group_size": GROUP, "n_split": n_gpus,
+        "M": M, "group_size": 0 if per_channel else GROUP, "n_split": n_gpus,
         "l2": "inputs larger than L2 (weights + activations + outputs of one step exceed 126 MB)",
     }
 
@@ -202,6 +204,7 @@ def run_ours(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     M = args.m
     peaks = load_peaks()
+    per_channel = args.scales == "channel"
 
     # ---- inputs resident in HBM: activations per shape, this rank's column slice of the weights
     layers, xs_dev = [], []
@@ -209,7 +212,7 @@ def run_ours(args) -> None:
         assert N % world == 0
         n_loc = N // world
         w = synthetic.weights(N, K, seed=1 + i)[rank * n_loc:(rank + 1) * n_loc].to(dev)
-        lin = W4A4Linear(K, n_loc, per_channel=False, device=dev)
+        lin = W4A4Linear(K, n_loc, per_channel=per_channel, device=dev)
         lin.weight.data.copy_(w)
         lin.quantize_()
         layers.append(lin)
@@ -221,12 +224,15 @@ def run_ours(args) -> None:
     def step(events=None):
         for i, (name, K, N) in enumerate(SHAPES):
             lin = layers[i]
-            xp, xsc = tc.dynamic_int4_quant_grouped(xs_dev[i], GROUP)
+            xp, xsc = tc.dynamic_int4_quant(xs_dev[i]) if per_channel else tc.dynamic_int4_quant_grouped(xs_dev[i], GROUP)
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            tc.cutlass_int4_fused_grouped_gemm(xp, lin.weight_int4, xsc, lin.weight_scale, outs[i], M,
-                                               lin.out_features, GROUP, K // GROUP)
+            if per_channel:
+                tc.cutlass_int4_scaled_mm(xp, lin.weight_int4, xsc, lin.weight_scale, outs[i], M, lin.out_features, K)
+            else:
+                tc.cutlass_int4_fused_grouped_gemm(xp, lin.weight_int4, xsc, lin.weight_scale, outs[i], M,
+                                                   lin.out_features, GROUP, K // GROUP)
             if events is not None:
                 e1.record()
                 events.append((i, e0, e1))
@@ -333,10 +339,10 @@ def run_ours(args) -> None:
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "metric": METRIC_CHANNEL if per_channel else METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "s4*s4->s32, f32 dequant", "data": "synthetic",
-            "config": workload_config(M, world), "clocks": clocks,
+            "config": workload_config(M, world, per_channel), "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h * 1,
                     "ms_per_step": e2e_s * 1e3},
             "gpu_launches": args.steps * 2 * len(SHAPES),
@@ -347,7 +353,8 @@ def run_ours(args) -> None:
                 # bf16 output is written back after the kernel ends, so a launch moves its algorithmic bytes
                 "traffic": sum(gemm_bytes(M, N // world, K) for _, K, N in SHAPES) / len(SHAPES),
                 "traffic_unit": "bytes per launch (mean of the 4 shapes), algorithmic; ncu-confirmed at M=1024",
-                "kernel": "w4a4_gemm_kernel (per-group-128 epilogue), 4 launches per step",
+                "kernel": ("w4a4_gemm_kernel (per-channel epilogue, 256x256 tiles on SM pairs)" if per_channel
+                           else "w4a4_gemm_kernel (per-group-128 epilogue)") + ", 4 launches per step",
                 "peak_source": f"2 x bf16 burst of MEASURED_PEAKS.json ({peaks['source']}); int8 dense = 2 x bf16 on B200",
                 "per_shape_us": {SHAPES[i][0]: statistics.mean(v) * 1e6 for i, v in per_shape.items()},
             },
@@ -395,7 +402,7 @@ def graph_time(fn_list, iters: int = 3) -> float:
 
 def bench_sweep(dev, peaks) -> list:
     """BASELINE configs[1] sweep, kernel-only: M in {1,16,128,1024,8192} x the four (K,N) shapes, group-128
-    fused GEMM (quantise excluded).  Operands rotate over enough copies to exceed L2 for the HBM-bound sizes."""
+    fused GEMM (quantise excluded), and beside it the per-channel GEMM of the same shape.  Operands rotate over enough copies to exceed L2 for the HBM-bound sizes."""
     import int4_native_tc as tc
     from fp8_inference_toolkit_b200 import synthetic
 
@@ -415,12 +422,22 @@ def bench_sweep(dev, peaks) -> list:
             fns = [(lambda w=w: tc.cutlass_int4_fused_grouped_gemm(xp, w, xsc, wsc, out, M, N, GROUP, G))
                    for _ in range(reps) for w in ws_]
             t = graph_time(fns)
+            del ws_, fns
+            # the same shape with per-channel scales (row-major operands, one dequant per tile)
+            wr_ = [synthetic.random_packed((N, K // 2), 200 + i, dev) for i in range(copies)]
+            xr = synthetic.random_packed((M, K // 2), 8, dev)
+            sa1, sb1 = xsc[0].contiguous(), wsc[0].contiguous()
+            fns = [(lambda w=w: tc.cutlass_int4_scaled_mm(xr, w, sa1, sb1, out, M, N, K))
+                   for _ in range(reps) for w in wr_]
+            tch = graph_time(fns)
+            del wr_, fns
             ops_ = 2.0 * M * N * K
             byts = gemm_bytes(M, N, K)
             out_rows.append({"M": M, "shape": name, "K": K, "N": N, "us": t * 1e6, "tops": ops_ / t / 1e12,
                              "gbs": byts / t / 1e9, "frac_int8_peak": ops_ / t / 1e12 / int8_peak,
-                             "frac_hbm": byts / t / 1e9 / peaks["hbm_gbs"]})
-            del ws_, fns
+                             "frac_hbm": byts / t / 1e9 / peaks["hbm_gbs"],
+                             "per_channel_us": tch * 1e6, "per_channel_tops": ops_ / tch / 1e12,
+                             "per_channel_frac_int8_peak": ops_ / tch / 1e12 / int8_peak})
     return out_rows
 
 
@@ -589,6 +606,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=8192, help="tokens per step")
+    ap.add_argument("--scales", default="group", choices=["group", "channel"],
+                    help="linear workload: per-group-128 scales (the headline) or per-token / per-channel scales")
     args = ap.parse_args()
     if args.workload == "quant":
         run_quant(args)

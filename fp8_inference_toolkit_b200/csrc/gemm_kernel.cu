@@ -18,7 +18,7 @@
 //   warp 1      MMA issuer (one lane) and owner of the TMEM allocation
 //   warps 4-7   converters: packed stage -> 128B-swizzled K-major int8 stage
 //   warps 8-15  epilogue: tcgen05.ld, int32 -> fp32, scales, fp32 accumulation across groups, store
-// Two TMEM accumulators (2 x BN columns) let group g+1 be multiplied while group g is drained.
+// Two to four TMEM accumulators (BN columns each) let later groups be multiplied while one is drained.
 // Every wait is bounded: on expiry the kernel sets bit 0 of the status word, all roles leave
 // their loops, TMEM is released and the kernel returns.
 #include "gemm.cuh"
@@ -47,13 +47,16 @@ template <int BN, int CG = 1>
 struct Cfg {
   static constexpr int QR = BN / CG;                                   // Q rows staged by this CTA
   static constexpr int NP = (CG == 2) ? 4 : ((BN >= 256) ? 5 : 6);     // packed stages
-  static constexpr int NI = (CG == 2) ? 4 : 2;                         // int8 stages
+  static constexpr int NI = (CG == 2) ? 4 : (BN >= 256 ? 2 : (BN >= 128 ? 3 : 4));   // int8 stages
+  // TMEM accumulators: as many as fit in the 512 columns (at most 4), so that narrow tiles -- whose K loop is a
+  // chain of short handshakes -- find a free accumulator and a converted stage without waiting
+  static constexpr int NT = (BN >= 256) ? 2 : 4;
   static constexpr int PK_P = kBM * kPackedRow;                        // 8 KB
   static constexpr int PK_Q = QR * kPackedRow;
   static constexpr int I8_P = kBM * kI8Row;                            // 16 KB
   static constexpr int I8_Q = QR * kI8Row;
   static constexpr int COLS_PER_WARP = BN / 2;                         // epilogue columns per thread
-  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;        // power of two for BN in {16..256}
+  static constexpr int TMEM_COLS = NT * BN;                            // 256 or 512: a power of two >= 32
   // shared memory layout (offsets from a 1024-byte aligned base)
   static constexpr int OFF_I8 = 0;
   static constexpr int OFF_PK = OFF_I8 + NI * (I8_P + I8_Q);
@@ -64,7 +67,7 @@ struct Cfg {
   static constexpr int SQ_BYTES = (kNS * SCALE_STAGE > kEpiWarps * 2 * COLS_PER_WARP * 4) ? kNS * SCALE_STAGE
                                                                                           : kEpiWarps * 2 * COLS_PER_WARP * 4;
   static constexpr int OFF_BAR = OFF_SQ + SQ_BYTES;
-  static constexpr int NUM_BARS = 2 * NP + 2 * NI + 4 + 2 * kNS;
+  static constexpr int NUM_BARS = 2 * NP + 2 * NI + 2 * NT + 2 * kNS;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // tmem ptr, abort flag
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;              // + alignment slack
 };
@@ -330,13 +333,13 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
       // CG = 1: the MMA warp waited for this scale stage before it issued the group, so an accumulator
       // that is full implies scales that have landed
       const uint32_t ss = flush % kNS;
-      const uint32_t buf = flush & 1u;
+      const uint32_t buf = flush % C::NT;
       if (CG == 2) {
         // in a CTA pair only the leader issues MMAs, so each CTA checks its own scale stage
         ok = wait_bar(bar_sc_full + ss * 8, (flush / kNS) & 1u, abort_flag);
         if (!ok) break;
       }
-      ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
+      ok = wait_bar(bar_tm_full + buf * 8, (flush / C::NT) & 1u, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       const float* st_p = sc + ss * (C::SCALE_STAGE / 4) + quad * 32;         // this warp's 32 row scales
@@ -477,8 +480,8 @@ __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* s
     const bool vec_ok = !SWAP && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (ti.q0 + col_base + CW <= ti.q_lim);
     const bool pair_ok = ((p.ldc & 1) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
-    const uint32_t buf = flush & 1u;
-    ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
+    const uint32_t buf = flush % C::NT;
+    ok = wait_bar(bar_tm_full + buf * 8, (flush / C::NT) & 1u, abort_flag);
     if (!ok) break;
     tc_fence_after_sync();
     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
@@ -551,8 +554,8 @@ __device__ __forceinline__ void epilogue_int32(const GemmParams& p, uint32_t tme
     const int prow = ti.p0 + quad * 32 + lane;
     const int nflush = per_group ? (ti.g1 - ti.g0) : 1;
     for (int fl = 0; fl < nflush; ++fl) {
-      const uint32_t buf = flush & 1u;
-      ok = wait_bar(bar_tm_full + buf * 8, (flush >> 1) & 1u, abort_flag);
+      const uint32_t buf = flush % C::NT;
+      ok = wait_bar(bar_tm_full + buf * 8, (flush / C::NT) & 1u, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
@@ -596,8 +599,8 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   const uint32_t bar_i8_full = bar_pk_empty + C::NP * 8;
   const uint32_t bar_i8_empty = bar_i8_full + C::NI * 8;
   const uint32_t bar_tm_full = bar_i8_empty + C::NI * 8;
-  const uint32_t bar_tm_empty = bar_tm_full + 2 * 8;
-  const uint32_t bar_sc_full = bar_tm_empty + 2 * 8;
+  const uint32_t bar_tm_empty = bar_tm_full + C::NT * 8;
+  const uint32_t bar_sc_full = bar_tm_empty + C::NT * 8;
   const uint32_t bar_sc_empty = bar_sc_full + kNS * 8;
   // where converters and epilogue warps arrive: the leader's barriers (shared::cluster addresses for CG = 2)
   const uint32_t arr_i8_full = (CG == 2) ? mapa_shared(bar_i8_full, 0) : bar_i8_full;
@@ -608,7 +611,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::NP; ++i) { mbar_init(bar_pk_full + i * 8, 1); mbar_init(bar_pk_empty + i * 8, kConvWarps); }
     for (int i = 0; i < C::NI; ++i) { mbar_init(bar_i8_full + i * 8, kConvWarps * CG); mbar_init(bar_i8_empty + i * 8, 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_tm_full + i * 8, 1); mbar_init(bar_tm_empty + i * 8, kEpiWarps * CG); }
+    for (int i = 0; i < C::NT; ++i) { mbar_init(bar_tm_full + i * 8, 1); mbar_init(bar_tm_empty + i * 8, kEpiWarps * CG); }
     for (int i = 0; i < kNS; ++i) { mbar_init(bar_sc_full + i * 8, 32); mbar_init(bar_sc_empty + i * 8, kEpiWarps); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -682,9 +685,9 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
       for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         const bool first = per_group_flush || g == ti.g0;
         const bool last = per_group_flush || g == ti.g1 - 1;
-        const uint32_t buf = flush & 1u;
+        const uint32_t buf = flush % C::NT;
         if (first) {
-          ok = wait_bar(bar_tm_empty + buf * 8, ((flush >> 1) & 1u) ^ 1u, abort_flag);
+          ok = wait_bar(bar_tm_empty + buf * 8, ((flush / C::NT) & 1u) ^ 1u, abort_flag);
           if (!ok) break;
         }
         const uint32_t s = it % C::NI, ph = (it / C::NI) & 1u;
