@@ -148,9 +148,8 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
       (d.epi_mode == EPI_CHANNEL || d.epi_mode == EPI_GROUP)) {
     const double eff1 = (double)tiles / (double)(((tiles + info->sm_count - 1) / info->sm_count) * info->sm_count);
     const double eff2 = (double)pair_tiles / (double)(((pair_tiles + clusters_max - 1) / clusters_max) * clusters_max);
-    // measured: +18-21 % for the one-flush per-channel epilogue; the per-group epilogue (which bounds that mode)
-    // gains nothing from it, so it stays on single CTAs unless forced
-    pair = d.epi_mode == EPI_CHANNEL && prow >= 512 && eff2 >= 0.9 * eff1;
+    // measured at M = 8192: +18-21 % with the one-flush per-channel epilogue, +4-5 % with the per-group one
+    pair = prow >= 512 && eff2 >= 0.9 * eff1;
     if (g_cta_pairs == 0) pair = false;
     if (g_cta_pairs == 1) pair = true;
   }

@@ -67,7 +67,7 @@ struct Cfg {
   static constexpr int SQ_BYTES = (kNS * SCALE_STAGE > kEpiWarps * 2 * COLS_PER_WARP * 4) ? kNS * SCALE_STAGE
                                                                                           : kEpiWarps * 2 * COLS_PER_WARP * 4;
   static constexpr int OFF_BAR = OFF_SQ + SQ_BYTES;
-  static constexpr int NUM_BARS = 2 * NP + 2 * NI + 2 * NT + 2 * kNS;
+  static constexpr int NUM_BARS = 2 * NP + 2 * NI + 2 * NT + 3 * kNS;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // tmem ptr, abort flag
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;              // + alignment slack
 };
@@ -303,8 +303,7 @@ __device__ __forceinline__ void store_pair(OutT* out, long long ldc, int prow, i
 // epilogue warps spend no instructions or registers on global addresses.
 template <int BN, typename OutT, bool SWAP, int CG>
 __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
-                                               uint32_t bar_tm_full, uint32_t bar_tm_empty, uint32_t bar_sc_full,
-                                               uint32_t bar_sc_empty,
+                                               uint32_t bar_tm_full, uint32_t bar_tm_empty, uint32_t bar_sc_empty,
                                                volatile int* abort_flag) {
   using C = Cfg<BN, CG>;
   constexpr int CW = C::COLS_PER_WARP;
@@ -330,15 +329,10 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
     for (int i = 0; i < CW / 2; ++i) f[i] = make_float2(0.f, 0.f);
     bool ok = true;
     for (int g = ti.g0; g < ti.g1; ++g) {
-      // CG = 1: the MMA warp waited for this scale stage before it issued the group, so an accumulator
-      // that is full implies scales that have landed
+      // the MMA warp waited for this scale stage (in a CTA pair: for both CTAs' stages) before it issued the
+      // group, so an accumulator that is full implies scales that have landed
       const uint32_t ss = flush % kNS;
       const uint32_t buf = flush % C::NT;
-      if (CG == 2) {
-        // in a CTA pair only the leader issues MMAs, so each CTA checks its own scale stage
-        ok = wait_bar(bar_sc_full + ss * 8, (flush / kNS) & 1u, abort_flag);
-        if (!ok) break;
-      }
       ok = wait_bar(bar_tm_full + buf * 8, (flush / C::NT) & 1u, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
@@ -602,6 +596,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   const uint32_t bar_tm_empty = bar_tm_full + C::NT * 8;
   const uint32_t bar_sc_full = bar_tm_empty + C::NT * 8;
   const uint32_t bar_sc_empty = bar_sc_full + kNS * 8;
+  const uint32_t bar_sc_peer = bar_sc_empty + kNS * 8;   // leader only: the second CTA's scale stage has landed
   // where converters and epilogue warps arrive: the leader's barriers (shared::cluster addresses for CG = 2)
   const uint32_t arr_i8_full = (CG == 2) ? mapa_shared(bar_i8_full, 0) : bar_i8_full;
   const uint32_t arr_tm_empty = (CG == 2) ? mapa_shared(bar_tm_empty, 0) : bar_tm_empty;
@@ -612,7 +607,9 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     for (int i = 0; i < C::NP; ++i) { mbar_init(bar_pk_full + i * 8, 1); mbar_init(bar_pk_empty + i * 8, kConvWarps); }
     for (int i = 0; i < C::NI; ++i) { mbar_init(bar_i8_full + i * 8, kConvWarps * CG); mbar_init(bar_i8_empty + i * 8, 1); }
     for (int i = 0; i < C::NT; ++i) { mbar_init(bar_tm_full + i * 8, 1); mbar_init(bar_tm_empty + i * 8, kEpiWarps * CG); }
-    for (int i = 0; i < kNS; ++i) { mbar_init(bar_sc_full + i * 8, 32); mbar_init(bar_sc_empty + i * 8, kEpiWarps); }
+    for (int i = 0; i < kNS; ++i) {
+      mbar_init(bar_sc_full + i * 8, 32); mbar_init(bar_sc_empty + i * 8, kEpiWarps); mbar_init(bar_sc_peer + i * 8, 1);
+    }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tmP);
@@ -693,9 +690,13 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         const uint32_t s = it % C::NI, ph = (it / C::NI) & 1u;
         ok = wait_bar(bar_i8_full + s * 8, ph, abort_flag);
         if (!ok) break;
-        if (CG == 1 && p.epi_mode == EPI_GROUP) {
+        if (p.epi_mode == EPI_GROUP) {
           ok = wait_bar(bar_sc_full + (flush % kNS) * 8, (flush / kNS) & 1u, abort_flag);
           if (!ok) break;
+          if (CG == 2) {
+            ok = wait_bar(bar_sc_peer + (flush % kNS) * 8, (flush / kNS) & 1u, abort_flag);
+            if (!ok) break;
+          }
         }
         tc_fence_after_sync();
         if (lane == 0) {
@@ -723,6 +724,22 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         if (last) ++flush;
       }
     }
+    } else if (CG == 2 && p.epi_mode == EPI_GROUP) {
+      // second CTA of a pair: this warp has no MMAs to issue; it tells the leader when a scale stage of this
+      // CTA has landed, so that the leader's "accumulator full" vouches for both CTAs' scales
+      const uint32_t arr_sc_peer = mapa_shared(bar_sc_peer, 0);
+      SchedT<CG> sched;
+      TileInfo ti;
+      uint32_t it = 0;
+      bool ok = true;
+      while (ok && sched.template next<BN>(p, ti)) {
+        for (int g = ti.g0; g < ti.g1; ++g, ++it) {
+          ok = wait_bar(bar_sc_full + (it % kNS) * 8, (it / kNS) & 1u, abort_flag);
+          if (!ok) break;
+          if (lane == 0) mbar_arrive_cluster(arr_sc_peer + (it % kNS) * 8);
+          __syncwarp();
+        }
+      }
     }
   } else if (p.epi_mode == EPI_GROUP) {
     // ---------------- scale loaders (warps 2 and 3 take alternate K groups) ----------------
@@ -789,8 +806,8 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     // ---------------- epilogue ----------------
     setmaxnreg_inc<kRegsEpi>();
     if (p.epi_mode == EPI_GROUP) {
-      if (p.swap) epilogue_group<BN, __nv_bfloat16, true, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
-      else epilogue_group<BN, __nv_bfloat16, false, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
+      if (p.swap) epilogue_group<BN, __nv_bfloat16, true, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, bar_sc_empty, abort_flag);
+      else epilogue_group<BN, __nv_bfloat16, false, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, bar_sc_empty, abort_flag);
     } else if (p.epi_mode == EPI_CHANNEL) {
       if (p.out_dtype == I4TC_FP16) {
         if (p.swap) epilogue_channel<BN, __half, true, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);

@@ -5,7 +5,6 @@ import pytest
 import torch
 
 from oracle import w4a4_oracle as O
-from tests.helpers import assert_close_bf16
 
 pytestmark = pytest.mark.gpu
 
@@ -20,7 +19,7 @@ def test_linear_module_matches_oracle(per_channel):
     x = synthetic.activations(M, K, 4)
     lin = torch.nn.Linear(K, N, bias=True, dtype=torch.bfloat16)
     lin.weight.data.copy_(w)
-    lin.bias.data.normal_(0, 0.1)
+    lin.bias.data.copy_(torch.randn(N, generator=torch.Generator().manual_seed(5)) * 0.1)
     q = W4A4Linear.from_linear(lin.cuda(), per_channel=per_channel)
     assert q.weight is None and q.weight_int4.dtype == torch.uint8
     y = q(x.cuda().view(2, 20, K))
@@ -33,8 +32,13 @@ def test_linear_module_matches_oracle(per_channel):
         xc, xs = O.quant_grouped(x, 128, "activation")
         wc, ws = O.quant_grouped(w, 128, "weight")
         ref = O.linear_grouped(xc, wc, xs, ws)
-    ref = (ref.float() + lin.bias.data.float().cpu()).to(torch.bfloat16)
-    assert_close_bf16(y.view(M, N), ref, "W4A4Linear")
+    # the bias can cancel the product almost completely, so the error is bounded relative to the two addends
+    # (1e-2 of the north star applied to the GEMM output, plus the helper's floor), not to their sum
+    g, bias = ref.float(), lin.bias.data.float().cpu()
+    full = (g + bias).to(torch.bfloat16).float()
+    bound = 1e-2 * (g.abs() + bias.abs()) + 1e-3 * g.abs().max()
+    err = (y.view(M, N).float().cpu() - full).abs()
+    assert (err <= bound).all(), f"W4A4Linear: worst error / bound = {(err / bound).max():.3f}"
     # state_dict round trip keeps the packed weight; no re-quantisation, identical output
     sd = {k: v.cpu() for k, v in q.state_dict().items()}
     assert set(sd) == {"weight_int4", "weight_scale", "bias"}
