@@ -50,6 +50,9 @@ struct GemmParams {
 
 // out[i] = bf16(sum_s ws[s * stride + i]), s ascending.
 int launch_split_reduce(const float* ws, long long stride, int splits, long long n, void* out, cudaStream_t st);
+// out[m, n] = cast((sum_s ws[s * stride + m * N + n] * sb[n]) * sa[m]): the ranges hold exact integer sums.
+int launch_split_reduce_scaled(const float* ws, long long stride, int splits, long long M, long long N, const float* sa,
+                               const float* sb, void* out, int out_dtype, cudaStream_t st);
 
 // cta_pair: pairs of CTAs compute 256 x 256 tiles (dense, unswapped, bn = 256, even grid; p.num_p_tiles counts
 // 256-row tiles and tmQ has 128-row boxes).

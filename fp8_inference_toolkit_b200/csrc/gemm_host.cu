@@ -9,6 +9,7 @@ static int g_force_bn = 0;    // 0 = choose automatically
 static int g_force_swap = -1; // -1 = choose automatically
 static int g_force_splits = 0; // 0 = choose automatically, 1 = never split, n = n K ranges
 static int g_cta_pairs = -1;   // -1 = choose automatically, 0 = never, 1 = whenever the problem allows it
+static bool g_pairs_launchable = true;   // cleared when an automatic cluster launch was refused
 
 struct Shape {
   int bn;
@@ -110,13 +111,14 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   p.num_q_tiles = (int)((qrow + sh.bn - 1) / sh.bn);
   const long long tiles = (long long)p.num_p_tiles * p.num_q_tiles;
   I4TC_REQUIRE(tiles < (1ll << 31), I4TC_EINVAL, "too many tiles");
-  // Split-K for the weight-streaming case (small M, per-group epilogue): a tile's K loop is a serial
+  // Split-K for the weight-streaming case (small M, scaled outputs): a tile's K loop is a serial
   // chain of per-group handshakes, so when there are fewer tiles than SMs -- or an awkward number
-  // of waves -- the groups are cut into ranges handled by different CTAs and the fp32 partial sums
-  // are added afterwards in a fixed order (deterministic).
+  // of waves -- the groups are cut into ranges handled by different CTAs and the partial sums are
+  // added afterwards in a fixed order: fp32 for per-group scales (deterministic), exact integers held
+  // in fp32 for per-channel scales (bit-identical to the unsplit result).
   p.splits = 1;
   p.groups_per_split = d.G;
-  if (d.epi_mode == EPI_GROUP && sh.swap && g_force_splits != 1) {
+  if ((d.epi_mode == EPI_GROUP || d.epi_mode == EPI_CHANNEL) && sh.swap && g_force_splits != 1) {
     // cost in microseconds: waves x groups per range x ~0.65 us per group handshake, plus writing and
     // reading the fp32 partial sums at ~6 TB/s and one more launch
     int best_s = 1;
@@ -153,21 +155,33 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
     if (g_cta_pairs == 0) pair = false;
     if (g_cta_pairs == 1) pair = true;
   }
+  if (pair && g_cta_pairs < 0 && !g_pairs_launchable) pair = false;
   CUtensorMap tmP, tmQ;
   const long long extent = d.rowmajor ? d.K / 2 : (long long)d.G;
   if (int rc = get_tensor_map(device, pbase, d.rowmajor, prow, extent, 128, &tmP)) return rc;
-  if (int rc = get_tensor_map(device, qbase, d.rowmajor, qrow, extent, pair ? 128 : sh.bn, &tmQ)) return rc;
-  int grid;
   if (pair) {
-    p.num_p_tiles = (int)((prow + 255) / 256);
-    grid = 2 * (int)(pair_tiles < clusters_max ? pair_tiles : clusters_max);
-  } else {
-    const long long items = tiles * p.splits;
-    grid = (int)(items < info->sm_count ? items : info->sm_count);
+    if (int rc = get_tensor_map(device, qbase, d.rowmajor, qrow, extent, 128, &tmQ)) return rc;
+    GemmParams pp = p;
+    pp.num_p_tiles = (int)((prow + 255) / 256);
+    const int grid = 2 * (int)(pair_tiles < clusters_max ? pair_tiles : clusters_max);
+    const int rc = launch_w4a4_gemm(pp, tmP, tmQ, sh.bn, grid, true, static_cast<cudaStream_t>(stream));
+    if (rc == I4TC_OK) return I4TC_OK;
+    if (g_cta_pairs == 1) return rc;   // the caller asked for pairs: report why they cannot run
+    // an environment that cannot launch clusters of two (a restricted SM partition, for instance): the launch
+    // was refused before anything ran; remember it and use single thread blocks from now on
+    cudaGetLastError();
+    g_pairs_launchable = false;
   }
-  if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, pair, static_cast<cudaStream_t>(stream))) return rc;
-  if (p.splits > 1)
+  if (int rc = get_tensor_map(device, qbase, d.rowmajor, qrow, extent, sh.bn, &tmQ)) return rc;
+  const long long items = tiles * p.splits;
+  const int grid = (int)(items < info->sm_count ? items : info->sm_count);
+  if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, false, static_cast<cudaStream_t>(stream))) return rc;
+  if (p.splits > 1) {
+    if (d.epi_mode == EPI_CHANNEL)
+      return launch_split_reduce_scaled(p.split_ws, p.ws_stride, p.splits, d.M, d.N, d.sa, d.sb, d.out, d.out_dtype,
+                                        static_cast<cudaStream_t>(stream));
     return launch_split_reduce(p.split_ws, p.ws_stride, p.splits, d.M * d.N, d.out, static_cast<cudaStream_t>(stream));
+  }
   return I4TC_OK;
 }
 

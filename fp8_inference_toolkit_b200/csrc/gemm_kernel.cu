@@ -490,6 +490,30 @@ __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* s
         __syncwarp();
         if (lane == 0) arrive_bar<CG>(bar_tm_empty + buf * 8);
       }
+      if (p.split_ws != nullptr) {
+        // split-K: this work item covers a range of K groups; its integer sums go out as fp32 (exact: below
+        // 2^24), element (m, n) at ws[split][m * ldc + n], and a second kernel adds the ranges and scales
+        float* ws = p.split_ws + (long long)ti.split * p.ws_stride;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int prow = ti.p0 + quad * 32 + 8 * (sl * 2 + h) + lr;
+          if (prow >= ti.p_lim) continue;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const int q = ti.q0 + col_base + c * 32 + kk * 8 + lq * 2;
+            const float d0 = __int2float_rn((int32_t)r[4 * kk + 2 * h]) * kInv256;
+            const float d1 = __int2float_rn((int32_t)r[4 * kk + 2 * h + 1]) * kInv256;
+            if (!SWAP) {
+              if (q < ti.q_lim) ws[(long long)prow * p.ldc + q] = d0;
+              if (q + 1 < ti.q_lim) ws[(long long)prow * p.ldc + q + 1] = d1;
+            } else {
+              if (q < ti.q_lim) ws[(long long)q * p.ldc + prow] = d0;
+              if (q + 1 < ti.q_lim) ws[(long long)(q + 1) * p.ldc + prow] = d1;
+            }
+          }
+        }
+        continue;
+      }
       float2 v[2][4];
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
@@ -888,6 +912,31 @@ __global__ void __launch_bounds__(256) split_reduce_kernel(const float* __restri
       out[j] = __float2bfloat16_rn(acc);
     }
   }
+}
+
+// Per-channel variant: the ranges hold exact integer sums; out[m, n] = cast((sum * scale_b[n]) * scale_a[m]).
+template <typename OutT>
+__global__ void __launch_bounds__(256) split_reduce_scaled_kernel(const float* __restrict__ ws, long long stride, int splits,
+                                                                 long long M, long long N, const float* __restrict__ sa,
+                                                                 const float* __restrict__ sb, OutT* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= M * N) return;
+  float acc = ws[i];
+  for (int s = 1; s < splits; ++s) acc += ws[(long long)s * stride + i];
+  const long long m = i / N, n = i - m * N;
+  out[i] = cast_out<OutT>((acc * __ldg(sb + n)) * __ldg(sa + m));
+}
+
+int launch_split_reduce_scaled(const float* ws, long long stride, int splits, long long M, long long N, const float* sa,
+                               const float* sb, void* out, int out_dtype, cudaStream_t st) {
+  const long long blocks = (M * N + 255) / 256;
+  if (out_dtype == I4TC_FP16)
+    split_reduce_scaled_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(ws, stride, splits, M, N, sa, sb, static_cast<__half*>(out));
+  else
+    split_reduce_scaled_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(ws, stride, splits, M, N, sa, sb,
+                                                                                static_cast<__nv_bfloat16*>(out));
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
 }
 
 int launch_split_reduce(const float* ws, long long stride, int splits, long long n, void* out, cudaStream_t st) {

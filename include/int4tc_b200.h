@@ -57,8 +57,9 @@ int i4tc_sm_count(int device);
  * Process-wide.  Results do not depend on it. */
 int i4tc_set_tuning(int tile_n, int swap);
 
-/* Test / tuning hook for the small-M per-group path: number of K ranges that different thread blocks
- * handle before a fixed-order fp32 reduction (0 = automatic, 1 = never split, 2..8 = forced).  The
+/* Test / tuning hook for the small-M paths with scaled outputs (9..128 tokens): number of K ranges that
+ * different thread blocks handle before a fixed-order reduction (0 = automatic, 1 = never split, 2..8 = forced;
+ * per-channel results do not depend on it, per-group results only in the order fp32 terms are added).  The
  * partial sums live in a workspace owned by the library (one per device, grown on demand); calls on
  * different streams of one device that both split must not overlap. */
 int i4tc_set_split_k(int splits);

@@ -255,6 +255,30 @@ def test_split_k_small_m(tc, ops, M, N, G):
         ops.set_split_k(0)
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 512, 4096), (9, 257, 12288), (100, 640, 1024)])
+def test_split_k_per_channel_exact(tc, ops, M, N, K):
+    """Small-M per-channel path with K cut into ranges: the ranges carry exact integer sums, so every split count
+    gives the oracle's result bit for bit."""
+    rng = np.random.RandomState(M + N + K)
+    a, b = rand_codes(rng, (M, K)), rand_codes(rng, (N, K))
+    sa = (rng.rand(M).astype(np.float32) + 0.01) * 0.1
+    sb = (rng.rand(N).astype(np.float32) + 0.01) * 0.01
+    ref = torch.from_numpy(O.dequant_per_channel(O.int_gemm(a, b), sa, sb))
+    ap, bp = dev_packed(a), dev_packed(b)
+    try:
+        ops.set_tuning(64, 1)   # tensor-core kernel, weights on the row side
+        for splits in (1, 2, 5, 8):
+            ops.set_split_k(splits)
+            for dtype in (torch.bfloat16, torch.float16):
+                out = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+                tc.cutlass_int4_scaled_mm(ap, bp, dev_f32(sa), dev_f32(sb), out, M, N, K)
+                ops.check_status()
+                assert torch.equal(out.cpu(), ref.to(dtype)), (splits, dtype)
+    finally:
+        ops.set_split_k(0)
+        ops.set_tuning(0, -1)
+
+
 def test_grouped_aliases_and_checks(tc, ops):
     rng = np.random.RandomState(9)
     M, N, G = 10, 64, 2
