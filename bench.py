@@ -356,7 +356,7 @@ def run_ours(args) -> None:
                 "traffic": sum(gemm_bytes(M, N // world, K) for _, K, N in SHAPES) / len(SHAPES),
                 "traffic_unit": "bytes per launch (mean of the 4 shapes), algorithmic; ncu-confirmed at M=1024",
                 "kernel": ("w4a4_gemm_kernel (per-channel epilogue, 256x256 tiles on SM pairs)" if per_channel
-                           else "w4a4_gemm_kernel (per-group-128 epilogue)") + ", 4 launches per step",
+                           else "w4a4_gemm_kernel (per-group-128 epilogue, 256x256 tiles on SM pairs)") + ", 4 launches per step",
                 "peak_source": f"2 x bf16 burst of MEASURED_PEAKS.json ({peaks['source']}); int8 dense = 2 x bf16 on B200",
                 "per_shape_us": {SHAPES[i][0]: statistics.mean(v) * 1e6 for i, v in per_shape.items()},
             },
