@@ -202,7 +202,7 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local)
     if world > 1:
         # keep stdout to the one JSON line: NCCL prints its version line (VERSION and WARN levels) to stdout
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/tmp/nccl_debug_%h_%p.log")
         dist.init_process_group("nccl", device_id=dev)
     M = args.m
     peaks = load_peaks()

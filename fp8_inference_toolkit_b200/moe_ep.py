@@ -5,7 +5,8 @@ Rank r owns experts [r*E/n, (r+1)*E/n) and T/n of the tokens.  Per layer:
   1. local sort of the (token, slot) pairs by global expert id (device kernel) -- sorted by expert
      is also sorted by destination rank;
   2. a small all-gather of per-expert counts (the only host synchronisation: split sizes);
-  3. dispatch all-to-all of the token rows in sorted order;
+  3. dispatch all-to-all of the token rows in sorted order (bf16 rows, or -- on request, CUDA path -- rows
+     already quantised to int4 + group scales: 3.8x fewer bytes, same result);
   4. on the owner: rows arrive grouped by source rank, each group sorted by local expert; a second
      device sort merges the groups, `gather+quantise` writes the expert-sorted packed layout,
      the grouped-tile GEMMs run, and the outputs are put back into arrival order;
@@ -63,11 +64,50 @@ def exchange(rows: torch.Tensor, send_splits, recv_splits, group=None) -> torch.
     return out
 
 
+def _moe_layer_ep_quantized(x, expert_ids, expert_w, weights, num_experts, group):
+    """CUDA path with the dispatch payload already quantised: 68 bytes per 128 values (64 of codes, one fp32 scale)
+    instead of 256 bytes of bf16.  The quantiser works on whole rows, so quantising before the exchange gives the
+    codes and scales it would give after it: the layer's result is unchanged bit for bit."""
+    from . import moe as _moe
+
+    T, k = expert_ids.shape
+    H = x.shape[1]
+    G = H // 128
+    world = dist.get_world_size(group)
+    plan = plan_dispatch(expert_ids, num_experts, _moe.moe_sort_tokens, group)
+    P = plan.num_pairs
+    ap, asc = _moe.moe_gather_quant(x, plan.sorted_pairs, k)           # [G, P, 64], [G, P] in send order
+    payload = torch.cat([ap.permute(1, 0, 2).reshape(P, G * 64),
+                         asc.t().contiguous().view(torch.uint8).view(P, G * 4)], dim=1)   # one row per pair
+    recv = exchange(payload, plan.send_splits, plan.recv_splits, group)
+    R = recv.shape[0]
+    if R > 0:
+        e_loc = num_experts // world
+        sp2, inv2, off2 = _moe.moe_sort_tokens(local_expert_ids(plan), e_loc)
+        sel = recv.index_select(0, sp2.long())                           # expert-sorted rows
+        ap2 = sel[:, :G * 64].reshape(R, G, 64).permute(1, 0, 2).contiguous()
+        asc2 = sel[:, G * 64:].contiguous().view(torch.float32).view(R, G).t().contiguous()
+        y = _moe.moe_experts_forward(ap2, asc2, off2, weights)
+        ones = torch.ones(R, dtype=torch.float32, device=x.device)
+        y_rows = _moe.moe_combine(y, inv2, ones, R, 1)                   # back to arrival order
+    else:
+        y_rows = x.new_empty((0, H))
+    y_back = exchange(y_rows, plan.recv_splits, plan.send_splits, group)
+    return _moe.moe_combine(y_back, plan.inv_pairs, expert_w.contiguous(), T, k)
+
+
 def moe_layer_ep(x: torch.Tensor, expert_ids: torch.Tensor, expert_w: torch.Tensor, weights, num_experts: int,
-                 group=None, sort_fn=None, expert_fn=None, combine_fn=None) -> torch.Tensor:
+                 group=None, sort_fn=None, expert_fn=None, combine_fn=None, quantized_dispatch=None) -> torch.Tensor:
     """Expert-parallel MoE layer.  ``x`` bf16 [T_local, H]; ``expert_ids`` int32 [T_local, k] (global ids);
-    ``expert_w`` f32 [T_local, k]; ``weights`` = this rank's ``MoEWeights`` (E/n experts)."""
+    ``expert_w`` f32 [T_local, k]; ``weights`` = this rank's ``MoEWeights`` (E/n experts).
+
+    ``quantized_dispatch`` (CUDA path only): send quantised rows (1088 bytes per 2048 values) instead of bf16 rows
+    (4096 bytes).  Off by default: over NVLink the exchange is a small part of the layer and the re-layout kernels
+    cost more than the bytes saved (measured on 2 GPUs: 0.96 ms against 0.79 ms per layer); it is for links an order
+    of magnitude slower."""
     if sort_fn is None:
+        if quantized_dispatch:
+            return _moe_layer_ep_quantized(x, expert_ids, expert_w, weights, num_experts, group)
         from . import moe as _moe  # CUDA kernels; raises if the library is missing
 
         sort_fn = _moe.moe_sort_tokens

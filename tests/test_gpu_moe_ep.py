@@ -37,9 +37,11 @@ def _worker(rank, world, port):
     mine = moe.MoEWeights(full.gate_up_packed[sl].contiguous(), full.gate_up_scale[sl].contiguous(),
                           full.down_packed[sl].contiguous(), full.down_scale[sl].contiguous(), e_loc, H, I)
     ts = slice(rank * t_loc, (rank + 1) * t_loc)
-    out = moe_ep.moe_layer_ep(x[ts].contiguous(), ids[ts].contiguous(), w[ts].contiguous(), mine, E)
-    ops.check_status()
-    assert torch.equal(out, ref[ts]), (out.float() - ref[ts].float()).abs().max().item()
+    for quantized in (False, True):   # bf16 rows, then rows quantised before the exchange: the same result
+        out = moe_ep.moe_layer_ep(x[ts].contiguous(), ids[ts].contiguous(), w[ts].contiguous(), mine, E,
+                                  quantized_dispatch=quantized)
+        ops.check_status()
+        assert torch.equal(out, ref[ts]), (quantized, (out.float() - ref[ts].float()).abs().max().item())
     dist.barrier()
     dist.destroy_process_group()
 
