@@ -107,7 +107,7 @@ def test_scaled_bit_exact(tc, ops, M, N, K, dtype):
         assert torch.equal(out.cpu(), ref), (tile_n, swap)
 
 
-@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (600, 1000, 1024), (1024, 264, 4096), (257, 256, 128)])
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (600, 1000, 1024), (1024, 264, 4096), (257, 256, 128), (520, 300, 192)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_cta_pairs_scaled_bit_exact(tc, ops, M, N, K, dtype):
     """Per-channel GEMM on SM pairs (256 x 256 tiles, forced on): bit-identical to the oracle, ragged M and N
