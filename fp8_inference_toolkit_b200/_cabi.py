@@ -16,6 +16,7 @@ ROLE_ACTIVATION, ROLE_WEIGHT = 0, 1
 _p = C.c_void_p
 _i = C.c_int
 _l = C.c_int64
+_f = C.c_float
 
 #: name -> (restype, argtypes); must list every symbol of include/int4tc_b200.h
 SIGNATURES = {
@@ -40,6 +41,7 @@ SIGNATURES = {
     "i4tc_moe_gather_quant": (_i, [_p, _i, _l, _l, _p, _l, _l, _p, _p, _i, _p]),
     "i4tc_moe_grouped_gemm": (_i, [_p, _p, _p, _p, _p, _p, _l, _l, _l, _l, _i, _p]),
     "i4tc_moe_silu_mul_quant": (_i, [_p, _l, _l, _p, _p, _i, _p]),
+    "i4tc_rmsnorm_quant_grouped": (_i, [_p, _l, _l, _l, _p, _f, _l, _p, _p, _i, _p]),
     "i4tc_moe_combine": (_i, [_p, _p, _p, _l, _l, _l, _p, _i, _p]),
     "i4tc_check_status": (_i, [_i, _p]),
 }

@@ -215,6 +215,8 @@ __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
 // MODE 0: rows of x.  MODE 1: rows gathered through row_index[r] / index_div.
 // MODE 2: input is bf16 [rows, 2*K] laid out [gate | up]; the quantised value is
 //         bf16(silu(gate) * up).
+// MODE 3: RMSNorm first: the quantised value is bf16(bf16(x * rsqrt(mean(x^2) + eps)) * aux[k]); a warp then
+//         needs its whole row (the grid is not split along K).
 // GIVEN: divisors come from `given_scale` (group-major) instead of the absmax.
 // ------------------------------------------------------------------------------------------
 constexpr int kQRows = 8;
@@ -222,8 +224,12 @@ constexpr int kQVecs = 4;                 // 8-element vectors per lane per segm
 constexpr int kQLane = 8 * kQVecs;        // 32 consecutive elements per lane
 constexpr int kQSeg = 32 * kQLane;        // 1024 elements per warp per segment
 
+// round to bf16 and widen again
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
 template <typename T, int MODE>
-__device__ __forceinline__ void load_segment(Vec8<T> (&v)[kQVecs], const T* src, int k, int K, bool row_ok) {
+__device__ __forceinline__ void load_segment(Vec8<T> (&v)[kQVecs], const T* src, int k, int K, bool row_ok,
+                                             const T* aux = nullptr, float row_factor = 0.f) {
   // k = first element of this lane; K % 32 == 0, so the lane's 32 elements are all in range or none
   if (row_ok && k < K) {
 #pragma unroll
@@ -235,6 +241,16 @@ __device__ __forceinline__ void load_segment(Vec8<T> (&v)[kQVecs], const T* src,
         float f[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = silu_mul_bf16(g.get(i), u.get(i));
+        v[j].set_all(f);
+      } else if (MODE == 3) {
+        // RMSNorm in front of the quantiser: bf16(bf16(x * inv_rms) * weight), the roundings of an unfused
+        // normalisation that works in fp32 and returns the input's type
+        Vec8<T> xv, wv;
+        xv.load(src + k + 8 * j);
+        wv.load(aux + k + 8 * j);
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = bf16_round(bf16_round(xv.get(i) * row_factor) * wv.get(i));
         v[j].set_all(f);
       } else {
         v[j].load(src + k + 8 * j);
@@ -270,7 +286,7 @@ template <typename T, int LPG, int MODE, bool GIVEN>
 __global__ void __launch_bounds__(256) quant_grouped_kernel(
     const T* __restrict__ x, int64_t rows, int K, int64_t ldx, const int32_t* __restrict__ row_index,
     int index_div, const float* __restrict__ given_scale, uint8_t* __restrict__ packed,
-    float* __restrict__ scale, int role, int segs_per_block) {
+    float* __restrict__ scale, int role, int segs_per_block, const T* __restrict__ aux, float eps) {
   constexpr int GS = LPG * kQLane;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t r0 = (int64_t)blockIdx.x * kQRows;
@@ -286,11 +302,30 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
     if (MODE == 1) sr = row_index[r] / index_div;
     src = x + sr * ldx;
   }
+  float row_factor = 0.f;
+  if (MODE == 3) {
+    // first pass over the row: sum of squares in fp32 (the second pass below hits L1/L2)
+    float ss = 0.f;
+    if (row_ok) {
+      for (int k = lane * kQLane; k < K; k += kQSeg) {
+#pragma unroll
+        for (int j = 0; j < kQVecs; ++j) {
+          Vec8<T> xv;
+          xv.load(src + k + 8 * j);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss = fmaf(xv.get(i), xv.get(i), ss);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    row_factor = rsqrtf(ss / (float)K + eps);
+  }
   Vec8<T> cur[kQVecs], nxt[kQVecs];
-  load_segment<T, MODE>(cur, src, seg_begin * kQSeg + lane * kQLane, K, row_ok);
+  load_segment<T, MODE>(cur, src, seg_begin * kQSeg + lane * kQLane, K, row_ok, aux, row_factor);
   for (int seg = seg_begin; seg < seg_end; ++seg) {
     const int k = seg * kQSeg + lane * kQLane;
-    if (seg + 1 < seg_end) load_segment<T, MODE>(nxt, src, k + kQSeg, K, row_ok);
+    if (seg + 1 < seg_end) load_segment<T, MODE>(nxt, src, k + kQSeg, K, row_ok, aux, row_factor);
     const bool ok = row_ok && k < K;
     const int g = k / GS;
     Recip q;
@@ -445,7 +480,7 @@ __global__ void unpack_int4_kernel(const uint8_t* __restrict__ packed, int64_t n
 template <typename T, int MODE, bool GIVEN>
 static int launch_grouped_t(const T* x, int64_t rows, int64_t K, int64_t ldx, int gs, const int32_t* row_index,
                             int index_div, const float* given, uint8_t* packed, float* scale, int role,
-                            cudaStream_t st) {
+                            cudaStream_t st, const void* aux = nullptr, float eps = 0.f) {
   if (rows == 0 || K == 0) return I4TC_OK;
   // Enough blocks to fill the GPU several times over; beyond that a block walks several segments
   // of its rows so that loads of the next segment overlap the arithmetic of the current one.
@@ -454,11 +489,13 @@ static int launch_grouped_t(const T* x, int64_t rows, int64_t K, int64_t ldx, in
   int spb = nseg;
   if (row_blocks < 2048) spb = (int)((int64_t)nseg * row_blocks / 2048);
   if (spb < 1) spb = 1;
+  if (MODE == 3) spb = nseg;   // a warp normalises with the statistics of its whole row
   dim3 grid((unsigned)row_blocks, (unsigned)((nseg + spb - 1) / spb));
   I4TC_REQUIRE(grid.y <= 65535, I4TC_EINVAL, "K=%lld too large for the grouped quantiser", (long long)K);
 #define I4TC_LAUNCH_G(LPG)                                                                             \
   quant_grouped_kernel<T, LPG, MODE, GIVEN><<<grid, 256, 0, st>>>(x, rows, (int)K, ldx, row_index,     \
-                                                                   index_div, given, packed, scale, role, spb)
+                                                                   index_div, given, packed, scale, role, spb, \
+                                                                   static_cast<const T*>(aux), eps)
   switch (gs) {
     case 32: I4TC_LAUNCH_G(1); break;
     case 64: I4TC_LAUNCH_G(2); break;
@@ -481,7 +518,7 @@ static int check_vec_input(const void* x, int dtype, int64_t ldx, const char* wh
 template <int MODE, bool GIVEN>
 static int launch_grouped(const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx, int64_t gs,
                           const int32_t* row_index, int index_div, const float* given, uint8_t* packed,
-                          float* scale, int role, int device, void* stream) {
+                          float* scale, int role, int device, void* stream, const void* aux = nullptr, float eps = 0.f) {
   I4TC_REQUIRE(rows >= 0 && K >= 0 && gs > 0, I4TC_EINVAL, "negative size");
   I4TC_REQUIRE(gs % 2 == 0, I4TC_EINVAL, "group_size must be even");
   I4TC_REQUIRE(K % gs == 0, I4TC_EINVAL, "K must be divisible by group_size");
@@ -498,15 +535,15 @@ static int launch_grouped(const void* x, int dtype, int64_t rows, int64_t K, int
     case I4TC_BF16:
       return launch_grouped_t<__nv_bfloat16, MODE, GIVEN>(static_cast<const __nv_bfloat16*>(x), rows, K, ldx,
                                                           (int)gs, row_index, index_div, given, packed, scale,
-                                                          role, st);
+                                                          role, st, aux, eps);
     case I4TC_FP16:
-      if (MODE == 2) break;
-      return launch_grouped_t<__half, MODE == 2 ? 0 : MODE, GIVEN>(static_cast<const __half*>(x), rows, K, ldx,
+      if (MODE >= 2) break;
+      return launch_grouped_t<__half, MODE >= 2 ? 0 : MODE, GIVEN>(static_cast<const __half*>(x), rows, K, ldx,
                                                                   (int)gs, row_index, index_div, given, packed,
                                                                   scale, role, st);
     case I4TC_FP32:
-      if (MODE == 2) break;
-      return launch_grouped_t<float, MODE == 2 ? 0 : MODE, GIVEN>(static_cast<const float*>(x), rows, K, ldx,
+      if (MODE >= 2) break;
+      return launch_grouped_t<float, MODE >= 2 ? 0 : MODE, GIVEN>(static_cast<const float*>(x), rows, K, ldx,
                                                                  (int)gs, row_index, index_div, given, packed,
                                                                  scale, role, st);
     default: break;
@@ -602,6 +639,17 @@ extern "C" int i4tc_moe_silu_mul_quant(const void* h, int64_t P, int64_t I, uint
                                        int device, void* stream) {
   return launch_grouped<2, false>(h, I4TC_BF16, P, I, 2 * I, 128, nullptr, 1, nullptr, packed, scale,
                                   I4TC_ROLE_ACTIVATION, device, stream);
+}
+
+extern "C" int i4tc_rmsnorm_quant_grouped(const void* x, int64_t rows, int64_t K, int64_t ldx, const void* norm_weight,
+                                          float eps, int64_t group_size, uint8_t* packed, float* scale, int device,
+                                          void* stream) {
+  I4TC_REQUIRE(norm_weight != nullptr || rows == 0, I4TC_EINVAL, "null norm_weight");
+  I4TC_REQUIRE(K % 32 == 0, I4TC_EINVAL, "K must be a multiple of 32");
+  I4TC_REQUIRE(aligned_to(norm_weight, 16), I4TC_EALIGN, "norm_weight must be 16-byte aligned");
+  I4TC_REQUIRE(eps >= 0.f, I4TC_EINVAL, "negative eps");
+  return launch_grouped<3, false>(x, I4TC_BF16, rows, K, ldx, group_size, nullptr, 1, nullptr, packed, scale,
+                                  I4TC_ROLE_ACTIVATION, device, stream, norm_weight, eps);
 }
 
 extern "C" int i4tc_unpack_int4_to_int8(const uint8_t* packed, int64_t rows, int64_t K, int8_t* out, int device,

@@ -66,6 +66,18 @@ class W4A4Int4TCLinearMethod:
         return out.reshape(*x.shape[:-1], N)
 
 
+def apply_quantized(layer: nn.Module, x_packed: torch.Tensor, x_scale: torch.Tensor, M: int,
+                    bias: torch.Tensor | None = None) -> torch.Tensor:
+    """The per-group linear on activations that are already quantised ([G,M,64] codes, [G,M] scales) -- for
+    callers that fuse the quantiser into the preceding op (RMSNorm, SwiGLU).  bf16 [M, N]."""
+    K = layer.input_size_per_partition
+    N = layer.output_size_per_partition
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x_scale.device)
+    ops.cutlass_int4_fused_grouped_gemm(x_packed, layer.weight_int4, x_scale, layer.weight_scale, out, M, N,
+                                        GROUP_SIZE, K // GROUP_SIZE)
+    return out if bias is None else out + bias
+
+
 class W4A4Linear(nn.Module):
     """Drop-in for ``nn.Linear`` whose weight is quantised to int4 at load time.
 

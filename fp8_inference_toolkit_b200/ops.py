@@ -117,6 +117,26 @@ def static_int4_weight_quant_grouped(weight: torch.Tensor, group_size: int):
     return _quant_grouped(weight, group_size, _cabi.ROLE_WEIGHT, "static_int4_weight_quant_grouped")
 
 
+def rmsnorm_int4_quant_grouped(input: torch.Tensor, norm_weight: torch.Tensor, eps: float, group_size: int = 128):
+    """RMSNorm fused in front of the grouped quantiser (no reference op; the reference's report names the fusion as
+    its follow-up).  bf16 [M,K], bf16 [K] -> (packed u8 [G,M,gs/2], scale f32 [G,M]) of
+    ``bf16(bf16(x * rsqrt(mean(x^2) + eps)) * norm_weight)``."""
+    _cuda2d(input, "input")
+    _require(input.dtype == torch.bfloat16 and norm_weight.dtype == torch.bfloat16, "input and norm_weight must be bfloat16")
+    _require(input.stride(1) == 1, "input rows must be contiguous")
+    _same_device(input, norm_weight)
+    M, K = input.shape
+    _require(norm_weight.is_contiguous() and norm_weight.numel() == K, "norm_weight must be a contiguous [K] tensor")
+    _require(group_size > 0 and K % group_size == 0, "K must be divisible by group_size")
+    G = K // group_size
+    packed = torch.empty((G, M, group_size // 2), dtype=torch.uint8, device=input.device)
+    scale = torch.empty((G, M), dtype=torch.float32, device=input.device)
+    check(lib.i4tc_rmsnorm_quant_grouped(input.data_ptr(), M, K, input.stride(0), norm_weight.data_ptr(), float(eps),
+                                         int(group_size), packed.data_ptr(), scale.data_ptr(), _dev(input),
+                                         _stream(input)), "rmsnorm_int4_quant_grouped")
+    return packed, scale
+
+
 def int4_quant_with_scales(input: torch.Tensor, scale: torch.Tensor, group_size: int = 0):
     """Quantise with caller-supplied divisors (no reference op; the "identical scales" form used to
     compare codes bit for bit).  ``scale`` [M] -> packed [M,K/2]; ``scale`` [G,M] -> packed [G,M,gs/2]."""

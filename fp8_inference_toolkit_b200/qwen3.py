@@ -11,7 +11,9 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from .linear import W4A4Linear
+from . import moe as _moe
+from . import ops
+from .linear import W4A4Linear, apply_quantized
 
 
 @dataclass
@@ -53,7 +55,7 @@ def apply_rope(x, cos, sin):
 
 
 class Block(nn.Module):
-    def __init__(self, cfg: Qwen3Config, device, per_channel: bool, gen: torch.Generator):
+    def __init__(self, cfg: Qwen3Config, device, per_channel: bool, gen: torch.Generator, fused: bool = True):
         super().__init__()
         self.cfg = cfg
         qkv_out = (cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim
@@ -65,6 +67,8 @@ class Block(nn.Module):
         self.ln2 = RMSNorm(cfg.hidden, cfg.eps, device)
         self.q_norm = RMSNorm(cfg.head_dim, cfg.eps, device)
         self.k_norm = RMSNorm(cfg.head_dim, cfg.eps, device)
+        # fold the quantisers into RMSNorm / SwiGLU (per-group scales only; the per-channel ops keep the plain path)
+        self.fused = fused and not per_channel
 
     @staticmethod
     def _lin(k, n, device, per_channel, gen):
@@ -78,6 +82,8 @@ class Block(nn.Module):
     def forward(self, x, cos, sin):
         cfg = self.cfg
         B, S, _ = x.shape
+        if self.fused:
+            return self._forward_fused(x, cos, sin)
         qkv = self.qkv(self.ln1(x))
         q, k, v = qkv.split([cfg.q_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim], -1)
         q = self.q_norm(q.view(B, S, cfg.q_heads, cfg.head_dim)).transpose(1, 2)
@@ -91,13 +97,38 @@ class Block(nn.Module):
         return x + self.down(F.silu(g) * u)
 
 
+    def _attention(self, qkv, B, S, cos, sin):
+        cfg = self.cfg
+        q, k, v = qkv.split([cfg.q_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim], -1)
+        q = self.q_norm(q.view(B, S, cfg.q_heads, cfg.head_dim)).transpose(1, 2)
+        k = self.k_norm(k.view(B, S, cfg.kv_heads, cfg.head_dim)).transpose(1, 2)
+        v = v.view(B, S, cfg.kv_heads, cfg.head_dim).transpose(1, 2)
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        return a.transpose(1, 2).reshape(B, S, -1)
+
+    def _forward_fused(self, x, cos, sin):
+        """Per-group mode with the quantisers folded into the ops in front of them: RMSNorm + quantise in one
+        kernel before qkv and gate+up, SwiGLU + quantise in one kernel before down."""
+        B, S, H = x.shape
+        M = B * S
+        xp, xs = ops.rmsnorm_int4_quant_grouped(x.view(M, H), self.ln1.weight, self.ln1.eps)
+        qkv = apply_quantized(self.qkv, xp, xs, M).view(B, S, -1)
+        x = x + self.o(self._attention(qkv, B, S, cos, sin))
+        xp, xs = ops.rmsnorm_int4_quant_grouped(x.view(M, H), self.ln2.weight, self.ln2.eps)
+        gu = apply_quantized(self.gate_up, xp, xs, M)
+        ap, asc = _moe.moe_silu_mul_quant(gu)
+        return x + apply_quantized(self.down, ap, asc, M).view(B, S, H)
+
+
 class Qwen3Prefill(nn.Module):
-    def __init__(self, cfg: Qwen3Config = Qwen3Config(), device="cuda", per_channel: bool = False, seed: int = 1):
+    def __init__(self, cfg: Qwen3Config = Qwen3Config(), device="cuda", per_channel: bool = False, seed: int = 1,
+                 fused: bool = True):
         super().__init__()
         self.cfg = cfg
         gen = torch.Generator(device=device).manual_seed(seed)
         self.embed = nn.Embedding(cfg.vocab, cfg.hidden, device=device, dtype=torch.bfloat16)
-        self.blocks = nn.ModuleList(Block(cfg, device, per_channel, gen) for _ in range(cfg.layers))
+        self.blocks = nn.ModuleList(Block(cfg, device, per_channel, gen, fused) for _ in range(cfg.layers))
         self.norm = RMSNorm(cfg.hidden, cfg.eps, device)
 
     @torch.no_grad()

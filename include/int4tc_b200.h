@@ -175,6 +175,15 @@ int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, const uint8_t*
                           int64_t num_pairs, int64_t N, int64_t num_groups,
                           int64_t num_experts, int device, void* stream);
 
+/* RMSNorm fused in front of the grouped quantiser: for every row of x (bf16 [rows, K], row stride ldx)
+ *   y = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * norm_weight[k]),  then y is quantised like i4tc_quant_grouped
+ * (activation role) -> packed [K/group_size, rows, group_size/2], scale [K/group_size, rows].
+ * No reference counterpart: the reference quantises the output of a separate normalisation; its report names
+ * this fusion as the follow-up (docs/native_int4_tc_implementation_report.md:515-562). */
+int i4tc_rmsnorm_quant_grouped(const void* x, int64_t rows, int64_t K, int64_t ldx, const void* norm_weight,
+                               float eps, int64_t group_size, uint8_t* packed, float* scale, int device,
+                               void* stream);
+
 /* SwiGLU + grouped re-quantise: h bf16 [P, 2I] laid out [gate | up] ->
  * act = bf16(silu(gate) * up) -> packed [I/128, P, 64], scale [I/128, P]. */
 int i4tc_moe_silu_mul_quant(const void* h, int64_t P, int64_t I, uint8_t* packed, float* scale,

@@ -71,3 +71,9 @@ def test_tiny_qwen3_prefill_runs():
     ids2 = ids.clone()
     ids2[:, -1] = (ids2[:, -1] + 1) % cfg.vocab
     assert torch.equal(m(ids2)[:, :-1], y[:, :-1])
+    # the fused quantisers (RMSNorm + quantise, SwiGLU + quantise) follow the plain path closely
+    m_plain = Qwen3Prefill(cfg, "cuda", fused=False)
+    m_plain.embed.load_state_dict(m.embed.state_dict())   # the linears are seeded, the embedding table is not
+    y_plain = m_plain(ids)
+    cos = torch.nn.functional.cosine_similarity(y.float().flatten(), y_plain.float().flatten(), dim=0).item()
+    assert cos > 0.995, cos

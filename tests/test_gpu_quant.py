@@ -137,3 +137,29 @@ def test_full_size_properties(tc):
     # every row uses the full code range somewhere (absmax element maps to +-7)
     u = tc.unpack_int4_to_int8(pr[:256], K)
     assert (u.abs().amax(dim=1) == 7).all()
+
+
+@pytest.mark.parametrize("M,K", [(37, 1024), (8, 4096), (130, 256)])
+def test_rmsnorm_quant_matches_unfused(tc, M, K):
+    """RMSNorm fused in front of the grouped quantiser against the unfused pair (fp32 normalisation returning
+    bf16, times a bf16 weight, then the grouped quantiser).  The two differ only where the row statistic's last
+    bit flips a bf16 rounding, so nearly all codes and all scales agree."""
+    from fp8_inference_toolkit_b200 import ops
+
+    g = torch.Generator().manual_seed(M + K)
+    x = (torch.randn(M, K, generator=g) * 1.5).to(torch.bfloat16).cuda()
+    w = (1.0 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16).cuda()
+    eps = 1e-6
+    xf = x.float()
+    y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(torch.bfloat16) * w
+    p_ref, s_ref = tc.dynamic_int4_quant_grouped(y, 128)
+    p, s = ops.rmsnorm_int4_quant_grouped(x, w, eps, 128)
+    assert p.shape == p_ref.shape and s.shape == s_ref.shape
+    assert torch.allclose(s, s_ref, rtol=1e-2, atol=0)
+    assert (s == s_ref).float().mean() > 0.95
+    assert (p == p_ref).float().mean() > 0.995
+    # a strided view of a wider buffer gives the same result
+    wide = torch.zeros(M, K + 64, dtype=torch.bfloat16, device="cuda")
+    wide[:, :K] = x
+    p2, s2 = ops.rmsnorm_int4_quant_grouped(wide[:, :K], w, eps, 128)
+    assert torch.equal(p2, p) and torch.equal(s2, s)
