@@ -607,10 +607,13 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--m", type=int, default=8192, help="tokens per step")
+    ap.add_argument("--m", type=int, default=None,
+                    help="tokens per step (default 8192; 16384, the largest of configs[2], for --workload quant)")
     ap.add_argument("--scales", default="group", choices=["group", "channel"],
                     help="linear workload: per-group-128 scales (the headline) or per-token / per-channel scales")
     args = ap.parse_args()
+    if args.m is None:
+        args.m = 16384 if args.workload == "quant" else 8192
     if args.workload == "quant":
         run_quant(args)
     elif args.workload == "prefill":
