@@ -16,12 +16,12 @@ struct Shape {
   bool swap;
 };
 
-// Picks the tile width and operand orientation.  Small M puts the weights on the 128-row side of
+// Picks the tile width and operand orientation.  Up to 64 tokens the weights go on the 128-row side of
 // the MMA (so that no tensor-core rows are wasted on padding and more CTAs stream weights);
 // otherwise the width with the fewest (cost-weighted) waves over the SMs wins.
 static Shape choose_shape(long long M, long long N, int sms, bool allow_swap, bool group_mode) {
   Shape s;
-  s.swap = allow_swap && M <= 128;
+  s.swap = allow_swap && M <= 64;
   if (g_force_swap >= 0 && allow_swap) s.swap = g_force_swap != 0;
   if (g_force_bn) {
     s.bn = g_force_bn;
@@ -29,6 +29,12 @@ static Shape choose_shape(long long M, long long N, int sms, bool allow_swap, bo
   }
   if (s.swap) {
     s.bn = M <= 64 ? 64 : 128;
+    return s;
+  }
+  if (M <= 128) {
+    // one row of tiles and K split into ranges: measured, 128-wide tiles win for the 4096..6144-row weight
+    // matrices (more work items), 256-wide ones for the 24576-row one (fewer MMA issues per weight byte)
+    s.bn = N >= 16384 ? 256 : 128;
     return s;
   }
   (void)group_mode;
@@ -118,7 +124,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   // in fp32 for per-channel scales (bit-identical to the unsplit result).
   p.splits = 1;
   p.groups_per_split = d.G;
-  if ((d.epi_mode == EPI_GROUP || d.epi_mode == EPI_CHANNEL) && sh.swap && g_force_splits != 1) {
+  if ((d.epi_mode == EPI_GROUP || d.epi_mode == EPI_CHANNEL) && d.M <= 128 && g_force_splits != 1) {
     // cost in microseconds: waves x groups per range x ~0.65 us per group handshake, plus writing and
     // reading the fp32 partial sums at ~6 TB/s and one more launch
     int best_s = 1;

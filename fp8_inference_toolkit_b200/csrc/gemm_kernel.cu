@@ -707,19 +707,32 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         const bool first = per_group_flush || g == ti.g0;
         const bool last = per_group_flush || g == ti.g1 - 1;
         const uint32_t buf = flush % C::NT;
-        if (first) {
-          ok = wait_bar(bar_tm_empty + buf * 8, ((flush / C::NT) & 1u) ^ 1u, abort_flag);
-          if (!ok) break;
-        }
         const uint32_t s = it % C::NI, ph = (it / C::NI) & 1u;
-        ok = wait_bar(bar_i8_full + s * 8, ph, abort_flag);
-        if (!ok) break;
-        if (p.epi_mode == EPI_GROUP) {
-          ok = wait_bar(bar_sc_full + (flush % kNS) * 8, (flush / kNS) & 1u, abort_flag);
-          if (!ok) break;
-          if (CG == 2) {
-            ok = wait_bar(bar_sc_peer + (flush % kNS) * 8, (flush / kNS) & 1u, abort_flag);
+        const bool need_sc = p.epi_mode == EPI_GROUP;
+        const uint32_t b_tm = bar_tm_empty + buf * 8, p_tm = ((flush / C::NT) & 1u) ^ 1u;
+        const uint32_t b_sc = bar_sc_full + (flush % kNS) * 8, b_pe = bar_sc_peer + (flush % kNS) * 8;
+        const uint32_t p_sc = (flush / kNS) & 1u;
+        // This warp's loop is the serial path of every small tile.  A probe of a completed barrier still costs
+        // 150-200 cycles, so everything the group needs (accumulator free, operands converted, scales landed) is
+        // probed back to back -- the latencies overlap -- and the one-at-a-time waits run only if something is missing.
+        bool ready = mbar_test_wait(bar_i8_full + s * 8, ph);
+        if (first) ready &= mbar_test_wait(b_tm, p_tm);
+        if (need_sc) ready &= mbar_test_wait(b_sc, p_sc);
+        if (need_sc && CG == 2) ready &= mbar_test_wait(b_pe, p_sc);
+        if (!__all_sync(0xffffffffu, ready)) {
+          if (first) {
+            ok = wait_bar(b_tm, p_tm, abort_flag);
             if (!ok) break;
+          }
+          ok = wait_bar(bar_i8_full + s * 8, ph, abort_flag);
+          if (!ok) break;
+          if (need_sc) {
+            ok = wait_bar(b_sc, p_sc, abort_flag);
+            if (!ok) break;
+            if (CG == 2) {
+              ok = wait_bar(b_pe, p_sc, abort_flag);
+              if (!ok) break;
+            }
           }
         }
         tc_fence_after_sync();
