@@ -146,6 +146,25 @@ __device__ __forceinline__ bool wait_bar_slow(uint32_t bar, uint32_t parity, vol
   if (!ok) *abort_flag = 1;
   return ok;
 }
+// The same wait for a role that runs as a single thread (no warp vote).
+__device__ __forceinline__ bool wait_bar_thread(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;
+  bool ok = mbar_try_wait(bar, parity);
+  if (!ok) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+      ok = mbar_try_wait(bar, parity);
+      if (ok) break;
+      if ((++spins & 63u) == 0) {
+        if (*abort_flag) break;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+      }
+    }
+  }
+  if (!ok) *abort_flag = 1;
+  return ok;
+}
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
   return wait_bar_slow(bar, parity, abort_flag);
@@ -694,7 +713,9 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (CG = 2: the leader CTA only) ----------------
-    if (leader) {
+    // One thread runs the whole loop: the loop is the serial path of every small tile, and a warp-wide version
+    // pays a vote and a reconvergence (~250 cycles) per K group for nothing.
+    if (leader && lane == 0) {
     constexpr uint32_t idesc = make_idesc<BN, CG>();
     const uint32_t peer_i8_empty = (CG == 2) ? mapa_shared(bar_i8_empty, 1) : 0u;
     const uint32_t peer_tm_full = (CG == 2) ? mapa_shared(bar_tm_full, 1) : 0u;
@@ -719,24 +740,24 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         if (first) ready &= mbar_test_wait(b_tm, p_tm);
         if (need_sc) ready &= mbar_test_wait(b_sc, p_sc);
         if (need_sc && CG == 2) ready &= mbar_test_wait(b_pe, p_sc);
-        if (!__all_sync(0xffffffffu, ready)) {
+        if (!ready) {
           if (first) {
-            ok = wait_bar(b_tm, p_tm, abort_flag);
+            ok = wait_bar_thread(b_tm, p_tm, abort_flag);
             if (!ok) break;
           }
-          ok = wait_bar(bar_i8_full + s * 8, ph, abort_flag);
+          ok = wait_bar_thread(bar_i8_full + s * 8, ph, abort_flag);
           if (!ok) break;
           if (need_sc) {
-            ok = wait_bar(b_sc, p_sc, abort_flag);
+            ok = wait_bar_thread(b_sc, p_sc, abort_flag);
             if (!ok) break;
             if (CG == 2) {
-              ok = wait_bar(b_pe, p_sc, abort_flag);
+              ok = wait_bar_thread(b_pe, p_sc, abort_flag);
               if (!ok) break;
             }
           }
         }
         tc_fence_after_sync();
-        if (lane == 0) {
+        {
           const uint32_t aP = sbase + C::OFF_I8 + s * (C::I8_P + C::I8_Q);
           const uint32_t aQ = aP + C::I8_P;
           const uint64_t dP = make_desc(aP), dQ = make_desc(aQ);
@@ -757,11 +778,10 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
             if (last) tc_commit(bar_tm_full + buf * 8);
           }
         }
-        __syncwarp();
         if (last) ++flush;
       }
     }
-    } else if (CG == 2 && p.epi_mode == EPI_GROUP) {
+    } else if (!leader && CG == 2 && p.epi_mode == EPI_GROUP) {
       // second CTA of a pair: this warp has no MMAs to issue; it tells the leader when a scale stage of this
       // CTA has landed, so that the leader's "accumulator full" vouches for both CTAs' scales
       const uint32_t arr_sc_peer = mapa_shared(bar_sc_peer, 0);
@@ -778,6 +798,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         }
       }
     }
+    __syncwarp();   // the issuing thread rejoins its warp before the block-wide teardown
   } else if (p.epi_mode == EPI_GROUP) {
     // ---------------- scale loaders (warps 2 and 3 take alternate K groups) ----------------
     const uint32_t w = (uint32_t)(warp - kScaleWarp0);
