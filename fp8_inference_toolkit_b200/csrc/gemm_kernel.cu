@@ -194,23 +194,29 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((kBM * CG) >> 4) << 24);
 }
 
-// Expand one packed tile (rows x 64 B, dense) into a swizzled int8 tile (rows x 128 B).
-// 16-byte packed chunk j of a row becomes int8 chunks 2j (even codes) and 2j+1 (odd codes).
-template <int ROWS>
-__device__ __forceinline__ void convert_tile(uint32_t pk, uint32_t i8, int tid) {
-  constexpr int CHUNKS = ROWS * 4;
-  constexpr int PER_THREAD = CHUNKS / (kConvWarps * 32);
-  static_assert(CHUNKS % (kConvWarps * 32) == 0, "tile rows must be a multiple of 32");
+// Expand the packed P tile (ROWS_P x 64 B, dense) and Q tile (ROWS_Q x 64 B) of one stage into swizzled int8 tiles
+// (rows x 128 B).  16-byte packed chunk j of a row becomes int8 chunks 2j (even codes) and 2j+1 (odd codes).
+// The two tiles are walked as one list of chunks, up to six loads in flight per thread, so that a narrow stage
+// (64 or 128 Q rows) is one round trip to shared memory instead of one per tile.
+template <int ROWS_P, int ROWS_Q>
+__device__ __forceinline__ void convert_stage(uint32_t pkP, uint32_t i8P, uint32_t pkQ, uint32_t i8Q, int tid) {
+  constexpr int NT = kConvWarps * 32;
+  static_assert((ROWS_P * 4) % NT == 0 && (ROWS_Q * 4) % NT == 0, "tile rows must be a multiple of 32");
+  constexpr int TP = ROWS_P * 4 / NT, TQ = ROWS_Q * 4 / NT, T = TP + TQ;
+  constexpr int BATCH = 6;
 #pragma unroll
-  for (int i0 = 0; i0 < PER_THREAD; i0 += 4) {
-    uint4 w[4];
+  for (int i0 = 0; i0 < T; i0 += BATCH) {
+    uint4 w[BATCH];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      if (i0 + i < PER_THREAD) w[i] = lds128(pk + (uint32_t)(tid + (i0 + i) * kConvWarps * 32) * 16u);
+    for (int i = 0; i < BATCH; ++i) {
+      const int c = i0 + i;
+      if (c < T) w[i] = lds128((c < TP ? pkP : pkQ) + (uint32_t)(tid + (c < TP ? c : c - TP) * NT) * 16u);
+    }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (i0 + i < PER_THREAD) {
-        const int q = tid + (i0 + i) * kConvWarps * 32;
+    for (int i = 0; i < BATCH; ++i) {
+      const int c = i0 + i;
+      if (c < T) {
+        const int q = tid + (c < TP ? c : c - TP) * NT;
         const int row = q >> 2, j = q & 3;
         uint4 lo, hi;
         lo.x = (w[i].x << 4) & 0xF0F0F0F0u; hi.x = w[i].x & 0xF0F0F0F0u;
@@ -218,7 +224,7 @@ __device__ __forceinline__ void convert_tile(uint32_t pk, uint32_t i8, int tid) 
         lo.z = (w[i].z << 4) & 0xF0F0F0F0u; hi.z = w[i].z & 0xF0F0F0F0u;
         lo.w = (w[i].w << 4) & 0xF0F0F0F0u; hi.w = w[i].w & 0xF0F0F0F0u;
         const uint32_t c0 = (uint32_t)((2 * j) ^ (row & 7));
-        const uint32_t base = i8 + (uint32_t)row * kI8Row;
+        const uint32_t base = (c < TP ? i8P : i8Q) + (uint32_t)row * kI8Row;
         sts128(base + c0 * 16u, lo);
         sts128(base + (c0 ^ 1u) * 16u, hi);
       }
@@ -850,8 +856,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         if (!ok) break;
         const uint32_t pkP = sbase + C::OFF_PK + sp_ * (C::PK_P + C::PK_Q);
         const uint32_t i8P = sbase + C::OFF_I8 + si * (C::I8_P + C::I8_Q);
-        convert_tile<kBM>(pkP, i8P, tid);
-        convert_tile<C::QR>(pkP + C::PK_P, i8P + C::I8_P, tid);
+        convert_stage<kBM, C::QR>(pkP, i8P, pkP + C::PK_P, i8P + C::I8_P, tid);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
