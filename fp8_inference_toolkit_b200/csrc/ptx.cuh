@@ -191,9 +191,6 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
       : "memory");
 }
 
-__device__ __forceinline__ void tmem_st_wait() {
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
 // 16 lanes x 256 bits, four column blocks: thread t receives, for column block k (8 columns) and
 // row half h, the two consecutive columns 8k + 2(t%4), +1 of lane (base + 8h + t/4) in
 // r[4k + 2h], r[4k + 2h + 1] (the accumulator-fragment layout of an m16n8 MMA).
@@ -206,23 +203,6 @@ __device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
-// Same shape, two column blocks (16 columns): r[4k + 2h], r[4k + 2h + 1] for k in {0, 1}.
-__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-      : "r"(taddr)
-      : "memory");
-}
-// Fills 32 lanes x 32 columns with one value.
-__device__ __forceinline__ void tmem_fill_32x32(uint32_t taddr, uint32_t v) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
-      "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v)
-      : "memory");
-}
-
 // ---- shared memory vector access ------------------------------------------------------
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
@@ -234,46 +214,8 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
                : "memory");
 }
 
-// ---- packed f32x2 arithmetic on 64-bit registers (two floats per register pair) ----------
-__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ uint64_t pack_b32x2(uint32_t lo, uint32_t hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
-__device__ __forceinline__ uint64_t lds64(uint32_t addr) {
-  uint64_t v;
-  asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr));
-  return v;
-}
-
-// 4-byte asynchronous global -> shared copy (no register staging) and its completion wait.
-__device__ __forceinline__ void cp_async_4(uint32_t dst_smem, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
-}
-// The same copy, writing zero instead when `valid` is false (nothing is read from `src` then).
+// 4-byte asynchronous global -> shared copy (no register staging); writes zero instead when `valid` is false
+// (nothing is read from `src` then).
 __device__ __forceinline__ void cp_async_4_zfill(uint32_t dst_smem, const void* src, bool valid) {
   const uint32_t n = valid ? 4u : 0u;
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst_smem), "l"(src), "r"(n) : "memory");
