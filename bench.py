@@ -36,6 +36,27 @@ UNIT = "TOPS"
 GROUP = 128
 
 
+_RESULT_FD = None
+
+
+def claim_stdout() -> None:
+    """Keep stdout to the one JSON line: libraries that write to file descriptor 1 themselves (NCCL prints its version
+    there) are sent to stderr for the rest of the run, and the result goes to the descriptor saved here."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -166,7 +187,7 @@ def run_reference(args) -> None:
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(M: int, n_gpus: int, per_channel: bool = False) -> dict:
@@ -201,8 +222,6 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # keep stdout to the one JSON line: NCCL prints its version line (VERSION and WARN levels) to stdout
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/tmp/nccl_debug_%h_%p.log")
         dist.init_process_group("nccl", device_id=dev)
     M = args.m
     peaks = load_peaks()
@@ -373,7 +392,7 @@ def run_ours(args) -> None:
                 "value": cops / t / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                 "sample": "16 of %d token rows of each of the 4 linears, one pass" % M,
             }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -540,7 +559,7 @@ def run_quant(args) -> None:
         us = statistics.mean(a.elapsed_time(b) for a, b in ev[mode]) * 1e3
         res[mode] = {"us": us, "GBs": byts / us / 1e3, "frac": byts / us / 1e3 / peaks["hbm_gbs"], "bytes": byts}
     tot_bytes = 2 * (res["row"]["bytes"] + res["group"]["bytes"])
-    print(json.dumps({
+    emit({
         "metric": "int4_quant_pack_gbs", "value": tot_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "dtype": "f32 on bf16 -> s4", "data": "synthetic",
@@ -549,7 +568,7 @@ def run_quant(args) -> None:
         "roofline": {"bound": "hbm", "achieved": res["group"]["GBs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": res["group"]["frac"], "traffic": None, "kernel": "quant_grouped_kernel",
                      "per_kernel": res},
-    }), flush=True)
+    })
 
 
 def run_prefill(args) -> None:
@@ -583,14 +602,14 @@ def run_prefill(args) -> None:
     ops.check_status()
     ms = e0.elapsed_time(e1) / args.steps
     lin_ops = 2 * B * S * cfg.layers * sum(N * K for _, K, N in SHAPES)
-    print(json.dumps({
+    emit({
         "metric": "qwen3_8b_w4a4_prefill_tokens_per_s", "value": B * S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
         "dtype": "s4*s4->s32 linears, bf16 attention", "data": "synthetic",
         "config": {"workload": "BASELINE configs[4]: Qwen3-8B-shaped prefill, %d layers, batch %d x %d, W4A4 group-128"
                                % (cfg.layers, B, S)},
         "linear_tops": lin_ops / (ms * 1e-3) / 1e12,
-    }), flush=True)
+    })
 
 
 def main() -> None:
@@ -612,6 +631,7 @@ def main() -> None:
     ap.add_argument("--scales", default="group", choices=["group", "channel"],
                     help="linear workload: per-group-128 scales (the headline) or per-token / per-channel scales")
     args = ap.parse_args()
+    claim_stdout()
     if args.m is None:
         args.m = 16384 if args.workload == "quant" else 8192
     if args.workload == "quant":
