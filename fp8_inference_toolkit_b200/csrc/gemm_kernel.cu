@@ -353,13 +353,16 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
 #pragma unroll
     for (int i = 0; i < CW / 2; ++i) f[i] = make_float2(0.f, 0.f);
     bool ok = true;
+    bool probed = false;   // the next accumulator was already seen full by a probe issued under the last slab's math
     for (int g = ti.g0; g < ti.g1; ++g) {
       // the MMA warp waited for this scale stage (in a CTA pair: for both CTAs' stages) before it issued the
       // group, so an accumulator that is full implies scales that have landed
       const uint32_t ss = flush % kNS;
       const uint32_t buf = flush % C::NT;
-      ok = wait_bar(bar_tm_full + buf * 8, (flush / C::NT) & 1u, abort_flag);
-      if (!ok) break;
+      if (!__all_sync(0xffffffffu, probed)) {
+        ok = wait_bar(bar_tm_full + buf * 8, (flush / C::NT) & 1u, abort_flag);
+        if (!ok) break;
+      }
       tc_fence_after_sync();
       const float* st_p = sc + ss * (C::SCALE_STAGE / 4) + quad * 32;         // this warp's 32 row scales
       const float* st_q = sc + ss * (C::SCALE_STAGE / 4) + kBM + col_base;    // this warp's CW column scales
@@ -381,6 +384,9 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) arrive_bar<CG>(bar_tm_empty + buf * 8);
+          // a probe of a completed barrier costs 150-200 cycles: ask about the next accumulator now, the answer
+          // arrives while the last slab is folded in
+          probed = (g + 1 < ti.g1) && mbar_test_wait(bar_tm_full + ((flush + 1) % C::NT) * 8, ((flush + 1) / C::NT) & 1u);
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
