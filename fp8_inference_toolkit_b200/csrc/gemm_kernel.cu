@@ -856,10 +856,14 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
       for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         const uint32_t sp_ = it % C::NP, php = (it / C::NP) & 1u;
         const uint32_t si = it % C::NI, phi = (it / C::NI) & 1u;
-        ok = wait_bar(bar_pk_full + sp_ * 8, php, abort_flag);
-        if (!ok) break;
-        ok = wait_bar(bar_i8_empty + si * 8, phi ^ 1u, abort_flag);
-        if (!ok) break;
+        // both probes in flight together (their latencies overlap); one-at-a-time waits only if something is missing
+        const bool ready = mbar_test_wait(bar_pk_full + sp_ * 8, php) & mbar_test_wait(bar_i8_empty + si * 8, phi ^ 1u);
+        if (!__all_sync(0xffffffffu, ready)) {
+          ok = wait_bar(bar_pk_full + sp_ * 8, php, abort_flag);
+          if (!ok) break;
+          ok = wait_bar(bar_i8_empty + si * 8, phi ^ 1u, abort_flag);
+          if (!ok) break;
+        }
         const uint32_t pkP = sbase + C::OFF_PK + sp_ * (C::PK_P + C::PK_Q);
         const uint32_t i8P = sbase + C::OFF_I8 + si * (C::I8_P + C::I8_Q);
         convert_stage<kBM, C::QR>(pkP, i8P, pkP + C::PK_P, i8P + C::I8_P, tid);
