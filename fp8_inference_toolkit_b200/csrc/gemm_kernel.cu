@@ -15,10 +15,13 @@
 //
 // Roles (512 threads):
 //   warp 0      TMA producer: packed P (128 x 64 B) and Q (BN x 64 B) tiles, one K group per stage
-//   warp 1      MMA issuer (one lane) and owner of the TMEM allocation
+//   warp 1      MMA issuer (one thread runs the whole loop) and owner of the TMEM allocation
+//   warps 2-3   per-group mode: copy the row and column scales of each K group into a ring in shared memory
 //   warps 4-7   converters: packed stage -> 128B-swizzled K-major int8 stage
 //   warps 8-15  epilogue: tcgen05.ld, int32 -> fp32, scales, fp32 accumulation across groups, store
 // Two to four TMEM accumulators (BN columns each) let later groups be multiplied while one is drained.
+// CG = 2: two CTAs on neighbouring SMs share a 256 x 256 tile (tcgen05.mma.cta_group::2 issued by the first
+// one); each stages and converts its own 128 rows of P and only half of the Q rows.
 // Every wait is bounded: on expiry the kernel sets bit 0 of the status word, all roles leave
 // their loops, TMEM is released and the kernel returns.
 #include "gemm.cuh"
