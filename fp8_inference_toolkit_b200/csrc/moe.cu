@@ -53,37 +53,52 @@ __global__ void __launch_bounds__(kSortChunk) moe_hist_kernel(const int32_t* __r
   if ((int)threadIdx.x < E) counts[(long long)blockIdx.x * E + threadIdx.x] = total;
 }
 
-// One block of E (<= 256) threads: exclusive scan over chunks per expert, then over experts.
+// One block of kMaxExperts threads, thread e = expert e.  Two passes over the [chunks, E] histogram, each with eight
+// independent loads in flight (a load-add-store chain per chunk would pay a trip to L2 per chunk): totals per
+// expert, an exclusive scan of the totals across experts (warp shuffles), then the running bases of every chunk.
 __global__ void __launch_bounds__(kMaxExperts) moe_scan_kernel(int32_t* __restrict__ counts, int chunks, int E,
                                                               int32_t* __restrict__ expert_offsets) {
-  __shared__ int s_tot[kMaxExperts];
-  __shared__ int s_off[kMaxExperts + 1];
-  const int e = threadIdx.x;
-  int run = 0;
-  if (e < E) {
-    for (int c = 0; c < chunks; ++c) {
-      const int v = counts[(long long)c * E + e];
-      counts[(long long)c * E + e] = run;
-      run += v;
+  __shared__ int s_warp[kMaxExperts / 32];
+  const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+  const bool ok = e < E;
+  int total = 0;
+  if (ok) {
+    for (int c0 = 0; c0 < chunks; c0 += 8) {
+      int v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (c0 + j < chunks) ? counts[(long long)(c0 + j) * E + e] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) total += v[j];
     }
-    s_tot[e] = run;
   }
-  __syncthreads();
-  if (e == 0) {
-    int acc = 0;
-    for (int i = 0; i < E; ++i) {
-      s_off[i] = acc;
-      acc += s_tot[i];
-    }
-    s_off[E] = acc;
+  // exclusive scan of `total` over the experts
+  int incl = total;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
   }
+  if (lane == 31) s_warp[warp] = incl;
   __syncthreads();
-  if (e < E) {
-    const int off = s_off[e];
+  int warp_base = 0;
+#pragma unroll
+  for (int w = 0; w < kMaxExperts / 32; ++w) warp_base += (w < warp) ? s_warp[w] : 0;
+  const int off = warp_base + incl - total;
+  if (ok) {
     expert_offsets[e] = off;
-    for (int c = 0; c < chunks; ++c) counts[(long long)c * E + e] += off;
+    if (e == E - 1) expert_offsets[E] = off + total;
+    int run = off;
+    for (int c0 = 0; c0 < chunks; c0 += 8) {
+      int v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (c0 + j < chunks) ? counts[(long long)(c0 + j) * E + e] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (c0 + j < chunks) counts[(long long)(c0 + j) * E + e] = run;
+        run += v[j];
+      }
+    }
   }
-  if (e == 0) expert_offsets[E] = s_off[E];
 }
 
 __global__ void __launch_bounds__(kSortChunk) moe_scatter_kernel(const int32_t* __restrict__ ids, int P, int E,
