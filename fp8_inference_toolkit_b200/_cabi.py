@@ -17,6 +17,7 @@ _p = C.c_void_p
 _i = C.c_int
 _l = C.c_int64
 _f = C.c_float
+_d = C.c_double
 
 #: name -> (restype, argtypes); must list every symbol of include/int4tc_b200.h
 SIGNATURES = {
@@ -29,10 +30,14 @@ SIGNATURES = {
     "i4tc_quant_rowwise": (_i, [_p, _i, _l, _l, _l, _p, _p, _i, _i, _p]),
     "i4tc_quant_grouped": (_i, [_p, _i, _l, _l, _l, _l, _p, _p, _i, _i, _p]),
     "i4tc_quant_with_scales": (_i, [_p, _i, _l, _l, _l, _l, _p, _p, _i, _p]),
+    "i4tc_quant_clipped_grouped": (_i, [_p, _i, _l, _l, _l, _l, _d, _p, _p, _i, _p]),
+    "i4tc_quant_asymmetric_grouped": (_i, [_p, _i, _l, _l, _l, _l, _d, _p, _p, _p, _p, _i, _p]),
+    "i4tc_weight_group_sums": (_i, [_p, _l, _l, _p, _i, _p]),
     "i4tc_unpack_int4_to_int8": (_i, [_p, _l, _l, _p, _i, _p]),
     "i4tc_gemm_int32": (_i, [_p, _p, _p, _l, _l, _l, _i, _p]),
     "i4tc_gemm_scaled": (_i, [_p, _p, _p, _p, _p, _i, _l, _l, _l, _i, _p]),
     "i4tc_gemm_grouped": (_i, [_p, _p, _p, _p, _p, _l, _l, _l, _l, _i, _p]),
+    "i4tc_gemm_grouped_azp": (_i, [_p, _p, _p, _p, _p, _p, _p, _l, _l, _l, _l, _i, _p]),
     "i4tc_gemm_grouped_int32": (_i, [_p, _p, _p, _l, _l, _l, _i, _p]),
     "i4tc_moe_sort_scratch_bytes": (_l, [_l, _l]),
     "i4tc_moe_sort": (_i, [_p, _l, _l, _p, _p, _p, _p, _l, _i, _p]),

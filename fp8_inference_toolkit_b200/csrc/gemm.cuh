@@ -50,6 +50,11 @@ struct GemmParams {
 
 // out[i] = bf16(sum_s ws[s * stride + i]), s ascending.
 int launch_split_reduce(const float* ws, long long stride, int splits, long long n, void* out, cudaStream_t st);
+// out = bf16(sum of the K ranges' fp32 sums + sum_g (sa * adj)[g, m] * (sb * wcs)[g, n]); defined with the
+// asymmetric quantisers
+int launch_azp_finish(const float* ws, long long stride, int splits, const float* sa, const float* sb,
+                      const float* adj, const float* wcs, int G, long long M, long long N, void* out,
+                      cudaStream_t st);
 // out[m, n] = cast((sum_s ws[s * stride + m * N + n] * sb[n]) * sa[m]): the ranges hold exact integer sums.
 int launch_split_reduce_scaled(const float* ws, long long stride, int splits, long long M, long long N, const float* sa,
                                const float* sb, void* out, int out_dtype, cudaStream_t st);

@@ -67,6 +67,10 @@ struct DenseArgs {
   bool rowmajor;    // operands are [rows, K/2] (else group-major [G, rows, 64])
   long long K;      // only for rowmajor
   int epi_mode;
+  // zero-point pass (per-group mode only): the GEMM leaves fp32 sums in the workspace and a second kernel adds
+  // sum_g scale_a * azp_adj * scale_b * w_col_sum before rounding to bf16
+  const float* azp_adj = nullptr;
+  const float* w_col_sum = nullptr;
 };
 
 static int run_dense(const DenseArgs& d, int device, void* stream) {
@@ -79,7 +83,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   I4TC_REQUIRE(d.M < (1ll << 31) - 256 && d.N < (1ll << 31) - 256, I4TC_EINVAL, "M or N too large");
 
   // a handful of tokens: stream the weights through the CUDA cores instead (unless a test pins the tile shape)
-  if (g_force_bn == 0 && g_force_swap < 0 && g_force_splits == 0 &&
+  if (g_force_bn == 0 && g_force_swap < 0 && g_force_splits == 0 && d.azp_adj == nullptr &&
       gemv_applicable(d.M, d.N, (long long)d.G * 128, d.epi_mode) && (!d.rowmajor || d.K == (long long)d.G * 128))
     return launch_w4a4_gemv(d.a, d.b, d.sa, d.sb, d.out, d.out_dtype, d.M, d.N, d.G, d.rowmajor, d.epi_mode,
                             info->sm_count, static_cast<cudaStream_t>(stream));
@@ -146,6 +150,18 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
       p.split_ws = ws;
     }
   }
+  if (d.azp_adj != nullptr && p.split_ws == nullptr) {
+    // one K range, written as fp32 to the workspace
+    p.ws_stride = (d.M * d.N + 3) & ~3ll;
+    float* ws = nullptr;
+    if (int rc = split_workspace(device, (size_t)p.ws_stride * sizeof(float), &ws)) return rc;
+    p.split_ws = ws;
+  }
+  auto finish = [&]() -> int {
+    if (d.azp_adj == nullptr) return I4TC_OK;
+    return launch_azp_finish(p.split_ws, p.ws_stride, p.splits, d.sa, d.sb, d.azp_adj, d.w_col_sum, d.G, d.M, d.N,
+                             d.out, static_cast<cudaStream_t>(stream));
+  };
 
   // CTA pairs (256 x 256 tiles on two SMs): each SM converts and stages a third less per unit of MMA work.
   // Worth it once the 256-row tiles fill the SM pairs about as well as the 128-row tiles fill the SMs.
@@ -171,7 +187,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
     pp.num_p_tiles = (int)((prow + 255) / 256);
     const int grid = 2 * (int)(pair_tiles < clusters_max ? pair_tiles : clusters_max);
     const int rc = launch_w4a4_gemm(pp, tmP, tmQ, sh.bn, grid, true, static_cast<cudaStream_t>(stream));
-    if (rc == I4TC_OK) return I4TC_OK;
+    if (rc == I4TC_OK) return finish();
     if (g_cta_pairs == 1) return rc;   // the caller asked for pairs: report why they cannot run
     // an environment that cannot launch clusters of two (a restricted SM partition, for instance): the launch
     // was refused before anything ran; remember it and use single thread blocks from now on
@@ -182,6 +198,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   const long long items = tiles * p.splits;
   const int grid = (int)(items < info->sm_count ? items : info->sm_count);
   if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, false, static_cast<cudaStream_t>(stream))) return rc;
+  if (d.azp_adj != nullptr) return finish();
   if (p.splits > 1) {
     if (d.epi_mode == EPI_CHANNEL)
       return launch_split_reduce_scaled(p.split_ws, p.ws_stride, p.splits, d.M, d.N, d.sa, d.sb, d.out, d.out_dtype,
@@ -255,6 +272,21 @@ extern "C" int i4tc_gemm_grouped(const uint8_t* a, const uint8_t* b, const float
   if (rc) return rc < 0 ? rc : I4TC_OK;
   I4TC_REQUIRE(scale_a && scale_b, I4TC_EINVAL, "null scale pointer");
   DenseArgs d{a, b, scale_a, scale_b, out, I4TC_BF16, M, N, (int)num_groups, false, 0, EPI_GROUP};
+  return run_dense(d, device, stream);
+}
+
+extern "C" int i4tc_gemm_grouped_azp(const uint8_t* a, const uint8_t* b, const float* scale_a, const float* scale_b,
+                                     const float* azp_adj, const float* w_col_sum, void* out, int64_t M, int64_t N,
+                                     int64_t group_size, int64_t num_groups, int device, void* stream) {
+  I4TC_REQUIRE(group_size == 128, I4TC_EUNSUPPORTED, "fused grouped GEMM only supports group_size=128");
+  I4TC_REQUIRE(num_groups > 0 && num_groups <= 512, I4TC_EINVAL, "num_groups must be in [1, 512]");
+  int rc = check_dense_common(a, b, out, M, N);
+  if (rc) return rc < 0 ? rc : I4TC_OK;
+  I4TC_REQUIRE(scale_a && scale_b && azp_adj && w_col_sum, I4TC_EINVAL, "null scale, azp_adj or w_col_sum pointer");
+  I4TC_REQUIRE(M * N < (1ll << 40), I4TC_EINVAL, "M * N too large for the fp32 workspace");
+  DenseArgs d{a, b, scale_a, scale_b, out, I4TC_BF16, M, N, (int)num_groups, false, 0, EPI_GROUP};
+  d.azp_adj = azp_adj;
+  d.w_col_sum = w_col_sum;
   return run_dense(d, device, stream);
 }
 

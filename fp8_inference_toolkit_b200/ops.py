@@ -117,6 +117,71 @@ def static_int4_weight_quant_grouped(weight: torch.Tensor, group_size: int):
     return _quant_grouped(weight, group_size, _cabi.ROLE_WEIGHT, "static_int4_weight_quant_grouped")
 
 
+def _ext_input(input: torch.Tensor, group_size: int, who: str):
+    _cuda2d(input, "input")
+    _require(input.dtype in (torch.bfloat16, torch.float16), f"{who}: input must be bfloat16 or float16")
+    M, K = input.shape
+    _require(group_size > 0 and K % group_size == 0, "K must be divisible by group_size")
+    _require(group_size % 2 == 0, "group_size must be even")
+    if input.stride(1) != 1:
+        input = input.contiguous()
+    return input, M, K, K // group_size
+
+
+def dynamic_int4_quant_clipped_grouped(input: torch.Tensor, group_size: int, clip_ratio: float):
+    """[M,K] -> (packed u8 [G,M,gs/2], scale f32 [G,M]) with the range ``absmax * clip_ratio`` per group.
+    Reference: ``int4_quant.cu:906`` (checks ``:909-916``)."""
+    x, M, K, G = _ext_input(input, group_size, "dynamic_int4_quant_clipped_grouped")
+    _require(0.0 < clip_ratio <= 1.0, "clip_ratio must be in (0, 1]")
+    packed = torch.empty((G, M, group_size // 2), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((G, M), dtype=torch.float32, device=x.device)
+    check(lib.i4tc_quant_clipped_grouped(x.data_ptr(), _DTYPES[x.dtype], M, K, x.stride(0), int(group_size),
+                                         float(clip_ratio), packed.data_ptr(), scale.data_ptr(), _dev(x),
+                                         _stream(x)), "dynamic_int4_quant_clipped_grouped")
+    return packed, scale
+
+
+def dynamic_int4_quant_asymmetric_clipped_grouped(input: torch.Tensor, group_size: int, clip_ratio: float,
+                                                  smooth_scale: torch.Tensor | None = None):
+    """[M,K] -> (packed u8 [G,M,gs/2], scale f32 [G,M], azp_adj f32 [G,M]); asymmetric codes stored as
+    ``u - 8``, optional division by ``smooth_scale`` [K] (same dtype as the input) and symmetric clipping first.
+    Reference: ``int4_quant.cu:1433`` (checks ``:1437-1470``)."""
+    who = "dynamic_int4_quant_asymmetric_clipped_grouped"
+    x, M, K, G = _ext_input(input, group_size, who)
+    _require(0.0 < clip_ratio <= 1.0, "clip_ratio must be in (0, 1]")
+    sm_ptr = None
+    if smooth_scale is not None:
+        _require(smooth_scale.is_cuda and smooth_scale.dtype == x.dtype, "smooth_scale must match the input's dtype")
+        _require(smooth_scale.numel() == K, "smooth_scale must be [K]")
+        _same_device(x, smooth_scale)
+        smooth_scale = smooth_scale.contiguous()
+        sm_ptr = smooth_scale.data_ptr()
+    packed = torch.empty((G, M, group_size // 2), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((G, M), dtype=torch.float32, device=x.device)
+    azp_adj = torch.empty((G, M), dtype=torch.float32, device=x.device)
+    check(lib.i4tc_quant_asymmetric_grouped(x.data_ptr(), _DTYPES[x.dtype], M, K, x.stride(0), int(group_size),
+                                            float(clip_ratio), sm_ptr, packed.data_ptr(), scale.data_ptr(),
+                                            azp_adj.data_ptr(), _dev(x), _stream(x)), who)
+    return packed, scale, azp_adj
+
+
+def dynamic_int4_quant_asymmetric_grouped(input: torch.Tensor, group_size: int):
+    """[M,K] -> (packed, scale, azp_adj) without clipping or smoothing.  Reference: ``int4_quant.cu:1262``."""
+    return dynamic_int4_quant_asymmetric_clipped_grouped(input, group_size, 1.0, None)
+
+
+def int4_weight_group_sums(b_packed: torch.Tensor) -> torch.Tensor:
+    """Group-major packed weights u8 [G,N,gs/2] -> ``w_col_sum`` f32 [G,N], the sum of each group's codes (the
+    operand the reference's callers build in torch, ``int4_native_tc/profile_layer.py:96-119``)."""
+    _packed(b_packed, "b_packed")
+    _require(b_packed.dim() == 3 and b_packed.shape[2] % 4 == 0, "b_packed must be [G, N, gs/2] with gs % 8 == 0")
+    G, N, half = b_packed.shape
+    out = torch.empty((G, N), dtype=torch.float32, device=b_packed.device)
+    check(lib.i4tc_weight_group_sums(b_packed.data_ptr(), G * N, 2 * half, out.data_ptr(), _dev(out),
+                                     _stream(out)), "int4_weight_group_sums")
+    return out
+
+
 def rmsnorm_int4_quant_grouped(input: torch.Tensor, norm_weight: torch.Tensor, eps: float, group_size: int = 128):
     """RMSNorm fused in front of the grouped quantiser (no reference op; the reference's report names the fusion as
     its follow-up).  bf16 [M,K], bf16 [K] -> (packed u8 [G,M,gs/2], scale f32 [G,M]) of
@@ -231,6 +296,34 @@ cutlass_int4_fused_grouped_gemm_v7 = cutlass_int4_fused_grouped_gemm
 cutlass_int4_fused_grouped_gemm_v8 = cutlass_int4_fused_grouped_gemm
 cutlass_int4_fused_grouped_gemm_v9 = cutlass_int4_fused_grouped_gemm
 cutlass_int4_scaled_mm_grouped = cutlass_int4_fused_grouped_gemm
+
+
+def cutlass_int4_fused_grouped_gemm_azp(a_packed, b_packed, scale_a, scale_b, out, azp_adj, w_col_sum, M: int,
+                                        N: int, group_size: int, num_groups: int) -> None:
+    """Per-group-128 fused linear with the zero-point term of asymmetric activations into the caller's bf16
+    ``out`` [M,N]: ``sum_g sa*sb*(acc_g + azp_adj[g,m]*w_col_sum[g,n])``.  Reference: ``int4_gemm.cu:4298``."""
+    _packed(a_packed, "a_packed")
+    _packed(b_packed, "b_packed")
+    _same_device(a_packed, b_packed, scale_a, scale_b, out, azp_adj, w_col_sum)
+    _require(group_size == 128, "fused grouped GEMM only supports group_size=128")
+    _require(out.dtype == torch.bfloat16, "cutlass_int4_fused_grouped_gemm_azp currently supports BF16 output only")
+    _require(out.is_contiguous() and out.numel() == M * N, "out must be a contiguous [M,N] tensor")
+    _require(a_packed.numel() == num_groups * M * 64, "a_packed must be [G, M, 64]")
+    _require(b_packed.numel() == num_groups * N * 64, "b_packed must be [G, N, 64]")
+    _f32(scale_a, "scale_a", num_groups * M)
+    _f32(scale_b, "scale_b", num_groups * N)
+    _f32(azp_adj, "azp_adj", num_groups * M)
+    _f32(w_col_sum, "w_col_sum", num_groups * N)
+    check(lib.i4tc_gemm_grouped_azp(a_packed.data_ptr(), b_packed.data_ptr(), scale_a.data_ptr(),
+                                    scale_b.data_ptr(), azp_adj.data_ptr(), w_col_sum.data_ptr(), out.data_ptr(),
+                                    M, N, group_size, num_groups, _dev(out), _stream(out)),
+          "cutlass_int4_fused_grouped_gemm_azp")
+
+
+# Same contract, different kernels in the reference (int4_gemm.cu:3838, 4149, 994).
+cutlass_int4_fused_grouped_gemm_v5_azp = cutlass_int4_fused_grouped_gemm_azp
+cutlass_int4_fused_grouped_gemm_v7_azp = cutlass_int4_fused_grouped_gemm_azp
+cutlass_int4_scaled_mm_azp_grouped = cutlass_int4_fused_grouped_gemm_azp
 
 
 def int4_grouped_partials(a_packed, b_packed, M: int, N: int, num_groups: int) -> torch.Tensor:

@@ -1,22 +1,15 @@
 """Ops of the reference surface that are outside the W4A4 hot path (W4A8, W4A16, FP8 and
-asymmetric variants; ``int4_native_tc/int4_native_tc/__init__.py:86-122``).  They are exported so
+int8-activation variants; ``int4_native_tc/int4_native_tc/__init__.py:86-122``).  They are exported so
 that ``from int4_native_tc import *`` keeps working, and raise when called."""
 from __future__ import annotations
 
 UNPORTED = [
     "cutlass_w4a8_scaled_mm",
     "cutlass_w4a16_mm_grouped",
-    "cutlass_int4_scaled_mm_azp_grouped",
     "cutlass_w4a8_scaled_mm_grouped",
-    "cutlass_int4_fused_grouped_gemm_azp",
-    "cutlass_int4_fused_grouped_gemm_v5_azp",
-    "cutlass_int4_fused_grouped_gemm_v7_azp",
     "dynamic_int8_quant",
     "dequant_int4_to_bf16",
     "dequant_int4_to_fp16",
-    "dynamic_int4_quant_clipped_grouped",
-    "dynamic_int4_quant_asymmetric_grouped",
-    "dynamic_int4_quant_asymmetric_clipped_grouped",
     "dynamic_int8_quant_grouped",
     "dynamic_int8_quant_asymmetric_grouped",
     "cutlass_int4_dequant_gemm_grouped",

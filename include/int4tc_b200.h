@@ -96,6 +96,32 @@ int i4tc_quant_with_scales(const void* x, int dtype, int64_t rows, int64_t K, in
                            int64_t group_size, const float* scale, uint8_t* packed,
                            int device, void* stream);
 
+/* Per-(row, group) symmetric int4 quantise + pack whose range is the group's absmax * clip_ratio:
+ *   s = absmax * clip_ratio / 7;  q = clamp(rint(x / s), -8, 7);  scale = max(s, 1/(7*512)).
+ * Replaces dynamic_int4_quant_clipped_grouped (int4_quant.cu:906, kernel :857).  x bf16 or fp16;
+ * gs in {64,128,256}; clip_ratio in (0, 1]; packed [K/gs, rows, gs/2] (4-byte aligned); scale [K/gs, rows]. */
+int i4tc_quant_clipped_grouped(const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx,
+                               int64_t group_size, double clip_ratio, uint8_t* packed, float* scale,
+                               int device, void* stream);
+
+/* Per-(row, group) asymmetric int4 quantise + pack:
+ *   v = x (or x / smooth_scale[k] when smooth_scale != NULL: [K], same dtype as x);
+ *   c = clamp(v, -t, t) with t = max|v| * clip_ratio;  s = max((max c - min c) / 15, 1/(7*512));
+ *   azp = clamp(rint(-min c / s), 0, 15);  u = clamp(rint(c / s + azp), 0, 15);
+ *   stored nibble = u - 8 (so the GEMM sees signed codes);  azp_adj = 8 - azp.
+ * Replaces dynamic_int4_quant_asymmetric_grouped (int4_quant.cu:1262, kernel :1189; clip_ratio = 1,
+ * smooth_scale = NULL) and dynamic_int4_quant_asymmetric_clipped_grouped (int4_quant.cu:1433, kernel :1324).
+ * Outputs: packed [K/gs, rows, gs/2] (4-byte aligned), scale [K/gs, rows], azp_adj [K/gs, rows]. */
+int i4tc_quant_asymmetric_grouped(const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx,
+                                  int64_t group_size, double clip_ratio, const void* smooth_scale,
+                                  uint8_t* packed, float* scale, float* azp_adj, int device, void* stream);
+
+/* out[r] = float(sum of the signed 4-bit codes of packed row r), r < rows, each row group_size / 2 bytes:
+ * on group-major weights [G, N, gs/2] (rows = G * N) this is the w_col_sum [G, N] operand of the zero-point
+ * GEMM.  The reference computes it in torch when weights are prepared (int4_native_tc/profile_layer.py:96-119). */
+int i4tc_weight_group_sums(const uint8_t* b_packed, int64_t rows, int64_t group_size, float* out,
+                           int device, void* stream);
+
 /* packed [rows, K/2] -> int8 [rows, K] with sign extension.
  * Replaces unpack_int4_to_int8 (int4_quant.cu:593, kernel :553). */
 int i4tc_unpack_int4_to_int8(const uint8_t* packed, int64_t rows, int64_t K, int8_t* out,
@@ -124,6 +150,17 @@ int i4tc_gemm_scaled(const uint8_t* a, const uint8_t* b, const float* scale_a,
 int i4tc_gemm_grouped(const uint8_t* a, const uint8_t* b, const float* scale_a,
                       const float* scale_b, void* out, int64_t M, int64_t N,
                       int64_t group_size, int64_t num_groups, int device, void* stream);
+
+/* Per-group-128 fused linear for asymmetrically quantised activations:
+ *   out[m,n] = bf16( sum_g scale_a[g,m] * scale_b[g,n] * (acc_g[m,n] + azp_adj[g,m] * w_col_sum[g,n]) ).
+ * Replaces cutlass_int4_fused_grouped_gemm_azp and its aliases _v5_azp / _v7_azp (int4_gemm.cu:4298, 3838,
+ * 4149; epilogue term :1851-1858) and cutlass_int4_scaled_mm_azp_grouped (:994).  Same operands as
+ * i4tc_gemm_grouped plus azp_adj [G, M] and w_col_sum [G, N] (fp32).  The tensor-core kernel leaves the fp32
+ * sums of the first term in the library's workspace (M * N * 4 bytes) and a second kernel adds the rank-G
+ * second term before the one rounding to bf16; the two terms are each summed in fp32, g ascending. */
+int i4tc_gemm_grouped_azp(const uint8_t* a, const uint8_t* b, const float* scale_a, const float* scale_b,
+                          const float* azp_adj, const float* w_col_sum, void* out, int64_t M, int64_t N,
+                          int64_t group_size, int64_t num_groups, int device, void* stream);
 
 /* int32 partial sums of every group, out [G, M, N]: the integer accumulators that the fused
  * kernel drains.  No reference op exposes them; used to check the integer path bit for bit. */

@@ -19,6 +19,7 @@ __all__ = [
     "progressive_int4_gemm_grouped", "dequant_int4_grouped_to_fp8", "dequant_int4_grouped_to_fp8_with_scales",
     # additions without a reference counterpart
     "moe_sort_tokens", "moe_w4a4_grouped_gemm", "int4_quant_with_scales", "int4_grouped_partials",
+    "int4_weight_group_sums",
 ]
 for _n in __all__:
     globals()[_n] = getattr(_ops, _n)

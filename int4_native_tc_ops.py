@@ -9,11 +9,19 @@ from fp8_inference_toolkit_b200.ops import (  # noqa: F401
     cutlass_int4_fused_grouped_gemm_v7,
     cutlass_int4_fused_grouped_gemm_v8,
     cutlass_int4_fused_grouped_gemm_v9,
+    cutlass_int4_fused_grouped_gemm_azp,
+    cutlass_int4_fused_grouped_gemm_v5_azp,
+    cutlass_int4_fused_grouped_gemm_v7_azp,
+    cutlass_int4_scaled_mm_azp_grouped,
     dynamic_int4_quant,
     static_int4_weight_quant,
     unpack_int4_to_int8,
     static_int4_weight_quant_grouped,
     dynamic_int4_quant_grouped,
+    dynamic_int4_quant_clipped_grouped,
+    dynamic_int4_quant_asymmetric_grouped,
+    dynamic_int4_quant_asymmetric_clipped_grouped,
+    int4_weight_group_sums,
     int4_quant_with_scales,
     int4_grouped_partials,
 )

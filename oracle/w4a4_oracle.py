@@ -135,6 +135,72 @@ def quant_with_scales(x, scale: np.ndarray, group_size: int | None = None) -> np
     return np.ascontiguousarray(np.clip(q, -8, 7).astype(np.int8))
 
 
+def _grouped_view(x, group_size: int, smooth_scale=None) -> np.ndarray:
+    """[R,K] -> fp32 [G,R,gs]; divides by ``smooth_scale[k]`` first when given (IEEE fp32)."""
+    xf = _to_f32(x)
+    if smooth_scale is not None:
+        xf = (xf / _to_f32(smooth_scale)[None, :]).astype(F32)
+    R, K = xf.shape
+    assert K % group_size == 0 and group_size % 2 == 0
+    return np.ascontiguousarray(xf.reshape(R, K // group_size, group_size).transpose(1, 0, 2))
+
+
+def quant_clipped_grouped(x, group_size: int = GROUP, clip_ratio: float = 1.0):
+    """Per-(row, group) symmetric int4 whose range is ``absmax * clip_ratio``
+    (``dynamic_int4_quant_clipped_grouped``, ``int4_quant.cu:857-903``): values beyond the
+    clipped range saturate at -8 / 7 (``:898-901``), the returned scale is floored
+    (``:889``).  Division form, like ``quant_codes``.  **Parity unpinned** (the reference has
+    no golden vector for it).  Returns (codes int8 [G,R,gs], scale f32 [G,R])."""
+    xg = _grouped_view(x, group_size)
+    cm = (np.abs(xg).max(axis=2) * F32(clip_ratio)).astype(F32)
+    codes = quant_codes(xg, cm[:, :, None])
+    s = (cm / F32(7.0)).astype(F32)
+    return np.ascontiguousarray(codes), np.maximum(s, K_MIN_SCALE).astype(F32)
+
+
+def quant_asymmetric_grouped(x, group_size: int = GROUP, clip_ratio: float = 1.0, smooth_scale=None):
+    """Per-(row, group) asymmetric int4 (``dynamic_int4_quant_asymmetric_grouped``,
+    ``int4_quant.cu:1189-1259``; with clipping and SmoothQuant division
+    ``dynamic_int4_quant_asymmetric_clipped_grouped``, ``:1324-1430``):
+
+    ``c = clamp(v, -t, t)``, ``t = max|v| * clip_ratio``; ``s = max((max c - min c)/15, floor)``;
+    ``azp = clamp(rint(-min c / s), 0, 15)``; ``u = clamp(rint(c / s + azp), 0, 15)``; the stored
+    code is ``u - 8`` (``:1181-1186``) and ``azp_adj = 8 - azp`` (``:1237``).  The kernel multiplies by
+    ``1/s`` under fast-math; the reference's torch restatement divides
+    (``int4_native_tc/test_enhanced_quantization.py:262-268``) and that IEEE form is used here.
+    **Parity unpinned.**  Returns (codes int8 [G,R,gs] in [-8,7], scale f32 [G,R], azp_adj f32 [G,R])."""
+    xg = _grouped_view(x, group_size, smooth_scale)
+    t = (np.abs(xg).max(axis=2) * F32(clip_ratio)).astype(F32)[:, :, None]
+    c = np.minimum(np.maximum(xg, -t), t).astype(F32)
+    mn = c.min(axis=2)
+    mx = c.max(axis=2)
+    s = np.maximum(((mx - mn).astype(F32) / F32(15.0)).astype(F32), K_MIN_SCALE).astype(F32)
+    azp = np.clip(np.rint(((-mn).astype(F32) / s).astype(F32)), 0.0, 15.0).astype(F32)
+    y = ((c / s[:, :, None]).astype(F32) + azp[:, :, None]).astype(F32)
+    u = np.clip(np.rint(y), 0.0, 15.0)
+    return np.ascontiguousarray((u - 8.0).astype(np.int8)), s, (F32(8.0) - azp).astype(F32)
+
+
+def weight_group_sums(b_codes: np.ndarray) -> np.ndarray:
+    """``w_col_sum[g,n] = sum_k codes[g,n,k]`` as fp32 (exact; ``int4_gemm.cu:991``)."""
+    return np.asarray(b_codes).astype(np.int32).sum(axis=-1).astype(F32)
+
+
+def linear_grouped_azp_f32(a_codes, b_codes, scale_a, scale_b, azp_adj, w_col_sum) -> np.ndarray:
+    """Per-group linear with the zero-point term, before the final cast, in the reference's order:
+    ``f += ((float(acc_g) + azp_adj[g,m] * w_col_sum[g,n]) * sx[g,m]) * sw[g,n]``
+    (``int4_gemm.cu:1851-1858``).  The bracket is an exact integer below 2**24."""
+    G, M, _ = a_codes.shape
+    N = b_codes.shape[1]
+    f = np.zeros((M, N), dtype=F32)
+    for g in range(G):
+        acc = int_gemm(a_codes[g], b_codes[g]).astype(F32)
+        acc = (acc + (azp_adj[g].astype(F32)[:, None] * w_col_sum[g].astype(F32)[None, :]).astype(F32)).astype(F32)
+        t = (acc * scale_a[g].astype(F32)[:, None]).astype(F32)
+        f = (f + (t * scale_b[g].astype(F32)[None, :]).astype(F32)).astype(F32)
+    return f
+
+
 def quant_codes_refcuda_form(xf: np.ndarray, absmax: np.ndarray) -> np.ndarray:
     """The reference CUDA kernel's formulation ``rint(x * (7/absmax))`` evaluated
     in IEEE fp32 (``int4_quant.cu:146,160-163``).  Informational only: used to
