@@ -1,9 +1,9 @@
 // Clipped, asymmetric and smoothed per-group activation quantisers, the per-group sums of weight codes, and
 // the zero-point pass that finishes a per-group linear whose activations were quantised asymmetrically.
 //
-// Quantisers: one warp owns one (row, K-group) slice; a lane keeps its gs/32 consecutive elements in
-// registers between the reductions (warp shuffles) and the quantise step, so the input is read once; a warp
-// writes gs/2 contiguous bytes.  The reference launches one 256-thread block per slice and reads it two or
+// Quantisers: a warp works on four (row, K-group) slices at a time, all 32 lanes on each; a lane keeps its
+// gs/32 consecutive elements of every slice in registers between the reductions (warp shuffles) and the quantise
+// step, so the input is read once; per slice the warp writes gs/2 contiguous bytes.  The reference launches one 256-thread block per slice and reads it two or
 // three times (int4_native_tc/csrc/int4_quant.cu:857-903, 1189-1259, 1324-1430).
 //
 // Code arithmetic (shared with the CPU oracle; IEEE fp32, round-half-even, no contraction):
@@ -60,92 +60,122 @@ __device__ __forceinline__ void load_elems(const T* src, bool vec, float (&v)[EP
   }
 }
 
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-__device__ __forceinline__ float warp_min(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
+// clamp(rint(v / s + off), lo, hi) + 1.5 * 2^23: the code sits in the low mantissa bits (two's complement).
+// Fast path (the caller guarantees |v / s + off| < 64): one FMA with r ~ 1/s (rcp.approx, within 2^-23) lies
+// within 3e-5 of the two-rounding IEEE value, so unless it is within 1e-4 of a rounding boundary both round to
+// the same integer; the rounding itself is an add and a subtract of 1.5 * 2^23 (round-half-even, no conversion
+// instructions, which issue at a quarter of the FMA rate).  Everything else takes the IEEE division.
+__device__ __forceinline__ uint32_t code_bits(float v, float s, float r, bool fast, float off, float lo, float hi) {
+  constexpr float kMagic = 12582912.0f;
+  const float y = fmaf(v, r, off);
+  float q = __fadd_rn(__fadd_rn(y, kMagic), -kMagic);
+  if (!fast || !(fabsf(__fsub_rn(y, q)) < 0.4999f)) q = rintf(__fadd_rn(__fdiv_rn(v, s), off));
+  q = fminf(fmaxf(q, lo), hi);
+  return __float_as_uint(__fadd_rn(q, kMagic));
 }
 
-// clamp(rint(v / s + off), lo, hi).  Fast path: one FMA with r ~ 1/s (rcp.approx, within 2^-23); for
-// |y| < 64 it lies within 3e-5 of the two-rounding IEEE value, so unless y is within 1e-4 of a rounding
-// boundary both round to the same integer.  Everything else takes the IEEE division.
-__device__ __forceinline__ float code_of(float v, float s, float r, bool fast, float off, float lo, float hi) {
-  float y = fmaf(v, r, off);
-  float q = rintf(y);
-  if (!fast || !(fabsf(y - q) < 0.4999f) || !(fabsf(y) < 64.0f)) q = rintf(__fadd_rn(__fdiv_rn(v, s), off));
-  return fminf(fmaxf(q, lo), hi);
-}
+constexpr int kSlicesPerWarp = 4;   // (row, group) slices a warp has in flight per iteration
 
 template <typename T, int EPL, bool ASYM>
-__global__ void __launch_bounds__(256) quant_ext_kernel(const T* __restrict__ x, long long rows, int G, long long ldx,
+__global__ void __launch_bounds__(256) quant_ext_kernel(const T* __restrict__ x, unsigned rows, unsigned G, long long ldx,
                                                         float clip, const T* __restrict__ smooth, bool vec_x,
                                                         bool vec_s, uint8_t* __restrict__ packed,
                                                         float* __restrict__ scale, float* __restrict__ azp_adj) {
   constexpr int GS = EPL * 32;
+  constexpr int U = kSlicesPerWarp;
   const int lane = threadIdx.x & 31;
-  const long long items = rows * G;
-  for (long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); w < items; w += (long long)gridDim.x * 8) {
-    const long long row = w / G;
-    const int g = (int)(w - row * G);
-    float v[EPL];
-    load_elems<T, EPL>(x + row * ldx + (long long)g * GS + lane * EPL, vec_x, v);
-    if (smooth != nullptr) {
-      float sm[EPL];
-      load_elems<T, EPL>(smooth + (long long)g * GS + lane * EPL, vec_s, sm);
+  const unsigned items = rows * G;   // < 2^31, checked by the host
+  for (unsigned w0 = (blockIdx.x * 8u + (threadIdx.x >> 5)) * U; w0 < items; w0 += gridDim.x * 8u * U) {
+    float v[U][EPL];
+    unsigned row[U], grp[U];
+    // consecutive slices (same row, next group) are adjacent in memory; all loads are issued before anything
+    // depends on them
+    {
+      unsigned r0 = w0 / G, g0 = w0 - r0 * G;
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) v[i] = __fdiv_rn(v[i], sm[i]);
+      for (int u = 0; u < U; ++u) {
+        row[u] = r0;
+        grp[u] = g0;
+        if (++g0 == G) { g0 = 0; ++r0; }
+        if (w0 + u < items) {
+          load_elems<T, EPL>(x + (long long)row[u] * ldx + (long long)grp[u] * GS + lane * EPL, vec_x, v[u]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) v[u][i] = 0.0f;
+        }
+      }
     }
-    float amax = 0.0f;
+    if (smooth != nullptr) {
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = warp_max(amax);
-    const float thr = __fmul_rn(amax, clip);
-
-    float s, off, lo, hi, out_scale;
-    bool zero = false;
-    if (ASYM) {
-      float mn = INFINITY, mx = -INFINITY;
+      for (int u = 0; u < U; ++u) {
+        if (w0 + u >= items) continue;
+        float sm[EPL];
+        load_elems<T, EPL>(smooth + (long long)grp[u] * GS + lane * EPL, vec_s, sm);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) v[u][i] = __fdiv_rn(v[u][i], sm[i]);
+      }
+    }
+    // reductions of the U slices side by side (independent shuffle chains)
+    float mn[U], mx[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      mn[u] = INFINITY; mx[u] = -INFINITY;
 #pragma unroll
       for (int i = 0; i < EPL; ++i) {
-        v[i] = fminf(fmaxf(v[i], -thr), thr);
-        mn = fminf(mn, v[i]);
-        mx = fmaxf(mx, v[i]);
+        mn[u] = fminf(mn[u], v[u][i]);
+        mx[u] = fmaxf(mx[u], v[u][i]);
       }
-      mn = warp_min(mn);
-      mx = warp_max(mx);
-      s = fmaxf(__fdiv_rn(__fsub_rn(mx, mn), 15.0f), ext_min_scale());
-      off = fminf(fmaxf(rintf(__fdiv_rn(-mn, s)), 0.0f), 15.0f);
-      lo = 0.0f; hi = 15.0f;
-      out_scale = s;
-    } else {
-      s = __fdiv_rn(thr, 7.0f);
-      zero = !(s > 0.0f);
-      off = 0.0f; lo = -8.0f; hi = 7.0f;
-      out_scale = fmaxf(s, ext_min_scale());
-      if (zero) s = 1.0f;
     }
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(s));
-    const bool fast = (r > 1e-30f) && (r < 1e30f);
-    uint32_t word = 0;
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      const float q = zero ? 0.0f : code_of(v[i], s, r, fast, off, lo, hi);
-      const uint32_t nib = ASYM ? ((uint32_t)(int)q ^ 8u) : ((uint32_t)(int)q & 0xFu);   // u - 8 == u ^ 8 as a nibble
-      word |= (nib & 0xFu) << (4 * i);
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        mn[u] = fminf(mn[u], __shfl_xor_sync(0xffffffffu, mn[u], o));
+        mx[u] = fmaxf(mx[u], __shfl_xor_sync(0xffffffffu, mx[u], o));
+      }
     }
-    uint8_t* dst = packed + ((long long)g * rows + row) * (GS / 2) + lane * (EPL / 2);
-    if constexpr (EPL == 2) *dst = (uint8_t)word;
-    else if constexpr (EPL == 4) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)word;
-    else *reinterpret_cast<uint32_t*>(dst) = word;
-    if (lane == 0) {
-      scale[(long long)g * rows + row] = out_scale;
-      if (ASYM) azp_adj[(long long)g * rows + row] = 8.0f - off;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (w0 + u >= items) continue;   // warp-uniform
+      // max|v| = max(-min, max); clamping to [-t, t] is monotone, so the clamped extremes are the clamped raw ones
+      const float thr = __fmul_rn(fmaxf(-mn[u], mx[u]), clip);
+      float s, off, out_scale;
+      bool zero = false;
+      if (ASYM) {
+        const float cmn = fminf(fmaxf(mn[u], -thr), thr), cmx = fminf(fmaxf(mx[u], -thr), thr);
+        s = fmaxf(__fdiv_rn(__fsub_rn(cmx, cmn), 15.0f), ext_min_scale());
+        off = fminf(fmaxf(rintf(__fdiv_rn(-cmn, s)), 0.0f), 15.0f);
+        out_scale = s;
+      } else {
+        s = __fdiv_rn(thr, 7.0f);
+        zero = !(s > 0.0f);
+        off = 0.0f;
+        out_scale = fmaxf(s, ext_min_scale());
+        if (zero) s = 1.0f;
+      }
+      const float lo = ASYM ? 0.0f : -8.0f, hi = ASYM ? 15.0f : 7.0f;
+      float r;
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(s));
+      // fast path only while every |v / s + off| of the slice stays below 64 (the error bound of code_bits);
+      // an unclipped symmetric slice may exceed the clip range by 1 / clip_ratio
+      const float vmax = ASYM ? thr : fmaxf(-mn[u], mx[u]);
+      const bool fast = (r > 1e-30f) && (r < 1e30f) && (vmax * r < 48.0f);
+      const long long slot = (long long)grp[u] * rows + row[u];
+      if (lane == 0) {
+        scale[slot] = out_scale;
+        if (ASYM) azp_adj[slot] = 8.0f - off;
+      }
+      uint32_t word = 0;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const float c = ASYM ? fminf(fmaxf(v[u][i], -thr), thr) : v[u][i];
+        const uint32_t bits = zero ? 0u : code_bits(c, s, r, fast, off, lo, hi);
+        word |= ((ASYM ? bits ^ 8u : bits) & 0xFu) << (4 * i);   // u - 8 == u ^ 8 as a nibble
+      }
+      uint8_t* dst = packed + slot * (GS / 2) + lane * (EPL / 2);
+      if constexpr (EPL == 2) *dst = (uint8_t)word;
+      else if constexpr (EPL == 4) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)word;
+      else *reinterpret_cast<uint32_t*>(dst) = word;
     }
   }
 }
@@ -155,16 +185,17 @@ int launch_ext_t(const T* x, long long rows, long long K, long long ldx, int gs,
                  uint8_t* packed, float* scale, float* azp_adj, int sm_count, cudaStream_t st) {
   const int G = (int)(K / gs);
   const long long items = rows * G;
-  long long blocks = (items + 7) / 8;
+  I4TC_REQUIRE(items < (1ll << 31) - (1ll << 20), I4TC_EINVAL, "rows * groups too large");
+  long long blocks = (items + 8 * kSlicesPerWarp - 1) / (8 * kSlicesPerWarp);
   const long long cap = (long long)sm_count * 8;
   if (blocks > cap) blocks = cap;
   const int epl = gs / 32;
   const bool vec_x = aligned_to(x, 2 * epl) && (ldx % epl == 0);
   const bool vec_s = smooth == nullptr || aligned_to(smooth, 2 * epl);
   switch (epl) {
-    case 2: quant_ext_kernel<T, 2, ASYM><<<(unsigned)blocks, 256, 0, st>>>(x, rows, G, ldx, clip, smooth, vec_x, vec_s, packed, scale, azp_adj); break;
-    case 4: quant_ext_kernel<T, 4, ASYM><<<(unsigned)blocks, 256, 0, st>>>(x, rows, G, ldx, clip, smooth, vec_x, vec_s, packed, scale, azp_adj); break;
-    default: quant_ext_kernel<T, 8, ASYM><<<(unsigned)blocks, 256, 0, st>>>(x, rows, G, ldx, clip, smooth, vec_x, vec_s, packed, scale, azp_adj); break;
+    case 2: quant_ext_kernel<T, 2, ASYM><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, (unsigned)rows, (unsigned)G, ldx, clip, smooth, vec_x, vec_s, packed, scale, azp_adj); break;
+    case 4: quant_ext_kernel<T, 4, ASYM><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, (unsigned)rows, (unsigned)G, ldx, clip, smooth, vec_x, vec_s, packed, scale, azp_adj); break;
+    default: quant_ext_kernel<T, 8, ASYM><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, (unsigned)rows, (unsigned)G, ldx, clip, smooth, vec_x, vec_s, packed, scale, azp_adj); break;
   }
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
