@@ -61,8 +61,9 @@ int launch_split_reduce_scaled(const float* ws, long long stride, int splits, lo
 
 // cta_pair: pairs of CTAs compute 256 x 256 tiles (dense, unswapped, bn = 256, even grid; p.num_p_tiles counts
 // 256-row tiles and tmQ has 128-row boxes).
+// epi_warps: 8 or 16 epilogue warps per CTA (16 needs bn >= 128).
 int launch_w4a4_gemm(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int bn, int grid,
-                     bool cta_pair, cudaStream_t st);
+                     bool cta_pair, int epi_warps, cudaStream_t st);
 
 // CUDA-core weight-streaming kernel for M <= 8 tokens (per-group or per-channel scales, 16-bit output).
 // x / w are the packed operands in either layout (rowmajor: [rows, G * 64]; else [G, rows, 64]).

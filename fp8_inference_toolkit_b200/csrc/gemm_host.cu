@@ -10,6 +10,13 @@ static int g_force_swap = -1; // -1 = choose automatically
 static int g_force_splits = 0; // 0 = choose automatically, 1 = never split, n = n K ranges
 static int g_cta_pairs = -1;   // -1 = choose automatically, 0 = never, 1 = whenever the problem allows it
 static bool g_pairs_launchable = true;   // cleared when an automatic cluster launch was refused
+static int g_epi_warps = 0;    // 0 = choose automatically, 8 or 16
+
+static int epi_warps_for(int epi_mode) {
+  if (g_epi_warps) return g_epi_warps;
+  (void)epi_mode;
+  return 8;
+}
 
 struct Shape {
   int bn;
@@ -186,7 +193,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
     GemmParams pp = p;
     pp.num_p_tiles = (int)((prow + 255) / 256);
     const int grid = 2 * (int)(pair_tiles < clusters_max ? pair_tiles : clusters_max);
-    const int rc = launch_w4a4_gemm(pp, tmP, tmQ, sh.bn, grid, true, static_cast<cudaStream_t>(stream));
+    const int rc = launch_w4a4_gemm(pp, tmP, tmQ, sh.bn, grid, true, epi_warps_for(d.epi_mode), static_cast<cudaStream_t>(stream));
     if (rc == I4TC_OK) return finish();
     if (g_cta_pairs == 1) return rc;   // the caller asked for pairs: report why they cannot run
     // an environment that cannot launch clusters of two (a restricted SM partition, for instance): the launch
@@ -197,7 +204,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   if (int rc = get_tensor_map(device, qbase, d.rowmajor, qrow, extent, sh.bn, &tmQ)) return rc;
   const long long items = tiles * p.splits;
   const int grid = (int)(items < info->sm_count ? items : info->sm_count);
-  if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, false, static_cast<cudaStream_t>(stream))) return rc;
+  if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, false, epi_warps_for(d.epi_mode), static_cast<cudaStream_t>(stream))) return rc;
   if (d.azp_adj != nullptr) return finish();
   if (p.splits > 1) {
     if (d.epi_mode == EPI_CHANNEL)
@@ -237,6 +244,12 @@ extern "C" int i4tc_set_split_k(int splits) {
 extern "C" int i4tc_set_cta_pairs(int mode) {
   I4TC_REQUIRE(mode >= -1 && mode <= 1, I4TC_EINVAL, "mode must be -1 (automatic), 0 or 1");
   g_cta_pairs = mode;
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_set_epilogue_warps(int warps) {
+  I4TC_REQUIRE(warps == 0 || warps == 8 || warps == 16, I4TC_EINVAL, "warps must be 0 (automatic), 8 or 16");
+  g_epi_warps = warps;
   return I4TC_OK;
 }
 
@@ -346,5 +359,5 @@ extern "C" int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, con
   // upper bound on tiles: every expert may add one partial row tile
   const long long max_tiles = ((num_pairs + 127) / 128 + num_experts) * p.num_q_tiles;
   const int grid = (int)(max_tiles < info->sm_count ? max_tiles : info->sm_count);
-  return launch_w4a4_gemm(p, tmP, tmQ, bn, grid, false, static_cast<cudaStream_t>(stream));
+  return launch_w4a4_gemm(p, tmP, tmQ, bn, grid, false, epi_warps_for(EPI_GROUP), static_cast<cudaStream_t>(stream));
 }

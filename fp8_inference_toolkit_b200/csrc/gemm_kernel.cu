@@ -13,13 +13,18 @@
 // 32-code chunk land in different 16-byte K slots; A and B use the same permutation, and integer
 // sums do not depend on the order of k.
 //
-// Roles (512 threads):
+// Roles (512 or 768 threads):
 //   warp 0      TMA producer: packed P (128 x 64 B) and Q (BN x 64 B) tiles, one K group per stage
 //   warp 1      MMA issuer (one thread runs the whole loop) and owner of the TMEM allocation
 //   warps 2-3   per-group mode: copy the row and column scales of each K group into a ring in shared memory
 //   warps 4-7   converters: packed stage -> 128B-swizzled K-major int8 stage
-//   warps 8-15  epilogue: tcgen05.ld, int32 -> fp32, scales, fp32 accumulation across groups, store
+//   warps 8-..  epilogue (8 or 16 warps): tcgen05.ld, int32 -> fp32, scales, fp32 accumulation across groups, store
 // Two to four TMEM accumulators (BN columns each) let later groups be multiplied while one is drained.
+// The MMA thread's loop is the serial path of the kernel (an MMA costs it ~50 cycles, a commit ~48, a barrier probe
+// 150-200), so it does the least possible per K group: two overlapped probes (operands converted, accumulator free),
+// four MMAs and ONE commit.  With a flush per group that commit's barrier tells the converters "stage free" and the
+// epilogue "accumulator full" at once; in a CTA pair it arrives in both CTAs (tcgen05.commit multicast).  The scale
+// stages are waited for by the epilogue warps, not by this thread.
 // CG = 2: two CTAs on neighbouring SMs share a 256 x 256 tile (tcgen05.mma.cta_group::2 issued by the first
 // one); each stages and converts its own 128 rows of P and only half of the Q rows.
 // Every wait is bounded: on expiry the kernel sets bit 0 of the status word, all roles leave
@@ -34,31 +39,44 @@ using namespace ptx;
 constexpr int kBM = 128;             // rows of the P tile == TMEM lanes
 constexpr int kPackedRow = 64;       // bytes of one packed row of one group
 constexpr int kI8Row = 128;          // bytes of one int8 row of one group (the swizzle width)
-constexpr int kThreads = 512;
 constexpr int kConvWarp0 = 4, kConvWarps = 4;
-constexpr int kEpiWarp0 = 8, kEpiWarps = 8;
+constexpr int kEpiWarp0 = 8;
 constexpr int kNS = 4;               // scale stages (per-group epilogue)
 constexpr int kScaleWarp0 = 2, kScaleWarps = 2;
-// register budgets per role (whole warpgroups): 128*56 + 128*72 + 256*192 = 65536
-constexpr int kRegsWg0 = 56, kRegsConv = 72, kRegsEpi = 192;
+// Register budgets per role (whole warpgroups), within what the launch allocates (threads x registers per thread):
+//   8 epilogue warps, 512 threads x 128: 128*56 + 128*72 + 256*192 = 65536
+//  16 epilogue warps, 768 threads x  80: 128*32 + 128*40 + 512*102 -> 104: 128*24 + 128*40 + 512*104 = 61440
+template <int EW> struct Regs;
+template <> struct Regs<8> { static constexpr int WG0 = 56, CONV = 64, EPI = 192; static constexpr bool PIPE = false; };
+template <> struct Regs<16> { static constexpr int WG0 = 24, CONV = 40, EPI = 104; static constexpr bool PIPE = false; };
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
 // CG = 1: one CTA computes a 128 x BN tile.  CG = 2: a pair of CTAs (a cluster of two SMs) computes a
 // 256 x BN tile with tcgen05.mma.cta_group::2; each CTA stages its own 128 P rows and only BN / 2 rows of
 // the Q operand, so a third less is converted and moved through shared memory per unit of MMA work.
-template <int BN, int CG = 1>
+// EW = number of epilogue warps (8 or 16): a drain is a chain of TMEM round trips and dependent conversions, so
+// four warps per scheduler hide what two cannot; 16 warps hold BN / 4 columns of running sums each.
+template <int BN, int CG = 1, int EW = 8>
 struct Cfg {
+  static_assert(EW == 8 || EW == 16, "8 or 16 epilogue warps");
+  static_assert(BN / (EW / 4) >= 32, "an epilogue warp drains at least one 32-column chunk");
+  static constexpr int EPI_WARPS = EW;
+  static constexpr int THREADS = (kEpiWarp0 + EW) * 32;
   static constexpr int QR = BN / CG;                                   // Q rows staged by this CTA
-  static constexpr int NP = (CG == 2) ? 4 : ((BN >= 256) ? 5 : 6);     // packed stages
-  static constexpr int NI = (CG == 2) ? 4 : (BN >= 256 ? 2 : (BN >= 128 ? 3 : 4));   // int8 stages
+  static constexpr int NP = (CG == 2) ? 4 : ((BN >= 128) ? 5 : 6);     // packed stages
+  static constexpr int NI = (CG == 2) ? 4 : (BN >= 256 ? 2 : 4);       // int8 stages
   // TMEM accumulators: as many as fit in the 512 columns (at most 4), so that narrow tiles -- whose K loop is a
   // chain of short handshakes -- find a free accumulator and a converted stage without waiting
   static constexpr int NT = (BN >= 256) ? 2 : 4;
+  // With a flush per group the epilogue waits on the barrier ring of the int8 stages.  Group j + NI can only be
+  // multiplied after group j + NI - NT was drained, so with NI >= NT a barrier never completes a second phase
+  // before the epilogue has seen the first.
+  static_assert(NI >= NT, "the int8 stage ring must be at least as deep as the accumulator ring");
   static constexpr int PK_P = kBM * kPackedRow;                        // 8 KB
   static constexpr int PK_Q = QR * kPackedRow;
   static constexpr int I8_P = kBM * kI8Row;                            // 16 KB
   static constexpr int I8_Q = QR * kI8Row;
-  static constexpr int COLS_PER_WARP = BN / 2;                         // epilogue columns per thread
+  static constexpr int COLS_PER_WARP = BN / (EW / 4);                  // epilogue columns per warp
   static constexpr int TMEM_COLS = NT * BN;                            // 256 or 512: a power of two >= 32
   // shared memory layout (offsets from a 1024-byte aligned base)
   static constexpr int OFF_I8 = 0;
@@ -67,10 +85,9 @@ struct Cfg {
   // the one-flush epilogues use the start of the same region for their per-warp column scales
   static constexpr int OFF_SQ = OFF_PK + NP * (PK_P + PK_Q);
   static constexpr int SCALE_STAGE = (kBM + BN) * 4;                  // bytes
-  static constexpr int SQ_BYTES = (kNS * SCALE_STAGE > kEpiWarps * 2 * COLS_PER_WARP * 4) ? kNS * SCALE_STAGE
-                                                                                          : kEpiWarps * 2 * COLS_PER_WARP * 4;
+  static constexpr int SQ_BYTES = (kNS * SCALE_STAGE > EW * COLS_PER_WARP * 4) ? kNS * SCALE_STAGE : EW * COLS_PER_WARP * 4;
   static constexpr int OFF_BAR = OFF_SQ + SQ_BYTES;
-  static constexpr int NUM_BARS = 2 * NP + 2 * NI + 2 * NT + 3 * kNS;
+  static constexpr int NUM_BARS = 2 * NP + 2 * NI + 2 * NT + 2 * kNS;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // tmem ptr, abort flag
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;              // + alignment slack
 };
@@ -329,18 +346,18 @@ __device__ __forceinline__ void store_pair(OutT* out, long long ldc, int prow, i
 // Scales.  Two otherwise idle warps copy the kBM row scales and BN column scales of each K group from
 // global to shared memory (4-byte cp.async, kNS stages ahead, completion signalled on an mbarrier), so the
 // epilogue warps spend no instructions or registers on global addresses.
-template <int BN, typename OutT, bool SWAP, int CG>
+template <int BN, typename OutT, bool SWAP, int CG, int EW>
 __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
-                                               uint32_t bar_tm_full, uint32_t bar_tm_empty, uint32_t bar_sc_empty,
-                                               volatile int* abort_flag) {
-  using C = Cfg<BN, CG>;
+                                               uint32_t bar_done, uint32_t bar_tm_empty, uint32_t bar_sc_full,
+                                               uint32_t bar_sc_empty, volatile int* abort_flag) {
+  using C = Cfg<BN, CG, EW>;
   constexpr int CW = C::COLS_PER_WARP;
   constexpr int NCH = CW / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ew = warp - kEpiWarp0;
   const int quad = warp & 3;         // TMEM lane quarter this warp may access
-  const int half = ew >> 2;          // which half of the BN columns
-  const int col_base = half * CW;
+  const int part = ew >> 2;          // which CW-wide part of the BN columns
+  const int col_base = part * CW;
   const int lq = lane & 3, lr = lane >> 2;
   const float* sc = reinterpret_cast<const float*>(smem + C::OFF_SQ);
   // order of the two multiplies: normal (p = m): (acc * sp) * sq ; swapped (p = n): (acc * sq) * sp.
@@ -356,17 +373,34 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
 #pragma unroll
     for (int i = 0; i < CW / 2; ++i) f[i] = make_float2(0.f, 0.f);
     bool ok = true;
-    bool probed = false;   // the next accumulator was already seen full by a probe issued under the last slab's math
+    // Software pipeline over the slabs: the load of slab u + 1 is in flight while slab u is folded in, and the first
+    // slab of the next group is requested under the last slab of this one (when its accumulator and scales are
+    // already there), so a warp's drain is not a chain of TMEM round trips.  rb[u & 1] holds slab u; a group has
+    // an even number of slabs, so every group starts in rb[0].
+    constexpr int S = 2 * NCH;
+    constexpr bool PIPE = Regs<EW>::PIPE;   // the second slab buffer needs 16 more registers
+    uint32_t rb[PIPE ? 2 : 1][16];
+    bool pre = false;      // the first slab of group `flush` was requested under the previous group's last slab
     for (int g = ti.g0; g < ti.g1; ++g) {
-      // the MMA warp waited for this scale stage (in a CTA pair: for both CTAs' stages) before it issued the
-      // group, so an accumulator that is full implies scales that have landed
+      // group number `flush` is done when the commit behind its MMAs arrives on the barrier of its int8 stage
+      // (the one the converters wait for before they reuse the stage); its scales have their own ring
       const uint32_t ss = flush % kNS;
       const uint32_t buf = flush % C::NT;
-      if (!__all_sync(0xffffffffu, probed)) {
-        ok = wait_bar(bar_tm_full + buf * 8, (flush / C::NT) & 1u, abort_flag);
-        if (!ok) break;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
+      if (!pre) {
+        const uint32_t b_done = bar_done + (flush % C::NI) * 8, p_done = (flush / C::NI) & 1u;
+        const uint32_t b_sc = bar_sc_full + ss * 8, p_sc = (flush / kNS) & 1u;
+        // both probes in flight together; the one-at-a-time waits run only if something is missing
+        const bool ready = mbar_test_wait(b_sc, p_sc) & mbar_test_wait(b_done, p_done);
+        if (!__all_sync(0xffffffffu, ready)) {
+          ok = wait_bar(b_done, p_done, abort_flag);
+          if (!ok) break;
+          ok = wait_bar(b_sc, p_sc, abort_flag);
+          if (!ok) break;
+        }
+        tc_fence_after_sync();
+        if (PIPE) tmem_ld_16x256b_x4(taddr, rb[0]);
       }
-      tc_fence_after_sync();
       const float* st_p = sc + ss * (C::SCALE_STAGE / 4) + quad * 32;         // this warp's 32 row scales
       const float* st_q = sc + ss * (C::SCALE_STAGE / 4) + kBM + col_base;    // this warp's CW column scales
       float2 sp2[4];
@@ -375,22 +409,31 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
         const float v = st_p[8 * a + lr] * kInv256;
         sp2[a] = make_float2(v, v);
       }
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
 #pragma unroll
-      for (int u = 0; u < 2 * NCH; ++u) {
+      for (int u = 0; u < S; ++u) {
         const int c = u >> 1, sl = u & 1;
-        uint32_t r[16];
-        tmem_ld_16x256b_x4(taddr + ((uint32_t)(sl * 16) << 16) + c * 32, r);
-        tmem_ld_wait();
-        if (u == 2 * NCH - 1) {
+        if (!PIPE) tmem_ld_16x256b_x4(taddr + ((uint32_t)(sl * 16) << 16) + c * 32, rb[0]);
+        tmem_ld_wait();   // slab u has arrived in rb[u & 1]
+        if (u + 1 < S) {
+          if (PIPE) tmem_ld_16x256b_x4(taddr + ((uint32_t)(((u + 1) & 1) * 16) << 16) + ((u + 1) >> 1) * 32, rb[(u + 1) & 1]);
+        } else {
           // all of this warp's part of the buffer is in registers: hand it back to the MMA warp
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) arrive_bar<CG>(bar_tm_empty + buf * 8);
-          // a probe of a completed barrier costs 150-200 cycles: ask about the next accumulator now, the answer
-          // arrives while the last slab is folded in
-          probed = (g + 1 < ti.g1) && mbar_test_wait(bar_tm_full + ((flush + 1) % C::NT) * 8, ((flush + 1) / C::NT) & 1u);
+          pre = false;
+          if (g + 1 < ti.g1) {
+            const uint32_t nf = flush + 1;
+            const bool ready = mbar_test_wait(bar_done + (nf % C::NI) * 8, (nf / C::NI) & 1u) &
+                               mbar_test_wait(bar_sc_full + (nf % kNS) * 8, (nf / kNS) & 1u);
+            if (__all_sync(0xffffffffu, ready)) {
+              tc_fence_after_sync();
+              if (PIPE) tmem_ld_16x256b_x4(tmem_base + ((uint32_t)(quad * 32) << 16) + (nf % C::NT) * BN + col_base, rb[0]);
+              pre = true;
+            }
+          }
         }
+        const uint32_t (&r)[16] = rb[PIPE ? (u & 1) : 0];
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const float2 sq = *reinterpret_cast<const float2*>(st_q + c * 32 + kk * 8 + lq * 2);
@@ -409,6 +452,7 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
       if (lane == 0) mbar_arrive(bar_sc_empty + ss * 8);
       ++flush;
     }
+    if (PIPE && pre) tmem_ld_wait();   // never taken: a request is only made when another group of this tile follows
     if (!ok) break;
     // ---- write the tile: thread owns rows 8a + lr, column pairs c * 32 + kk * 8 + 2 lq ----
     OutT* out = static_cast<OutT*>(p.out);
@@ -465,18 +509,18 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
 
 // One flush per tile with per-channel scales: out = cast((acc * scale_b[n]) * scale_a[m]), the
 // reference's order.  Same slab register layout and quad-transposed stores as the per-group epilogue.
-template <int BN, typename OutT, bool SWAP, int CG>
+template <int BN, typename OutT, bool SWAP, int CG, int EW>
 __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
                                                  uint32_t bar_tm_full, uint32_t bar_tm_empty,
                                                  volatile int* abort_flag) {
-  using C = Cfg<BN, CG>;
+  using C = Cfg<BN, CG, EW>;
   constexpr int CW = C::COLS_PER_WARP;
   constexpr int NCH = CW / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ew = warp - kEpiWarp0;
   const int quad = warp & 3;
-  const int half = ew >> 2;
-  const int col_base = half * CW;
+  const int part = ew >> 2;
+  const int col_base = part * CW;
   const int lq = lane & 3, lr = lane >> 2;
   float* sq_s = reinterpret_cast<float*>(smem + C::OFF_SQ) + ew * CW;
   constexpr float kInv256 = 1.0f / 256.0f;
@@ -585,17 +629,17 @@ __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* s
 
 // One flush per tile (EPI_INT32) or raw per-group dumps (EPI_GROUP_INT32): int32 out = acc >> 8.
 // Thread = tile row here (32x32b loads): these are the verification paths, not the fast ones.
-template <int BN>
+template <int BN, int EW>
 __device__ __forceinline__ void epilogue_int32(const GemmParams& p, uint32_t tmem_base,
-                                               uint32_t bar_tm_full, uint32_t bar_tm_empty,
+                                               uint32_t bar_tm_full, uint32_t bar_done, uint32_t bar_tm_empty,
                                                volatile int* abort_flag) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, 1, EW>;
   constexpr int NCH = C::COLS_PER_WARP / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ew = warp - kEpiWarp0;
   const int quad = warp & 3;
-  const int half = ew >> 2;
-  const int col_base = half * C::COLS_PER_WARP;
+  const int part = ew >> 2;
+  const int col_base = part * C::COLS_PER_WARP;
   const bool per_group = p.epi_mode == EPI_GROUP_INT32;
 
   Sched sched;
@@ -607,7 +651,9 @@ __device__ __forceinline__ void epilogue_int32(const GemmParams& p, uint32_t tme
     const int nflush = per_group ? (ti.g1 - ti.g0) : 1;
     for (int fl = 0; fl < nflush; ++fl) {
       const uint32_t buf = flush % C::NT;
-      ok = wait_bar(bar_tm_full + buf * 8, (flush / C::NT) & 1u, abort_flag);
+      // a flush per group: the group's commit arrives on the barrier of its int8 stage (see epilogue_group)
+      ok = per_group ? wait_bar(bar_done + (flush % C::NI) * 8, (flush / C::NI) & 1u, abort_flag)
+                     : wait_bar(bar_tm_full + buf * 8, (flush / C::NT) & 1u, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
@@ -632,11 +678,12 @@ __device__ __forceinline__ void epilogue_int32(const GemmParams& p, uint32_t tme
 // ------------------------------------------------------------------------------------------
 // The kernel
 // ------------------------------------------------------------------------------------------
-template <int BN, int CG>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, int CG, int EW>
+__global__ void __launch_bounds__((kEpiWarp0 + EW) * 32, 1)
 w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmP,
                  const __grid_constant__ CUtensorMap tmQ) {
-  using C = Cfg<BN, CG>;
+  using C = Cfg<BN, CG, EW>;
+  using R = Regs<EW>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -654,7 +701,6 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   const uint32_t bar_tm_empty = bar_tm_full + C::NT * 8;
   const uint32_t bar_sc_full = bar_tm_empty + C::NT * 8;
   const uint32_t bar_sc_empty = bar_sc_full + kNS * 8;
-  const uint32_t bar_sc_peer = bar_sc_empty + kNS * 8;   // leader only: the second CTA's scale stage has landed
   // where converters and epilogue warps arrive: the leader's barriers (shared::cluster addresses for CG = 2)
   const uint32_t arr_i8_full = (CG == 2) ? mapa_shared(bar_i8_full, 0) : bar_i8_full;
   const uint32_t arr_tm_empty = (CG == 2) ? mapa_shared(bar_tm_empty, 0) : bar_tm_empty;
@@ -664,9 +710,9 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::NP; ++i) { mbar_init(bar_pk_full + i * 8, 1); mbar_init(bar_pk_empty + i * 8, kConvWarps); }
     for (int i = 0; i < C::NI; ++i) { mbar_init(bar_i8_full + i * 8, kConvWarps * CG); mbar_init(bar_i8_empty + i * 8, 1); }
-    for (int i = 0; i < C::NT; ++i) { mbar_init(bar_tm_full + i * 8, 1); mbar_init(bar_tm_empty + i * 8, kEpiWarps * CG); }
+    for (int i = 0; i < C::NT; ++i) { mbar_init(bar_tm_full + i * 8, 1); mbar_init(bar_tm_empty + i * 8, EW * CG); }
     for (int i = 0; i < kNS; ++i) {
-      mbar_init(bar_sc_full + i * 8, 32); mbar_init(bar_sc_empty + i * 8, kEpiWarps); mbar_init(bar_sc_peer + i * 8, 1);
+      mbar_init(bar_sc_full + i * 8, 32); mbar_init(bar_sc_empty + i * 8, EW);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -683,14 +729,13 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Rebalance registers between the roles (whole warpgroups): the epilogue keeps up to BN/2 fp32
-  // running sums per thread.  128*56 + 128*72 + 256*192 = 65536 registers.
-  // The setmaxnreg of each role sits at the top of that role's branch below.
+  // Rebalance registers between the roles (whole warpgroups): the epilogue keeps BN / 2 (8 warps) or BN / 4
+  // (16 warps) fp32 running sums per thread.  The setmaxnreg of each role sits at the top of that role's branch.
 
   const bool per_group_flush = (p.epi_mode == EPI_GROUP) || (p.epi_mode == EPI_GROUP_INT32);
 
   if (warp < 4) {
-  setmaxnreg_dec<kRegsWg0>();
+  setmaxnreg_dec<R::WG0>();
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     SchedT<CG> sched;
@@ -732,8 +777,6 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     // pays a vote and a reconvergence (~250 cycles) per K group for nothing.
     if (leader && lane == 0) {
     constexpr uint32_t idesc = make_idesc<BN, CG>();
-    const uint32_t peer_i8_empty = (CG == 2) ? mapa_shared(bar_i8_empty, 1) : 0u;
-    const uint32_t peer_tm_full = (CG == 2) ? mapa_shared(bar_tm_full, 1) : 0u;
     SchedT<CG> sched;
     TileInfo ti;
     uint32_t it = 0, flush = 0;
@@ -744,17 +787,10 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         const bool last = per_group_flush || g == ti.g1 - 1;
         const uint32_t buf = flush % C::NT;
         const uint32_t s = it % C::NI, ph = (it / C::NI) & 1u;
-        const bool need_sc = p.epi_mode == EPI_GROUP;
         const uint32_t b_tm = bar_tm_empty + buf * 8, p_tm = ((flush / C::NT) & 1u) ^ 1u;
-        const uint32_t b_sc = bar_sc_full + (flush % kNS) * 8, b_pe = bar_sc_peer + (flush % kNS) * 8;
-        const uint32_t p_sc = (flush / kNS) & 1u;
-        // This warp's loop is the serial path of every small tile.  A probe of a completed barrier still costs
-        // 150-200 cycles, so everything the group needs (accumulator free, operands converted, scales landed) is
-        // probed back to back -- the latencies overlap -- and the one-at-a-time waits run only if something is missing.
+        // both probes back to back -- their latencies overlap -- and the one-at-a-time waits only if something is missing
         bool ready = mbar_test_wait(bar_i8_full + s * 8, ph);
         if (first) ready &= mbar_test_wait(b_tm, p_tm);
-        if (need_sc) ready &= mbar_test_wait(b_sc, p_sc);
-        if (need_sc && CG == 2) ready &= mbar_test_wait(b_pe, p_sc);
         if (!ready) {
           if (first) {
             ok = wait_bar_thread(b_tm, p_tm, abort_flag);
@@ -762,14 +798,6 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
           }
           ok = wait_bar_thread(bar_i8_full + s * 8, ph, abort_flag);
           if (!ok) break;
-          if (need_sc) {
-            ok = wait_bar_thread(b_sc, p_sc, abort_flag);
-            if (!ok) break;
-            if (CG == 2) {
-              ok = wait_bar_thread(b_pe, p_sc, abort_flag);
-              if (!ok) break;
-            }
-          }
         }
         tc_fence_after_sync();
         {
@@ -783,35 +811,19 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
             if (CG == 2) mma_i8_cg2(d_tmem, dP + (uint64_t)(2 * k), dQ + (uint64_t)(2 * k), idesc, (first && k == 0) ? 0u : 1u);
             else mma_i8(d_tmem, dP + (uint64_t)(2 * k), dQ + (uint64_t)(2 * k), idesc, (first && k == 0) ? 0u : 1u);
           }
+          // "stage free" for the converters; with a flush per group the same arrival is the epilogue's "accumulator
+          // full".  In a CTA pair one commit arrives on the barrier at this offset in both CTAs.
           if (CG == 2) {
-            // one arrival per CTA: the stage is free for both converters, the accumulator full for both epilogues
-            tc_commit_cg2(bar_i8_empty + s * 8);
-            tc_commit_cg2(peer_i8_empty + s * 8);
-            if (last) { tc_commit_cg2(bar_tm_full + buf * 8); tc_commit_cg2(peer_tm_full + buf * 8); }
+            tc_commit_cg2_both(bar_i8_empty + s * 8, (uint16_t)3);
+            if (last && !per_group_flush) tc_commit_cg2_both(bar_tm_full + buf * 8, (uint16_t)3);
           } else {
             tc_commit(bar_i8_empty + s * 8);
-            if (last) tc_commit(bar_tm_full + buf * 8);
+            if (last && !per_group_flush) tc_commit(bar_tm_full + buf * 8);
           }
         }
         if (last) ++flush;
       }
     }
-    } else if (!leader && CG == 2 && p.epi_mode == EPI_GROUP) {
-      // second CTA of a pair: this warp has no MMAs to issue; it tells the leader when a scale stage of this
-      // CTA has landed, so that the leader's "accumulator full" vouches for both CTAs' scales
-      const uint32_t arr_sc_peer = mapa_shared(bar_sc_peer, 0);
-      SchedT<CG> sched;
-      TileInfo ti;
-      uint32_t it = 0;
-      bool ok = true;
-      while (ok && sched.template next<BN>(p, ti)) {
-        for (int g = ti.g0; g < ti.g1; ++g, ++it) {
-          ok = wait_bar(bar_sc_full + (it % kNS) * 8, (it / kNS) & 1u, abort_flag);
-          if (!ok) break;
-          if (lane == 0) mbar_arrive_cluster(arr_sc_peer + (it % kNS) * 8);
-          __syncwarp();
-        }
-      }
     }
     __syncwarp();   // the issuing thread rejoins its warp before the block-wide teardown
   } else if (p.epi_mode == EPI_GROUP) {
@@ -849,7 +861,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   }
   } else if (warp < kConvWarp0 + kConvWarps) {
     // ---------------- converters ----------------
-    setmaxnreg_dec<kRegsConv>();
+    setmaxnreg_dec<R::CONV>();
     const int tid = threadIdx.x - kConvWarp0 * 32;
     SchedT<CG> sched;
     TileInfo ti;
@@ -880,20 +892,20 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     }
   } else {
     // ---------------- epilogue ----------------
-    setmaxnreg_inc<kRegsEpi>();
+    setmaxnreg_inc<R::EPI>();
     if (p.epi_mode == EPI_GROUP) {
-      if (p.swap) epilogue_group<BN, __nv_bfloat16, true, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, bar_sc_empty, abort_flag);
-      else epilogue_group<BN, __nv_bfloat16, false, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, bar_sc_empty, abort_flag);
+      if (p.swap) epilogue_group<BN, __nv_bfloat16, true, CG, EW>(p, smem, tmem_base, bar_i8_empty, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
+      else epilogue_group<BN, __nv_bfloat16, false, CG, EW>(p, smem, tmem_base, bar_i8_empty, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
     } else if (p.epi_mode == EPI_CHANNEL) {
       if (p.out_dtype == I4TC_FP16) {
-        if (p.swap) epilogue_channel<BN, __half, true, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
-        else epilogue_channel<BN, __half, false, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        if (p.swap) epilogue_channel<BN, __half, true, CG, EW>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        else epilogue_channel<BN, __half, false, CG, EW>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
       } else {
-        if (p.swap) epilogue_channel<BN, __nv_bfloat16, true, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
-        else epilogue_channel<BN, __nv_bfloat16, false, CG>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        if (p.swap) epilogue_channel<BN, __nv_bfloat16, true, CG, EW>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        else epilogue_channel<BN, __nv_bfloat16, false, CG, EW>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
       }
     } else {
-      epilogue_int32<BN>(p, tmem_base, bar_tm_full, bar_tm_empty, abort_flag);   // CG = 1 only
+      epilogue_int32<BN, EW>(p, tmem_base, bar_tm_full, bar_i8_empty, bar_tm_empty, abort_flag);   // CG = 1 only
     }
   }
 
@@ -909,23 +921,23 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, 1u);
 }
 
-template <int BN, int CG>
+template <int BN, int CG, int EW>
 static int launch_bn(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int grid, cudaStream_t st) {
-  using C = Cfg<BN, CG>;
+  using C = Cfg<BN, CG, EW>;
   static_assert(C::SMEM_BYTES <= 232448, "shared memory layout exceeds the 227 KB a CTA may use");
   static bool configured[64] = {false};
   int dev = 0;
   I4TC_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    I4TC_CUDA(cudaFuncSetAttribute(w4a4_gemm_kernel<BN, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    I4TC_CUDA(cudaFuncSetAttribute(w4a4_gemm_kernel<BN, CG, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured[dev] = true;
   }
   if (CG == 1) {
-    w4a4_gemm_kernel<BN, CG><<<grid, kThreads, C::SMEM_BYTES, st>>>(p, tmP, tmQ);
+    w4a4_gemm_kernel<BN, CG, EW><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(p, tmP, tmQ);
   } else {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(C::THREADS, 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -935,7 +947,7 @@ static int launch_bn(const GemmParams& p, const CUtensorMap& tmP, const CUtensor
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    I4TC_CUDA(cudaLaunchKernelEx(&cfg, w4a4_gemm_kernel<BN, CG>, p, tmP, tmQ));
+    I4TC_CUDA(cudaLaunchKernelEx(&cfg, w4a4_gemm_kernel<BN, CG, EW>, p, tmP, tmQ));
   }
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
@@ -999,17 +1011,18 @@ int launch_split_reduce(const float* ws, long long stride, int splits, long long
 }
 
 int launch_w4a4_gemm(const GemmParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ, int bn, int grid,
-                     bool cta_pair, cudaStream_t st) {
+                     bool cta_pair, int epi_warps, cudaStream_t st) {
+  const bool wide = epi_warps == 16 && bn >= 128;   // 64-column tiles have only 8 x 32 columns to hand out
   if (cta_pair) {
     I4TC_REQUIRE(bn == 256 && (grid % 2) == 0 && p.expert_offsets == nullptr && !p.swap && p.splits == 1 &&
                      (p.epi_mode == EPI_CHANNEL || p.epi_mode == EPI_GROUP),
                  I4TC_EINVAL, "CTA-pair launch needs a dense, unswapped 256-wide problem and an even grid");
-    return launch_bn<256, 2>(p, tmP, tmQ, grid, st);
+    return wide ? launch_bn<256, 2, 16>(p, tmP, tmQ, grid, st) : launch_bn<256, 2, 8>(p, tmP, tmQ, grid, st);
   }
   switch (bn) {
-    case 64: return launch_bn<64, 1>(p, tmP, tmQ, grid, st);
-    case 128: return launch_bn<128, 1>(p, tmP, tmQ, grid, st);
-    case 256: return launch_bn<256, 1>(p, tmP, tmQ, grid, st);
+    case 64: return launch_bn<64, 1, 8>(p, tmP, tmQ, grid, st);
+    case 128: return wide ? launch_bn<128, 1, 16>(p, tmP, tmQ, grid, st) : launch_bn<128, 1, 8>(p, tmP, tmQ, grid, st);
+    case 256: return wide ? launch_bn<256, 1, 16>(p, tmP, tmQ, grid, st) : launch_bn<256, 1, 8>(p, tmP, tmQ, grid, st);
     default: return fail(I4TC_EINVAL, "unsupported tile width %d", bn);
   }
 }

@@ -169,6 +169,13 @@ __device__ __forceinline__ void tc_commit_cg2(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
 }
+// The same with one instruction for both CTAs of the pair: the barrier at this offset in every CTA of `cta_mask`
+// receives one arrival (an arrival is not a load: nothing is copied between the CTAs).
+__device__ __forceinline__ void tc_commit_cg2_both(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(cta_mask)
+               : "memory");
+}
 // mbarrier arrives once all tcgen05 operations issued so far by this thread have completed.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)

@@ -354,6 +354,11 @@ def set_cta_pairs(mode: int = -1) -> None:
     check(lib.i4tc_set_cta_pairs(mode), "set_cta_pairs")
 
 
+def set_epilogue_warps(warps: int = 0) -> None:
+    """Force 8 or 16 epilogue warps per thread block of the tensor-core GEMM (tests); 0 restores automatic."""
+    check(lib.i4tc_set_epilogue_warps(warps), "set_epilogue_warps")
+
+
 def check_status(device=None) -> None:
     """Raise if any kernel gave up on a bounded wait since the last call (synchronises the stream)."""
     dev = torch.cuda.current_device() if device is None else torch.device(device).index

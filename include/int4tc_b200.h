@@ -69,6 +69,10 @@ int i4tc_set_split_k(int splits);
  * row side, scaled outputs).  Process-wide.  Results do not depend on it.  No reference counterpart. */
 int i4tc_set_cta_pairs(int mode);
 
+/* Test / tuning hook: number of epilogue warps per thread block of the tensor-core GEMM (0 = automatic, 8 or 16;
+ * 64-column tiles always use 8).  Process-wide.  Results do not depend on it.  No reference counterpart. */
+int i4tc_set_epilogue_warps(int warps);
+
 /* ---- quantise + pack ------------------------------------------------------- */
 
 /* Per-row symmetric int4 quantise + pack, one pass over the input.

@@ -303,7 +303,7 @@ def test_grouped_aliases_and_checks(tc, ops):
 
 
 @pytest.mark.parametrize("M", [1, 16, 128, 1024])
-@pytest.mark.parametrize("shape", ["qkv", "o", "down"])
+@pytest.mark.parametrize("shape", ["qkv", "o", "gate_up", "down"])
 def test_config1_quantised_linear(tc, ops, M, shape):
     """Qwen3-8B shapes, group-128: GPU quantise + fused GEMM against the oracle end to end."""
     from fp8_inference_toolkit_b200 import synthetic
@@ -323,12 +323,15 @@ def test_config1_quantised_linear(tc, ops, M, shape):
     assert_close_bf16(out, O.linear_grouped(xc, wc, xso, wso), f"{shape} M={M}")
 
 
-def test_config1_largest_sampled_rows(tc, ops):
-    """M=8192, gate+up (K=4096, N=24576): 32 sampled rows against the oracle, plus linearity in the
-    activation scales (doubling scale_a doubles the output exactly in bf16)."""
+@pytest.mark.parametrize("shape", ["qkv", "o", "gate_up", "down"])
+@pytest.mark.parametrize("epi_warps", [8, 16])
+def test_config1_largest_sampled_rows(tc, ops, shape, epi_warps):
+    """M=8192, all four Qwen3-8B linears: 32 sampled rows against the oracle, plus linearity in the
+    activation scales (doubling scale_a doubles the output exactly in bf16); both epilogue widths."""
     from fp8_inference_toolkit_b200 import synthetic
 
-    M, (K, N) = 8192, synthetic.QWEN3_8B_SHAPES["gate_up"]
+    M, (K, N) = 8192, synthetic.QWEN3_8B_SHAPES[shape]
+    ops.set_epilogue_warps(epi_warps)
     G = K // 128
     x = synthetic.activations(M, K, seed=0, device="cuda")
     w = synthetic.weights(N, K, seed=1, device="cuda")
@@ -342,7 +345,34 @@ def test_config1_largest_sampled_rows(tc, ops):
     xc = O.unpack_int4(xp[:, ridx].cpu().numpy())
     wc = O.unpack_int4(wp.cpu().numpy())
     ref = O.linear_grouped(xc, wc, xs[:, ridx].cpu().numpy(), ws.cpu().numpy())
-    assert_close_bf16(out[ridx], ref, "gate_up M=8192 sampled rows")
+    assert_close_bf16(out[ridx], ref, f"{shape} M=8192 sampled rows")
     out2 = torch.empty_like(out)
     tc.cutlass_int4_fused_grouped_gemm(xp, wp, (xs * 2).contiguous(), ws, out2, M, N, 128, G)
+    ops.set_epilogue_warps(0)
     assert torch.equal(out2.float(), out.float() * 2)
+
+
+@pytest.mark.parametrize("K,N", [(2560, 9728), (2560, 3584), (9728, 2560)])
+@pytest.mark.parametrize("M", [1, 10, 32, 64, 100, 700])
+def test_reference_kernel_test_shapes(tc, ops, M, K, N):
+    """The shapes of the reference's own kernel-vs-kernel checks (int4_native_tc/test_v5_correctness.py:12-52,
+    116-138: Qwen3-4B projections at M in {1, 10, 32, 64, 100, 700}), here against the CPU oracle: quantised
+    codes bit for bit, per-group integer partial sums bit for bit, bf16 output within 1e-2 / cosine 0.9999."""
+    from fp8_inference_toolkit_b200 import synthetic
+
+    G = K // 128
+    x = synthetic.activations(M, K, seed=M)
+    w = synthetic.weights(N, K, seed=K + N)
+    xp, xs = tc.dynamic_int4_quant_grouped(x.cuda(), 128)
+    wp, ws = tc.static_int4_weight_quant_grouped(w.cuda(), 128)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    tc.cutlass_int4_fused_grouped_gemm(xp, wp, xs, ws, out, M, N, 128, G)
+    ops.check_status()
+    xc, xso = O.quant_grouped(x, 128, "activation")
+    wc, wso = O.quant_grouped(w, 128, "weight")
+    assert np.array_equal(xp.cpu().numpy(), O.pack_int4(xc))
+    assert np.array_equal(wp.cpu().numpy(), O.pack_int4(wc))
+    assert_close_bf16(out, O.linear_grouped(xc, wc, xso, wso), f"K={K} N={N} M={M}")
+    if M <= 32:
+        part = ops.int4_grouped_partials(xp, wp, M, N, G)
+        assert np.array_equal(part.cpu().numpy(), O.grouped_int_partials(xc, wc))
