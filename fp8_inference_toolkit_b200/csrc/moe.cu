@@ -8,6 +8,7 @@
 //   3. stable rank inside the chunk + scatter -> sorted_pairs, inv_pairs
 // The scratch ([chunks, E] int32) is caller-provided global memory.
 #include "common.cuh"
+#include <mutex>
 
 namespace i4tc {
 
@@ -56,8 +57,11 @@ __global__ void __launch_bounds__(kSortChunk) moe_hist_kernel(const int32_t* __r
 // One block of kMaxExperts threads, thread e = expert e.  Two passes over the [chunks, E] histogram, each with eight
 // independent loads in flight (a load-add-store chain per chunk would pay a trip to L2 per chunk): totals per
 // expert, an exclusive scan of the totals across experts (warp shuffles), then the running bases of every chunk.
+// Pairs whose id lies outside [0, E) are left out of the sort; the tail of sorted_pairs that they would have
+// filled is set to -1 here, so that no later kernel reads an uninitialised pair index.
 __global__ void __launch_bounds__(kMaxExperts) moe_scan_kernel(int32_t* __restrict__ counts, int chunks, int E,
-                                                              int32_t* __restrict__ expert_offsets) {
+                                                              int32_t* __restrict__ expert_offsets,
+                                                              int32_t* __restrict__ sorted_pairs, int P) {
   __shared__ int s_warp[kMaxExperts / 32];
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
   const bool ok = e < E;
@@ -86,7 +90,10 @@ __global__ void __launch_bounds__(kMaxExperts) moe_scan_kernel(int32_t* __restri
   const int off = warp_base + incl - total;
   if (ok) {
     expert_offsets[e] = off;
-    if (e == E - 1) expert_offsets[E] = off + total;
+    if (e == E - 1) {
+      expert_offsets[E] = off + total;
+      s_warp[0] = off + total;   // read below, after the barrier (s_warp is no longer needed for the scan)
+    }
     int run = off;
     for (int c0 = 0; c0 < chunks; c0 += 8) {
       int v[8];
@@ -99,6 +106,8 @@ __global__ void __launch_bounds__(kMaxExperts) moe_scan_kernel(int32_t* __restri
       }
     }
   }
+  __syncthreads();
+  for (int i = s_warp[0] + threadIdx.x; i < P; i += kMaxExperts) sorted_pairs[i] = -1;
 }
 
 __global__ void __launch_bounds__(kSortChunk) moe_scatter_kernel(const int32_t* __restrict__ ids, int P, int E,
@@ -121,7 +130,8 @@ __global__ void __launch_bounds__(kSortChunk) moe_scatter_kernel(const int32_t* 
   }
 }
 
-// out[t, :] = bf16( sum_j w[t, j] * y[inv[t*k + j], :] ), fp32 accumulation in ascending j.
+// out[t, :] = bf16( sum_j w[t, j] * y[inv[t*k + j], :] ), fp32 accumulation in ascending j, one fused multiply-add
+// per term.
 __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y,
                                                          const int32_t* __restrict__ inv,
                                                          const float* __restrict__ w, int top_k, int H,
@@ -139,8 +149,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
       const uint32_t ww[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        acc[2 * i] += wj * __uint_as_float(ww[i] << 16);
-        acc[2 * i + 1] += wj * __uint_as_float(ww[i] & 0xFFFF0000u);
+        acc[2 * i] = __fmaf_rn(wj, __uint_as_float(ww[i] << 16), acc[2 * i]);
+        acc[2 * i + 1] = __fmaf_rn(wj, __uint_as_float(ww[i] & 0xFFFF0000u), acc[2 * i + 1]);
       }
     }
     union { __nv_bfloat16 h[8]; uint4 u; } pk;
@@ -154,7 +164,7 @@ int moe_sort_launch(const int32_t* ids, int64_t P, int64_t E, int32_t* sorted_pa
                     int32_t* expert_offsets, int32_t* scratch, cudaStream_t st) {
   const int chunks = (int)((P + kSortChunk - 1) / kSortChunk);
   moe_hist_kernel<<<chunks, kSortChunk, 0, st>>>(ids, (int)P, (int)E, scratch);
-  moe_scan_kernel<<<1, kMaxExperts, 0, st>>>(scratch, chunks, (int)E, expert_offsets);
+  moe_scan_kernel<<<1, kMaxExperts, 0, st>>>(scratch, chunks, (int)E, expert_offsets, sorted_pairs, (int)P);
   moe_scatter_kernel<<<chunks, kSortChunk, 0, st>>>(ids, (int)P, (int)E, scratch, sorted_pairs, inv_pairs);
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
@@ -208,10 +218,15 @@ constexpr int kNoAllocScratchInts = 16384;  // ceil(num_pairs / 1024) * num_expe
 static __device__ __align__(256) int32_t g_sort_scratch[kNoAllocScratchInts];
 
 static int32_t* g_sort_scratch_ptr[64] = {nullptr};
+static std::mutex g_sort_scratch_mutex;
 
-// Resolves the device address of g_sort_scratch for `device` (which must be current).
+// Resolves the device address of g_sort_scratch for `device` (which must be current).  The first
+// resolution on a device also makes the CUDA runtime load this module there (with lazy module loading
+// that is when the driver sets aside the array and the kernels' code), which is why callers that will
+// have no free device memory later do it at start-up through i4tc_moe_sort_noalloc_prepare.
 static int sort_scratch_for(int device, int32_t** out) {
   I4TC_REQUIRE(device >= 0 && device < 64, I4TC_EINVAL, "device ordinal %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_sort_scratch_mutex);
   if (g_sort_scratch_ptr[device] == nullptr) {
     int32_t* ptr = nullptr;
     I4TC_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_sort_scratch));
@@ -223,6 +238,19 @@ static int sort_scratch_for(int device, int32_t** out) {
 }
 
 extern "C" int64_t i4tc_moe_sort_noalloc_max_scratch_ints(void) { return kNoAllocScratchInts; }
+
+extern "C" int i4tc_moe_sort_noalloc_prepare(int device) {
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  int32_t* scratch = nullptr;
+  if (int rc = sort_scratch_for(device, &scratch)) return rc;
+  // ask for the kernels' attributes so that their code is resident too (nothing is launched)
+  cudaFuncAttributes attr;
+  I4TC_CUDA(cudaFuncGetAttributes(&attr, moe_hist_kernel));
+  I4TC_CUDA(cudaFuncGetAttributes(&attr, moe_scan_kernel));
+  I4TC_CUDA(cudaFuncGetAttributes(&attr, moe_scatter_kernel));
+  return I4TC_OK;
+}
 
 extern "C" int i4tc_moe_sort_noalloc(const int32_t* expert_ids, int64_t num_pairs, int64_t num_experts,
                                      int32_t* sorted_pairs, int32_t* inv_pairs, int32_t* expert_offsets,
@@ -239,13 +267,13 @@ extern "C" int i4tc_moe_sort_noalloc(const int32_t* expert_ids, int64_t num_pair
   DeviceGuard guard(device);
   I4TC_CUDA(guard.err);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int32_t* scratch = nullptr;
+  if (int rc = sort_scratch_for(device, &scratch)) return rc;   // also on an empty call, so that one can serve as a warm-up
   if (num_pairs == 0) {
     I4TC_CUDA(cudaMemsetAsync(expert_offsets, 0, (num_experts + 1) * sizeof(int32_t), st));
     return I4TC_OK;
   }
   I4TC_REQUIRE(expert_ids && sorted_pairs, I4TC_EINVAL, "null pointer");
-  int32_t* scratch = nullptr;
-  if (int rc = sort_scratch_for(device, &scratch)) return rc;
   // Nothing in the scratch has to start at zero: the histogram pass writes every entry that the
   // scan and scatter passes of this call read, so the previous call's contents are never seen.
   return moe_sort_launch(expert_ids, num_pairs, num_experts, sorted_pairs, inv_pairs, expert_offsets, scratch, st);

@@ -200,12 +200,42 @@ __device__ __forceinline__ uint32_t pack8(const Vec8<T>& x, const Recip& q, bool
   return (wl | wh) ^ 0x88888888u;  // offset-binary nibbles (n+8) -> two's complement
 }
 
-// silu(g) * u rounded to bf16 and widened again: the value the next quantiser sees.
-// exp through the special-function unit (2 ulp) and a correctly rounded reciprocal: the result is rounded
-// to bf16 right after, which hides the difference from an exact sigmoid in all but ~1e-4 of the values.
+// e**t for t clamped to [-87, 87] as a fixed sequence of correctly rounded fp32 operations (never contracted into
+// fused multiply-adds): n = rint(t * log2(e)); r = (t - n * ln2_hi) - n * ln2_lo; degree-7 Taylor polynomial of r by
+// Horner's rule; times 2**n.  A CPU repeats it bit for bit with plain IEEE single-precision arithmetic.
+__device__ __forceinline__ float exp_reproducible(float t) {
+  t = fminf(fmaxf(t, -87.0f), 87.0f);
+  const float n = rintf(__fmul_rn(t, 1.4426950408889634f));
+  const float r = __fsub_rn(__fsub_rn(t, __fmul_rn(n, 0.693145751953125f)), __fmul_rn(n, 1.428606765330187045e-06f));
+  float p = 1.0f / 5040.0f;
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f / 720.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f / 120.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f / 24.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f / 6.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 0.5f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+  return __fmul_rn(p, __int_as_float(((int)n + 127) << 23));   // |n| <= 126: an exact power of two
+}
+
+// (g * sigmoid(g)) * u with sigmoid(g) = 1 / (1 + exp_reproducible(-g)): the definition of SwiGLU here.
+__device__ __forceinline__ float silu_mul_reproducible(float g, float u) {
+  const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_reproducible(-g)));
+  return __fmul_rn(__fmul_rn(g, sig), u);
+}
+
+// silu(g) * u rounded to bf16 and widened again: the value the next quantiser sees, bit-identical to
+// bf16(silu_mul_reproducible(g, u)).  The fast evaluation (exp through the special-function unit, documented error
+// 2 + |1.173 x| ulp, and a correctly rounded reciprocal) is within ~17 ulp of that definition for |g| <= 8; it decides
+// the bf16 rounding unless the fp32 value lies within 32 ulp of a rounding boundary (one element in a thousand),
+// and only those elements and the rare |g| > 8 are evaluated by the definition itself.
 __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
-  float sig = __frcp_rn(1.0f + __expf(-g));
-  return __bfloat162float(__float2bfloat16_rn((g * sig) * u));
+  const float sig = __frcp_rn(1.0f + __expf(-g));
+  float y = __fmul_rn(__fmul_rn(g, sig), u);
+  const uint32_t low = __float_as_uint(y) & 0xFFFFu;
+  const bool near_boundary = (low - (0x8000u - 32u)) <= 64u;
+  if (near_boundary || !(fabsf(g) <= 8.0f)) y = silu_mul_reproducible(g, u);
+  return __bfloat162float(__float2bfloat16_rn(y));
 }
 
 // ------------------------------------------------------------------------------------------
@@ -285,7 +315,7 @@ __device__ __forceinline__ float absmax_of<__nv_bfloat16>(const Vec8<__nv_bfloat
 template <typename T, int LPG, int MODE, bool GIVEN>
 __global__ void __launch_bounds__(256) quant_grouped_kernel(
     const T* __restrict__ x, int64_t rows, int K, int64_t ldx, const int32_t* __restrict__ row_index,
-    int index_div, const float* __restrict__ given_scale, uint8_t* __restrict__ packed,
+    int index_div, int64_t src_rows, const float* __restrict__ given_scale, uint8_t* __restrict__ packed,
     float* __restrict__ scale, int role, int segs_per_block, const T* __restrict__ aux, float eps) {
   constexpr int GS = LPG * kQLane;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -297,10 +327,15 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
   const int seg_end = min(nseg, seg_begin + segs_per_block);
 
   const T* src = nullptr;
+  bool src_ok = row_ok;   // MODE 1: false for a pair index that names no row of x (such a row is quantised as zeros)
   if (row_ok) {
     int64_t sr = r;
-    if (MODE == 1) sr = row_index[r] / index_div;
-    src = x + sr * ldx;
+    if (MODE == 1) {
+      const int idx = row_index[r];
+      sr = idx / index_div;
+      src_ok = idx >= 0 && sr < src_rows;
+    }
+    if (src_ok) src = x + sr * ldx;
   }
   float row_factor = 0.f;
   if (MODE == 3) {
@@ -319,13 +354,14 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    row_factor = rsqrtf(ss / (float)K + eps);
+    // correctly rounded division, addition and reciprocal square root: a CPU can repeat the row statistic exactly
+    row_factor = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps));
   }
   Vec8<T> cur[kQVecs], nxt[kQVecs];
-  load_segment<T, MODE>(cur, src, seg_begin * kQSeg + lane * kQLane, K, row_ok, aux, row_factor);
+  load_segment<T, MODE>(cur, src, seg_begin * kQSeg + lane * kQLane, K, src_ok, aux, row_factor);
   for (int seg = seg_begin; seg < seg_end; ++seg) {
     const int k = seg * kQSeg + lane * kQLane;
-    if (seg + 1 < seg_end) load_segment<T, MODE>(nxt, src, k + kQSeg, K, row_ok, aux, row_factor);
+    if (seg + 1 < seg_end) load_segment<T, MODE>(nxt, src, k + kQSeg, K, src_ok, aux, row_factor);
     const bool ok = row_ok && k < K;
     const int g = k / GS;
     Recip q;
@@ -479,7 +515,7 @@ __global__ void unpack_int4_kernel(const uint8_t* __restrict__ packed, int64_t n
 // ------------------------------------------------------------------------------------------
 template <typename T, int MODE, bool GIVEN>
 static int launch_grouped_t(const T* x, int64_t rows, int64_t K, int64_t ldx, int gs, const int32_t* row_index,
-                            int index_div, const float* given, uint8_t* packed, float* scale, int role,
+                            int index_div, int64_t src_rows, const float* given, uint8_t* packed, float* scale, int role,
                             cudaStream_t st, const void* aux = nullptr, float eps = 0.f) {
   if (rows == 0 || K == 0) return I4TC_OK;
   // Enough blocks to fill the GPU several times over; beyond that a block walks several segments
@@ -494,7 +530,7 @@ static int launch_grouped_t(const T* x, int64_t rows, int64_t K, int64_t ldx, in
   I4TC_REQUIRE(grid.y <= 65535, I4TC_EINVAL, "K=%lld too large for the grouped quantiser", (long long)K);
 #define I4TC_LAUNCH_G(LPG)                                                                             \
   quant_grouped_kernel<T, LPG, MODE, GIVEN><<<grid, 256, 0, st>>>(x, rows, (int)K, ldx, row_index,     \
-                                                                   index_div, given, packed, scale, role, spb, \
+                                                                   index_div, src_rows, given, packed, scale, role, spb, \
                                                                    static_cast<const T*>(aux), eps)
   switch (gs) {
     case 32: I4TC_LAUNCH_G(1); break;
@@ -518,7 +554,8 @@ static int check_vec_input(const void* x, int dtype, int64_t ldx, const char* wh
 template <int MODE, bool GIVEN>
 static int launch_grouped(const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx, int64_t gs,
                           const int32_t* row_index, int index_div, const float* given, uint8_t* packed,
-                          float* scale, int role, int device, void* stream, const void* aux = nullptr, float eps = 0.f) {
+                          float* scale, int role, int device, void* stream, const void* aux = nullptr, float eps = 0.f,
+                          int64_t src_rows = 0) {
   I4TC_REQUIRE(rows >= 0 && K >= 0 && gs > 0, I4TC_EINVAL, "negative size");
   I4TC_REQUIRE(gs % 2 == 0, I4TC_EINVAL, "group_size must be even");
   I4TC_REQUIRE(K % gs == 0, I4TC_EINVAL, "K must be divisible by group_size");
@@ -534,17 +571,17 @@ static int launch_grouped(const void* x, int dtype, int64_t rows, int64_t K, int
   switch (dtype) {
     case I4TC_BF16:
       return launch_grouped_t<__nv_bfloat16, MODE, GIVEN>(static_cast<const __nv_bfloat16*>(x), rows, K, ldx,
-                                                          (int)gs, row_index, index_div, given, packed, scale,
+                                                          (int)gs, row_index, index_div, src_rows, given, packed, scale,
                                                           role, st, aux, eps);
     case I4TC_FP16:
       if (MODE >= 2) break;
       return launch_grouped_t<__half, MODE >= 2 ? 0 : MODE, GIVEN>(static_cast<const __half*>(x), rows, K, ldx,
-                                                                  (int)gs, row_index, index_div, given, packed,
+                                                                  (int)gs, row_index, index_div, src_rows, given, packed,
                                                                   scale, role, st);
     case I4TC_FP32:
       if (MODE >= 2) break;
       return launch_grouped_t<float, MODE >= 2 ? 0 : MODE, GIVEN>(static_cast<const float*>(x), rows, K, ldx,
-                                                                 (int)gs, row_index, index_div, given, packed,
+                                                                 (int)gs, row_index, index_div, src_rows, given, packed,
                                                                  scale, role, st);
     default: break;
   }
@@ -626,13 +663,14 @@ extern "C" int i4tc_quant_with_scales(const void* x, int dtype, int64_t rows, in
                                  I4TC_ROLE_ACTIVATION, device, stream);
 }
 
-extern "C" int i4tc_moe_gather_quant(const void* x, int dtype, int64_t K, int64_t ldx, const int32_t* sorted_pairs,
-                                     int64_t num_pairs, int64_t top_k, uint8_t* packed, float* scale, int device,
-                                     void* stream) {
+extern "C" int i4tc_moe_gather_quant(const void* x, int dtype, int64_t num_tokens, int64_t K, int64_t ldx,
+                                     const int32_t* sorted_pairs, int64_t num_pairs, int64_t top_k, uint8_t* packed,
+                                     float* scale, int device, void* stream) {
   I4TC_REQUIRE(top_k > 0 && top_k < (1 << 20), I4TC_EINVAL, "bad top_k");
+  I4TC_REQUIRE(num_tokens >= 0, I4TC_EINVAL, "negative num_tokens");
   I4TC_REQUIRE(sorted_pairs || num_pairs == 0, I4TC_EINVAL, "null sorted_pairs");
   return launch_grouped<1, false>(x, dtype, num_pairs, K, ldx, 128, sorted_pairs, (int)top_k, nullptr, packed,
-                                  scale, I4TC_ROLE_ACTIVATION, device, stream);
+                                  scale, I4TC_ROLE_ACTIVATION, device, stream, nullptr, 0.f, num_tokens);
 }
 
 extern "C" int i4tc_moe_silu_mul_quant(const void* h, int64_t P, int64_t I, uint8_t* packed, float* scale,

@@ -46,7 +46,8 @@ def moe_sort_tokens(expert_ids: torch.Tensor, num_experts: int):
 
 
 def moe_gather_quant(x: torch.Tensor, sorted_pairs: torch.Tensor, top_k: int):
-    """Rows ``x[sorted_pairs // top_k]`` grouped-quantised (gs=128) into [G,P,64] / [G,P]."""
+    """Rows ``x[sorted_pairs // top_k]`` grouped-quantised (gs=128) into [G,P,64] / [G,P].  A pair index that
+    names no row of ``x`` (the -1 entries the sort leaves for ids outside [0, E)) gives a row of zero codes."""
     _require(x.is_cuda and x.dim() == 2 and x.is_contiguous(), "x must be a contiguous 2D CUDA tensor")
     _require(x.dtype == torch.bfloat16, "x must be bfloat16")
     K = x.shape[1]
@@ -55,7 +56,7 @@ def moe_gather_quant(x: torch.Tensor, sorted_pairs: torch.Tensor, top_k: int):
     G = K // 128
     packed = torch.empty((G, P, 64), dtype=torch.uint8, device=x.device)
     scale = torch.empty((G, P), dtype=torch.float32, device=x.device)
-    check(lib.i4tc_moe_gather_quant(x.data_ptr(), _cabi.BF16, K, x.stride(0), sorted_pairs.data_ptr(), P, top_k,
+    check(lib.i4tc_moe_gather_quant(x.data_ptr(), _cabi.BF16, x.shape[0], K, x.stride(0), sorted_pairs.data_ptr(), P, top_k,
                                     packed.data_ptr(), scale.data_ptr(), _dev(x), _stream(x)), "moe_gather_quant")
     return packed, scale
 

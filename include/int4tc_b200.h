@@ -176,7 +176,8 @@ int i4tc_gemm_grouped_int32(const uint8_t* a, const uint8_t* b, int32_t* out, in
 /* Stable counting sort of the T*top_k (token, slot) pairs by expert id.
  * expert_ids: [num_pairs] int32 in [0, E); ids outside that range are left out.
  * Outputs: sorted_pairs [num_pairs] int32 (pair index = token*top_k + slot, ascending inside an
- * expert), inv_pairs [num_pairs] (sorted position of each pair, -1 if left out; may be NULL),
+ * expert; the entries past expert_offsets[E], which left-out pairs would have filled, are set to -1),
+ * inv_pairs [num_pairs] (sorted position of each pair, -1 if left out; may be NULL),
  * expert_offsets [E+1] int32.  E <= 256.  `scratch` is caller-provided device memory of at least
  * i4tc_moe_sort_scratch_bytes(num_pairs, E) bytes that the sort uses for per-chunk histograms. */
 int64_t i4tc_moe_sort_scratch_bytes(int64_t num_pairs, int64_t num_experts);
@@ -190,20 +191,27 @@ int i4tc_moe_sort(const int32_t* expert_ids, int64_t num_pairs, int64_t num_expe
  * reference.  The scratch is a fixed 64 KiB array inside the library (held by every GPU that loads
  * it, until exit), so the limit is ceil(num_pairs / 1024) * num_experts <= 16384 entries
  * (i4tc_moe_sort_noalloc_max_scratch_ints()); larger problems are rejected with I4TC_EINVAL and
- * should use i4tc_moe_sort.  The call allocates nothing: no cudaMalloc, no cudaFree, no library
- * allocator.  The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress); make that first call before starting any stream capture.  All calls
+ * should use i4tc_moe_sort.  The call itself allocates nothing: no cudaMalloc, no cudaFree, no library
+ * allocator.  One thing happens only once per device: the first use there looks up the array's device
+ * address (cudaGetSymbolAddress), and if nothing of this library's MoE code ran on that device before, the
+ * CUDA runtime loads the code module at that moment -- with lazy module loading that is when the driver
+ * sets aside the 64 KiB array and the kernels' code, which does need free device memory.  So do that first
+ * use at start-up, while memory is still free and before any stream capture: call
+ * i4tc_moe_sort_noalloc_prepare(device) (launches nothing) or make one call with num_pairs = 0.  All calls
  * share the one array, which keeps whatever the last call left in it (no entry has to start at
  * zero: each call overwrites what it reads), so two calls that overlap on the GPU -- different
  * streams, or different threads -- race; keep them ordered.  Outputs are identical to i4tc_moe_sort. */
 int64_t i4tc_moe_sort_noalloc_max_scratch_ints(void);
+int i4tc_moe_sort_noalloc_prepare(int device);
 int i4tc_moe_sort_noalloc(const int32_t* expert_ids, int64_t num_pairs, int64_t num_experts,
                           int32_t* sorted_pairs, int32_t* inv_pairs, int32_t* expert_offsets,
                           int device, void* stream);
 
 /* Gather rows x[sorted_pairs[i] / top_k] and grouped-quantise them (gs=128, activation
- * role) straight into expert-sorted group-major layout: packed [K/128, P, 64], scale [K/128, P]. */
-int i4tc_moe_gather_quant(const void* x, int dtype, int64_t K, int64_t ldx,
+ * role) straight into expert-sorted group-major layout: packed [K/128, P, 64], scale [K/128, P].
+ * x has num_tokens rows; a pair index outside [0, num_tokens * top_k) (the -1 entries the sort leaves for
+ * left-out pairs) reads nothing and is quantised as a row of zeros. */
+int i4tc_moe_gather_quant(const void* x, int dtype, int64_t num_tokens, int64_t K, int64_t ldx,
                           const int32_t* sorted_pairs, int64_t num_pairs, int64_t top_k,
                           uint8_t* packed, float* scale, int device, void* stream);
 

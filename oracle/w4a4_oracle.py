@@ -19,8 +19,16 @@ Pinning status
   ``absmax/7`` instead (``benchmark/benchmark_w4a8fp8.py:200-204``,
   ``int4_native_tc/profile_bottleneck.py:21-29``).  The oracle and the CUDA
   kernels both use that second, IEEE-reproducible form (see ``quant_codes``).
+* per-group dequant: the reference accumulates ``acc += float(mma) * sx * sw``
+  (``int4_native_tc/csrc/int4_gemm.cu:1436,1859-1862``) and is built with
+  ``--use_fast_math`` (``int4_native_tc/setup.py:52``), i.e. with multiply-add
+  contraction: the compiled statement is ``acc = fma(float(mma) * sx, sw, acc)``.
+  ``linear_grouped_f32`` states exactly that (one rounding for the product by
+  ``sx``, one for the fused multiply-add), emulated exactly on the CPU by ``fma32``.
 * MoE: **parity unpinned** (the reference has no MoE); it is a composition of
-  the grouped quantiser and the grouped linear below.
+  the grouped quantiser and the grouped linear below, with SwiGLU stated as a
+  formula of correctly rounded fp32 operations (``silu_mul``) so that a GPU
+  kernel can reproduce it bit for bit.
 """
 from __future__ import annotations
 
@@ -31,6 +39,25 @@ F32 = np.float32
 #: activation scale floor, ``int4_native_tc/csrc/int4_quant.cu:97``
 K_MIN_SCALE = F32(1.0) / (F32(7.0) * F32(512.0))
 GROUP = 128
+
+
+def fma32(a, b, c) -> np.ndarray:
+    """Correctly rounded fp32 fused multiply-add ``round(a * b + c)`` of float32 arrays.
+
+    The product of two fp32 numbers is exact in float64; the sum with ``c`` is formed in float64 rounded to odd
+    (error term from TwoSum), which makes the final rounding to fp32 the single rounding of the exact value."""
+    a64 = np.asarray(a, dtype=F32).astype(np.float64)
+    b64 = np.asarray(b, dtype=F32).astype(np.float64)
+    c64 = np.asarray(c, dtype=F32).astype(np.float64)
+    p = a64 * b64
+    s = p + c64
+    bb = s - p
+    err = (p - (s - bb)) + (c64 - bb)
+    bits = np.asarray(s).view(np.int64)
+    need = (err != 0) & ((bits & 1) == 0) & np.isfinite(s)
+    toward = np.where(err > 0, np.inf, -np.inf)
+    s = np.where(need, np.nextafter(s, toward), s)
+    return s.astype(F32)
 
 
 # --------------------------------------------------------------------------- #
@@ -188,8 +215,9 @@ def weight_group_sums(b_codes: np.ndarray) -> np.ndarray:
 
 def linear_grouped_azp_f32(a_codes, b_codes, scale_a, scale_b, azp_adj, w_col_sum) -> np.ndarray:
     """Per-group linear with the zero-point term, before the final cast, in the reference's order:
-    ``f += ((float(acc_g) + azp_adj[g,m] * w_col_sum[g,n]) * sx[g,m]) * sw[g,n]``
-    (``int4_gemm.cu:1851-1858``).  The bracket is an exact integer below 2**24."""
+    ``f = fma((float(acc_g) + azp_adj[g,m] * w_col_sum[g,n]) * sx[g,m], sw[g,n], f)``
+    (``int4_gemm.cu:1851-1858``, contracted as the build flags make it; see the module header).
+    The bracket is an exact integer below 2**24."""
     G, M, _ = a_codes.shape
     N = b_codes.shape[1]
     f = np.zeros((M, N), dtype=F32)
@@ -197,7 +225,7 @@ def linear_grouped_azp_f32(a_codes, b_codes, scale_a, scale_b, azp_adj, w_col_su
         acc = int_gemm(a_codes[g], b_codes[g]).astype(F32)
         acc = (acc + (azp_adj[g].astype(F32)[:, None] * w_col_sum[g].astype(F32)[None, :]).astype(F32)).astype(F32)
         t = (acc * scale_a[g].astype(F32)[:, None]).astype(F32)
-        f = (f + (t * scale_b[g].astype(F32)[None, :]).astype(F32)).astype(F32)
+        f = fma32(t, np.broadcast_to(scale_b[g].astype(F32)[None, :], t.shape), f)
     return f
 
 
@@ -208,6 +236,37 @@ def quant_codes_refcuda_form(xf: np.ndarray, absmax: np.ndarray) -> np.ndarray:
     inv = np.where(absmax == 0, F32(0.0), F32(7.0) / np.where(absmax == 0, F32(1.0), absmax)).astype(F32)
     q = np.rint((xf.astype(F32) * inv).astype(F32))
     return np.clip(q, -8.0, 7.0).astype(np.int8)
+
+
+def rmsnorm_quant_grouped(x: torch.Tensor, weight: torch.Tensor, eps: float, group_size: int = GROUP):
+    """RMSNorm in front of the grouped activation quantiser, as the fused kernel states it (no reference
+    counterpart: the reference quantises the output of a separate normalisation).
+
+    Row statistic: 32 partial sums of squares, partial ``l`` taking elements ``1024 s + 32 l + (0..31)`` of the row
+    in ascending order with one fused multiply-add each, added pairwise in a butterfly (distance 16, 8, 4, 2, 1);
+    ``factor = 1 / sqrt(sum / K + eps)`` with correctly rounded division, addition and reciprocal square root.
+    Value: ``bf16(bf16(x * factor) * weight[k])``, then ``quant_grouped(..., "activation")``.
+    ``x`` bf16 [M, K] with K a multiple of 32; returns (codes [G, M, gs] int8, scale [G, M] fp32)."""
+    xf = x.float().numpy().astype(F32)
+    M, K = xf.shape
+    assert K % 32 == 0
+    nseg = (K + 1023) // 1024
+    pad = np.zeros((M, nseg * 1024), dtype=F32)
+    pad[:, :K] = xf
+    lanes = pad.reshape(M, nseg, 32, 32)          # [row, segment, lane, element]
+    ss = np.zeros((M, 32), dtype=F32)
+    for sgm in range(nseg):
+        for i in range(32):
+            v = lanes[:, sgm, :, i]
+            ss = fma32(v, v, ss)
+    for o in (16, 8, 4, 2, 1):
+        ss = (ss + ss[:, np.arange(32) ^ o]).astype(F32)
+    tot = ss[:, 0]
+    arg = ((tot / F32(K)).astype(F32) + F32(eps)).astype(F32)
+    factor = (1.0 / np.sqrt(arg.astype(np.float64))).astype(F32)     # correctly rounded (float64 has bits to spare)
+    y = torch.from_numpy((xf * factor[:, None]).astype(F32)).to(torch.bfloat16).float().numpy()
+    y = torch.from_numpy((y * weight.float().numpy()[None, :]).astype(F32)).to(torch.bfloat16)
+    return quant_grouped(y, group_size, "activation")
 
 
 # --------------------------------------------------------------------------- #
@@ -254,15 +313,16 @@ def linear_per_channel(a_codes, b_codes, scale_a, scale_b) -> torch.Tensor:
 def linear_grouped_f32(a_codes, b_codes, scale_a, scale_b) -> np.ndarray:
     """Per-group W4A4 linear before the final cast.  ``a_codes`` [G,M,gs],
     ``b_codes`` [G,N,gs], scales [G,M] / [G,N].  fp32 accumulation in ascending
-    group order: ``f += (float(acc_g) * sx[g,m]) * sw[g,n]``
-    (``int4_gemm.cu:1436,1859-1862,2462``)."""
+    group order: ``f = fma(float(acc_g) * sx[g,m], sw[g,n], f)``, the reference's
+    ``acc += float(mma) * sx * sw`` as its build flags contract it
+    (``int4_gemm.cu:1436,1859-1862,2462``, ``setup.py:52``)."""
     G, M, _ = a_codes.shape
     N = b_codes.shape[1]
     f = np.zeros((M, N), dtype=F32)
     for g in range(G):
         acc = int_gemm(a_codes[g], b_codes[g]).astype(F32)
         t = (acc * scale_a[g].astype(F32)[:, None]).astype(F32)
-        f = (f + (t * scale_b[g].astype(F32)[None, :]).astype(F32)).astype(F32)
+        f = fma32(t, np.broadcast_to(scale_b[g].astype(F32)[None, :], t.shape), f)
     return f
 
 
@@ -298,12 +358,40 @@ def moe_sort(expert_ids: np.ndarray, num_experts: int):
     return order, offsets
 
 
+_EXP_COEF = [F32(1.0 / 5040.0), F32(1.0 / 720.0), F32(1.0 / 120.0), F32(1.0 / 24.0), F32(1.0 / 6.0), F32(0.5),
+             F32(1.0), F32(1.0)]
+_LOG2E = F32(1.4426950408889634)
+_LN2_HI = F32(0.693145751953125)
+_LN2_LO = F32(1.428606765330187045e-06)
+
+
+def exp_f32(t: np.ndarray) -> np.ndarray:
+    """``e**t`` for fp32 ``t`` clamped to [-87, 87], as a fixed sequence of correctly rounded fp32 operations
+    (no fused multiply-add): n = rint(t * log2(e)); r = (t - n * ln2_hi) - n * ln2_lo; a degree-7 Taylor polynomial
+    of r by Horner's rule; times 2**n.  About 1 ulp; what matters is that a GPU kernel can repeat it exactly."""
+    t = np.minimum(np.maximum(np.asarray(t, dtype=F32), F32(-87.0)), F32(87.0))
+    n = np.rint((t * _LOG2E).astype(F32)).astype(F32)
+    r = ((t - (n * _LN2_HI).astype(F32)).astype(F32) - (n * _LN2_LO).astype(F32)).astype(F32)
+    p = np.full_like(r, _EXP_COEF[0])
+    for c in _EXP_COEF[1:]:
+        p = ((p * r).astype(F32) + c).astype(F32)
+    return np.ldexp(p, n.astype(np.int32)).astype(F32)
+
+
+def silu_mul_f32(g: np.ndarray, u: np.ndarray) -> np.ndarray:
+    """``(g * sigmoid(g)) * u`` in fp32 with ``sigmoid(g) = 1 / (1 + exp_f32(-g))`` (IEEE division)."""
+    g = np.asarray(g, dtype=F32)
+    u = np.asarray(u, dtype=F32)
+    sig = (F32(1.0) / (F32(1.0) + exp_f32(-g)).astype(F32)).astype(F32)
+    return ((g * sig).astype(F32) * u).astype(F32)
+
+
 def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
-    """SwiGLU on a bf16 [R, 2I] tensor laid out [gate | up]; fp32 math, bf16 result."""
+    """SwiGLU on a bf16 [R, 2I] tensor laid out [gate | up]; fp32 math (``silu_mul_f32``), bf16 result."""
     I = gate_up.shape[1] // 2
-    g = gate_up[:, :I].float()
-    u = gate_up[:, I:].float()
-    return (g * torch.sigmoid(g) * u).to(torch.bfloat16)
+    g = gate_up[:, :I].float().numpy()
+    u = gate_up[:, I:].float().numpy()
+    return to_bf16(silu_mul_f32(g, u))
 
 
 def moe_layer(x: torch.Tensor, expert_ids, expert_w, w_gate_up_q, w_down_q, num_experts: int):
@@ -332,7 +420,11 @@ def moe_layer(x: torch.Tensor, expert_ids, expert_w, w_gate_up_q, w_down_q, num_
         dq, ds = w_down_q[e]
         o = linear_grouped(ha, dq, hs, ds)
         y[tok, slot] = o.float()
-    out = torch.zeros(T, H, dtype=torch.float32)
+    out = np.zeros((T, H), dtype=F32)
+    wn = expert_w.float().numpy()
+    yn = y.numpy()
+    valid = (ids >= 0) & (ids < num_experts)
     for j in range(k):
-        out = out + expert_w[:, j : j + 1].float() * y[:, j]
-    return out.to(torch.bfloat16)
+        term = fma32(np.broadcast_to(wn[:, j : j + 1], (T, H)), yn[:, j], out)   # out = fma(w, y, out)
+        out = np.where(valid[:, j : j + 1], term, out)
+    return to_bf16(out)

@@ -139,6 +139,24 @@ def test_full_size_properties(tc):
     assert (u.abs().amax(dim=1) == 7).all()
 
 
+@pytest.mark.parametrize("M,K", [(37, 1024), (8, 4096), (130, 256), (5, 1536), (64, 12288)])
+def test_rmsnorm_quant_against_oracle(M, K):
+    """RMSNorm + grouped quantise against the CPU oracle: the row statistic is a fixed sequence of correctly
+    rounded fp32 operations, so codes and scales are compared bit for bit."""
+    from fp8_inference_toolkit_b200 import ops
+    from oracle import w4a4_oracle as O
+
+    g = torch.Generator().manual_seed(3 * M + K)
+    x = (torch.randn(M, K, generator=g) * 1.5).to(torch.bfloat16)
+    x[0] = 0  # a zero row: factor = 1 / sqrt(eps), all codes zero
+    w = (1.0 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16)
+    eps = 1e-6
+    p, s = ops.rmsnorm_int4_quant_grouped(x.cuda(), w.cuda(), eps, 128)
+    codes, so = O.rmsnorm_quant_grouped(x, w, eps, 128)
+    assert np.array_equal(p.cpu().numpy(), O.pack_int4(codes))
+    assert np.array_equal(s.cpu().numpy(), so)
+
+
 @pytest.mark.parametrize("M,K", [(37, 1024), (8, 4096), (130, 256)])
 def test_rmsnorm_quant_matches_unfused(tc, M, K):
     """RMSNorm fused in front of the grouped quantiser against the unfused pair (fp32 normalisation returning

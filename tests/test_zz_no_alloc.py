@@ -38,6 +38,9 @@ def _sort_both(cabi, ids_np, E):
 def test_noalloc_sort_matches_on_two_calls_in_a_row():
     from fp8_inference_toolkit_b200 import _cabi
 
+    # what a server does at start-up, while device memory is still free: resolve the array's address on this
+    # device (which also loads the code module); nothing is launched
+    _cabi.check(_cabi.lib.i4tc_moe_sort_noalloc_prepare(torch.cuda.current_device()), "i4tc_moe_sort_noalloc_prepare")
     rng = np.random.RandomState(11)
     # first a large problem that fills most of the built-in scratch, then a smaller one with a
     # different expert count, so stale contents of the shared array would show
