@@ -2,9 +2,27 @@
 
 ``ops`` mirrors the reference extension's op surface; ``moe`` adds the MoE grouped ops;
 ``linear`` holds the ``nn.Module`` that plays the vLLM plugin's two-phase protocol.
-Importing this package loads ``csrc/libint4tc_b200.so`` and fails if it has not been built.
+The CUDA library ``csrc/libint4tc_b200.so`` is loaded by the first access to an op (``ops``, ``moe``, ``linear`` or
+any op name) and that access fails if the library has not been built; the pure-PyTorch pieces (``calibration``,
+``synthetic``, the bookkeeping of ``moe_ep``) import without it.
 """
-from . import ops, moe  # noqa: F401
-from .ops import *  # noqa: F401,F403
+import importlib
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
+
+_LAZY_MODULES = ("ops", "moe", "linear", "qwen3", "moe_ep", "calibration", "synthetic", "unported", "_cabi")
+
+
+def __getattr__(name):
+    if name in _LAZY_MODULES:
+        return importlib.import_module(f"{__name__}.{name}")
+    ops = importlib.import_module(f"{__name__}.ops")
+    try:
+        return getattr(ops, name)
+    except AttributeError:
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}") from None
+
+
+def __dir__():
+    ops = importlib.import_module(f"{__name__}.ops")
+    return sorted(set(globals()) | set(_LAZY_MODULES) | set(dir(ops)))

@@ -66,14 +66,14 @@ struct DeviceInfo {
   int cc_minor = 0;
   int max_smem_optin = 0;
   unsigned int* status = nullptr;  // device status word written by bounded waits
-  float* split_ws = nullptr;       // split-K partial sums (grown on demand, owned by the library)
-  size_t split_ws_bytes = 0;
 };
 
 // Cached per-device properties; allocates the status word on first use.
 int device_info(int device, const DeviceInfo** out);
-// Returns the library-owned split-K workspace of `device`, at least `bytes` large (reallocated if needed).
-int split_workspace(int device, size_t bytes, float** out);
+// Returns the library-owned split-K workspace of (`device`, `stream`), at least `bytes` large.  A buffer that was
+// handed out is never freed or moved: when a stream needs more than it has, a larger buffer is allocated beside
+// the old one (which stays valid for launches and CUDA graphs that already hold it).
+int split_workspace(int device, cudaStream_t stream, size_t bytes, float** out);
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 

@@ -29,6 +29,11 @@ struct GemmParams {
   const float* sq;   // Q-side scales, element (g, q) at sq[g * sq_gstride + q]
   long long sp_gstride;
   long long sq_gstride;
+  // Zero-point term of asymmetrically quantised activations (EPI_GROUP only; nullptr = none): group g adds
+  // zp[g, p] * zq[g, q] to its integer sum before the scales (activation side: azp_adj, weight side: w_col_sum);
+  // same strides as sp / sq.
+  const float* zp;
+  const float* zq;
   void* out;
   long long ldc;        // row stride of out in elements
   long long out_gstride;// EPI_GROUP_INT32: elements between consecutive groups
@@ -50,11 +55,6 @@ struct GemmParams {
 
 // out[i] = bf16(sum_s ws[s * stride + i]), s ascending.
 int launch_split_reduce(const float* ws, long long stride, int splits, long long n, void* out, cudaStream_t st);
-// out = bf16(sum of the K ranges' fp32 sums + sum_g (sa * adj)[g, m] * (sb * wcs)[g, n]); defined with the
-// asymmetric quantisers
-int launch_azp_finish(const float* ws, long long stride, int splits, const float* sa, const float* sb,
-                      const float* adj, const float* wcs, int G, long long M, long long N, void* out,
-                      cudaStream_t st);
 // out[m, n] = cast((sum_s ws[s * stride + m * N + n] * sb[n]) * sa[m]): the ranges hold exact integer sums.
 int launch_split_reduce_scaled(const float* ws, long long stride, int splits, long long M, long long N, const float* sa,
                                const float* sb, void* out, int out_dtype, cudaStream_t st);

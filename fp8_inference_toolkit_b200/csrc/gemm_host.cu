@@ -2,18 +2,21 @@
 // tile-shape choice and launch.
 #include "gemm.cuh"
 #include <stdlib.h>
+#include <atomic>
 
 namespace i4tc {
 
-static int g_force_bn = 0;    // 0 = choose automatically
-static int g_force_swap = -1; // -1 = choose automatically
-static int g_force_splits = 0; // 0 = choose automatically, 1 = never split, n = n K ranges
-static int g_cta_pairs = -1;   // -1 = choose automatically, 0 = never, 1 = whenever the problem allows it
-static bool g_pairs_launchable = true;   // cleared when an automatic cluster launch was refused
-static int g_epi_warps = 0;    // 0 = choose automatically, 8 or 16
+// Process-wide tuning hooks.  Atomics: a host thread may change one while another thread launches (each launch
+// reads every hook once, at its start).
+static std::atomic<int> g_force_bn{0};      // 0 = choose automatically
+static std::atomic<int> g_force_swap{-1};   // -1 = choose automatically
+static std::atomic<int> g_force_splits{0};  // 0 = choose automatically, 1 = never split, n = n K ranges
+static std::atomic<int> g_cta_pairs{-1};    // -1 = choose automatically, 0 = never, 1 = whenever the problem allows it
+static std::atomic<bool> g_pairs_launchable{true};   // cleared when an automatic cluster launch was refused
+static std::atomic<int> g_epi_warps{0};     // 0 = choose automatically, 8 or 16
 
 static int epi_warps_for(int epi_mode) {
-  if (g_epi_warps) return g_epi_warps;
+  if (const int w = g_epi_warps.load()) return w;
   (void)epi_mode;
   return 8;
 }
@@ -29,9 +32,9 @@ struct Shape {
 static Shape choose_shape(long long M, long long N, int sms, bool allow_swap, bool group_mode) {
   Shape s;
   s.swap = allow_swap && M <= 64;
-  if (g_force_swap >= 0 && allow_swap) s.swap = g_force_swap != 0;
-  if (g_force_bn) {
-    s.bn = g_force_bn;
+  if (const int fs = g_force_swap.load(); fs >= 0 && allow_swap) s.swap = fs != 0;
+  if (const int fb = g_force_bn.load()) {
+    s.bn = fb;
     return s;
   }
   if (s.swap) {
@@ -74,8 +77,7 @@ struct DenseArgs {
   bool rowmajor;    // operands are [rows, K/2] (else group-major [G, rows, 64])
   long long K;      // only for rowmajor
   int epi_mode;
-  // zero-point pass (per-group mode only): the GEMM leaves fp32 sums in the workspace and a second kernel adds
-  // sum_g scale_a * azp_adj * scale_b * w_col_sum before rounding to bf16
+  // zero-point term (per-group mode only): group g adds azp_adj[g, m] * w_col_sum[g, n] to its integer sum
   const float* azp_adj = nullptr;
   const float* w_col_sum = nullptr;
 };
@@ -114,11 +116,13 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   if (!sh.swap) {
     pbase = d.a; qbase = d.b; prow = d.M; qrow = d.N;
     p.sp = d.sa; p.sq = d.sb;
+    p.zp = d.azp_adj; p.zq = d.w_col_sum;
     p.sp_gstride = per_group_scales ? d.M : 0;
     p.sq_gstride = per_group_scales ? d.N : 0;
   } else {
     pbase = d.b; qbase = d.a; prow = d.N; qrow = d.M;
     p.sp = d.sb; p.sq = d.sa;
+    p.zp = d.w_col_sum; p.zq = d.azp_adj;
     p.sp_gstride = per_group_scales ? d.N : 0;
     p.sq_gstride = per_group_scales ? d.M : 0;
   }
@@ -146,29 +150,17 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
       const double cost = (double)((tiles * s + info->sm_count - 1) / info->sm_count) * gps * 0.65 + traffic_us + 3.0;
       if (cost < best_cost) { best_cost = cost; best_s = s; }
     }
-    if (g_force_splits > 1) best_s = g_force_splits <= d.G ? g_force_splits : d.G;
+    if (const int fs = g_force_splits.load(); fs > 1) best_s = fs <= d.G ? fs : d.G;
     if (best_s > 1) {
       p.splits = best_s;
       p.groups_per_split = (d.G + best_s - 1) / best_s;
       p.splits = (d.G + p.groups_per_split - 1) / p.groups_per_split;  // no empty range
       p.ws_stride = (d.M * d.N + 3) & ~3ll;   // every range starts on a 16-byte boundary
       float* ws = nullptr;
-      if (int rc = split_workspace(device, (size_t)p.splits * p.ws_stride * sizeof(float), &ws)) return rc;
+      if (int rc = split_workspace(device, static_cast<cudaStream_t>(stream), (size_t)p.splits * p.ws_stride * sizeof(float), &ws)) return rc;
       p.split_ws = ws;
     }
   }
-  if (d.azp_adj != nullptr && p.split_ws == nullptr) {
-    // one K range, written as fp32 to the workspace
-    p.ws_stride = (d.M * d.N + 3) & ~3ll;
-    float* ws = nullptr;
-    if (int rc = split_workspace(device, (size_t)p.ws_stride * sizeof(float), &ws)) return rc;
-    p.split_ws = ws;
-  }
-  auto finish = [&]() -> int {
-    if (d.azp_adj == nullptr) return I4TC_OK;
-    return launch_azp_finish(p.split_ws, p.ws_stride, p.splits, d.sa, d.sb, d.azp_adj, d.w_col_sum, d.G, d.M, d.N,
-                             d.out, static_cast<cudaStream_t>(stream));
-  };
 
   // CTA pairs (256 x 256 tiles on two SMs): each SM converts and stages a third less per unit of MMA work.
   // Worth it once the 256-row tiles fill the SM pairs about as well as the 128-row tiles fill the SMs.
@@ -194,7 +186,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
     pp.num_p_tiles = (int)((prow + 255) / 256);
     const int grid = 2 * (int)(pair_tiles < clusters_max ? pair_tiles : clusters_max);
     const int rc = launch_w4a4_gemm(pp, tmP, tmQ, sh.bn, grid, true, epi_warps_for(d.epi_mode), static_cast<cudaStream_t>(stream));
-    if (rc == I4TC_OK) return finish();
+    if (rc == I4TC_OK) return I4TC_OK;
     if (g_cta_pairs == 1) return rc;   // the caller asked for pairs: report why they cannot run
     // an environment that cannot launch clusters of two (a restricted SM partition, for instance): the launch
     // was refused before anything ran; remember it and use single thread blocks from now on
@@ -205,7 +197,6 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   const long long items = tiles * p.splits;
   const int grid = (int)(items < info->sm_count ? items : info->sm_count);
   if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, false, epi_warps_for(d.epi_mode), static_cast<cudaStream_t>(stream))) return rc;
-  if (d.azp_adj != nullptr) return finish();
   if (p.splits > 1) {
     if (d.epi_mode == EPI_CHANNEL)
       return launch_split_reduce_scaled(p.split_ws, p.ws_stride, p.splits, d.M, d.N, d.sa, d.sb, d.out, d.out_dtype,
@@ -296,7 +287,6 @@ extern "C" int i4tc_gemm_grouped_azp(const uint8_t* a, const uint8_t* b, const f
   int rc = check_dense_common(a, b, out, M, N);
   if (rc) return rc < 0 ? rc : I4TC_OK;
   I4TC_REQUIRE(scale_a && scale_b && azp_adj && w_col_sum, I4TC_EINVAL, "null scale, azp_adj or w_col_sum pointer");
-  I4TC_REQUIRE(M * N < (1ll << 40), I4TC_EINVAL, "M * N too large for the fp32 workspace");
   DenseArgs d{a, b, scale_a, scale_b, out, I4TC_BF16, M, N, (int)num_groups, false, 0, EPI_GROUP};
   d.azp_adj = azp_adj;
   d.w_col_sum = w_col_sum;
@@ -331,7 +321,8 @@ extern "C" int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, con
 
   // 256-column tiles amortise the conversion of the activation tile better; narrow outputs fall
   // back to 128 columns.
-  int bn = g_force_bn ? g_force_bn : ((N % 256 == 0) ? 256 : 128);
+  const int forced_bn = g_force_bn.load();
+  int bn = forced_bn ? forced_bn : ((N % 256 == 0) ? 256 : 128);
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.P_rows = (int)num_pairs;

@@ -346,7 +346,10 @@ __device__ __forceinline__ void store_pair(OutT* out, long long ldc, int prow, i
 // Scales.  Two otherwise idle warps copy the kBM row scales and BN column scales of each K group from
 // global to shared memory (4-byte cp.async, kNS stages ahead, completion signalled on an mbarrier), so the
 // epilogue warps spend no instructions or registers on global addresses.
-template <int BN, typename OutT, bool SWAP, int CG, int EW>
+// AZP: the zero-point term of asymmetric activations, acc_g + zp[p] * zq[q] before the scales (one more packed
+// multiply-add per pair; an exact integer below 2^24 like acc_g itself).  The two extra vectors of a group travel
+// with its scales: the ring then holds two stages of double size instead of four.
+template <int BN, typename OutT, bool SWAP, int CG, int EW, bool AZP>
 __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
                                                uint32_t bar_done, uint32_t bar_tm_empty, uint32_t bar_sc_full,
                                                uint32_t bar_sc_empty, volatile int* abort_flag) {
@@ -364,6 +367,8 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
   // The accumulators are 256 x the integer sums; 2^-8 rides on the row-side scale (exact in both orders).
   constexpr bool pq_order = !SWAP;
   constexpr float kInv256 = 1.0f / 256.0f;
+  constexpr uint32_t NS = AZP ? kNS / 2 : kNS;                       // scale stages in the ring
+  constexpr int STAGE_F = (AZP ? 2 : 1) * (C::SCALE_STAGE / 4);      // floats per stage
 
   SchedT<CG> sched;
   TileInfo ti;
@@ -384,12 +389,12 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
     for (int g = ti.g0; g < ti.g1; ++g) {
       // group number `flush` is done when the commit behind its MMAs arrives on the barrier of its int8 stage
       // (the one the converters wait for before they reuse the stage); its scales have their own ring
-      const uint32_t ss = flush % kNS;
+      const uint32_t ss = flush % NS;
       const uint32_t buf = flush % C::NT;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
       if (!pre) {
         const uint32_t b_done = bar_done + (flush % C::NI) * 8, p_done = (flush / C::NI) & 1u;
-        const uint32_t b_sc = bar_sc_full + ss * 8, p_sc = (flush / kNS) & 1u;
+        const uint32_t b_sc = bar_sc_full + ss * 8, p_sc = (flush / NS) & 1u;
         // both probes in flight together; the one-at-a-time waits run only if something is missing
         const bool ready = mbar_test_wait(b_sc, p_sc) & mbar_test_wait(b_done, p_done);
         if (!__all_sync(0xffffffffu, ready)) {
@@ -401,13 +406,18 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
         tc_fence_after_sync();
         if (PIPE) tmem_ld_16x256b_x4(taddr, rb[0]);
       }
-      const float* st_p = sc + ss * (C::SCALE_STAGE / 4) + quad * 32;         // this warp's 32 row scales
-      const float* st_q = sc + ss * (C::SCALE_STAGE / 4) + kBM + col_base;    // this warp's CW column scales
-      float2 sp2[4];
+      const float* st_p = sc + ss * STAGE_F + quad * 32;         // this warp's 32 row scales
+      const float* st_q = sc + ss * STAGE_F + kBM + col_base;    // this warp's CW column scales
+      float2 sp2[4], zp2[AZP ? 4 : 1];
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
         const float v = st_p[8 * a + lr] * kInv256;
         sp2[a] = make_float2(v, v);
+        if (AZP) {
+          // the accumulators are 256 x the integer sums, so the zero-point term is scaled alike (exact)
+          const float z = st_p[(kBM + BN) + 8 * a + lr] * 256.0f;
+          zp2[a] = make_float2(z, z);
+        }
       }
 #pragma unroll
       for (int u = 0; u < S; ++u) {
@@ -425,7 +435,7 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
           if (g + 1 < ti.g1) {
             const uint32_t nf = flush + 1;
             const bool ready = mbar_test_wait(bar_done + (nf % C::NI) * 8, (nf / C::NI) & 1u) &
-                               mbar_test_wait(bar_sc_full + (nf % kNS) * 8, (nf / kNS) & 1u);
+                               mbar_test_wait(bar_sc_full + (nf % NS) * 8, (nf / NS) & 1u);
             if (__all_sync(0xffffffffu, ready)) {
               tc_fence_after_sync();
               if (PIPE) tmem_ld_16x256b_x4(tmem_base + ((uint32_t)(quad * 32) << 16) + (nf % C::NT) * BN + col_base, rb[0]);
@@ -437,11 +447,14 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const float2 sq = *reinterpret_cast<const float2*>(st_q + c * 32 + kk * 8 + lq * 2);
+          float2 zq = make_float2(0.f, 0.f);
+          if (AZP) zq = *reinterpret_cast<const float2*>(st_q + (kBM + BN) + c * 32 + kk * 8 + lq * 2);
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int a = sl * 2 + h;
-            const float2 d = make_float2(__int2float_rn((int32_t)r[4 * kk + 2 * h]),
-                                         __int2float_rn((int32_t)r[4 * kk + 2 * h + 1]));
+            float2 d = make_float2(__int2float_rn((int32_t)r[4 * kk + 2 * h]),
+                                   __int2float_rn((int32_t)r[4 * kk + 2 * h + 1]));
+            if (AZP) d = __ffma2_rn(zp2[a], zq, d);
             float2& acc = f[(a * NCH + c) * 4 + kk];
             if (pq_order) acc = __ffma2_rn(__fmul2_rn(d, sp2[a]), sq, acc);
             else acc = __ffma2_rn(__fmul2_rn(d, sq), sp2[a], acc);
@@ -829,6 +842,9 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   } else if (p.epi_mode == EPI_GROUP) {
     // ---------------- scale loaders (warps 2 and 3 take alternate K groups) ----------------
     const uint32_t w = (uint32_t)(warp - kScaleWarp0);
+    const bool azp = p.zp != nullptr;
+    const uint32_t ns = azp ? kNS / 2 : kNS;                        // with zero-point vectors: two stages of double size
+    const uint32_t stage_bytes = (azp ? 2u : 1u) * C::SCALE_STAGE;
     SchedT<CG> sched;
     TileInfo ti;
     uint32_t it = 0;
@@ -836,23 +852,27 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     while (ok && sched.template next<BN>(p, ti)) {
       for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         if ((it % kScaleWarps) != w) continue;
-        const uint32_t ss = it % kNS;
-        ok = wait_bar(bar_sc_empty + ss * 8, ((it / kNS) & 1u) ^ 1u, abort_flag);
+        const uint32_t ss = it % ns;
+        ok = wait_bar(bar_sc_empty + ss * 8, ((it / ns) & 1u) ^ 1u, abort_flag);
         if (!ok) break;
-        const uint32_t dst = sbase + C::OFF_SQ + ss * C::SCALE_STAGE;
+        const uint32_t dst = sbase + C::OFF_SQ + ss * stage_bytes;
         const float* src_p = p.sp + (long long)g * p.sp_gstride;
+        const float* src_zp = azp ? p.zp + (long long)g * p.sp_gstride : nullptr;
 #pragma unroll
         for (int j = 0; j < kBM / 32; ++j) {
           const int row = ti.p0 + j * 32 + lane;
           const bool v = row < ti.p_lim;
           cp_async_4_zfill(dst + (uint32_t)(j * 32 + lane) * 4u, v ? src_p + row : p.sp, v);
+          if (azp) cp_async_4_zfill(dst + (uint32_t)(kBM + BN + j * 32 + lane) * 4u, v ? src_zp + row : p.sp, v);
         }
         const float* src_q = p.sq + ti.sq_off + (long long)g * p.sq_gstride;
+        const float* src_zq = azp ? p.zq + (long long)g * p.sq_gstride : nullptr;
 #pragma unroll
         for (int j = 0; j < BN / 32; ++j) {
           const int q = ti.q0 + j * 32 + lane;
           const bool v = q < ti.q_lim;
           cp_async_4_zfill(dst + (uint32_t)(kBM + j * 32 + lane) * 4u, v ? src_q + q : p.sq, v);
+          if (azp) cp_async_4_zfill(dst + (uint32_t)(2 * kBM + BN + j * 32 + lane) * 4u, v ? src_zq + q : p.sq, v);
         }
         cp_async_mbar_arrive_noinc(bar_sc_full + ss * 8);   // fires when this lane's copies have landed
       }
@@ -894,8 +914,13 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     // ---------------- epilogue ----------------
     setmaxnreg_inc<R::EPI>();
     if (p.epi_mode == EPI_GROUP) {
-      if (p.swap) epilogue_group<BN, __nv_bfloat16, true, CG, EW>(p, smem, tmem_base, bar_i8_empty, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
-      else epilogue_group<BN, __nv_bfloat16, false, CG, EW>(p, smem, tmem_base, bar_i8_empty, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
+      if (p.zp != nullptr) {
+        if (p.swap) epilogue_group<BN, __nv_bfloat16, true, CG, EW, true>(p, smem, tmem_base, bar_i8_empty, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
+        else epilogue_group<BN, __nv_bfloat16, false, CG, EW, true>(p, smem, tmem_base, bar_i8_empty, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
+      } else {
+        if (p.swap) epilogue_group<BN, __nv_bfloat16, true, CG, EW, false>(p, smem, tmem_base, bar_i8_empty, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
+        else epilogue_group<BN, __nv_bfloat16, false, CG, EW, false>(p, smem, tmem_base, bar_i8_empty, arr_tm_empty, bar_sc_full, bar_sc_empty, abort_flag);
+      }
     } else if (p.epi_mode == EPI_CHANNEL) {
       if (p.out_dtype == I4TC_FP16) {
         if (p.swap) epilogue_channel<BN, __half, true, CG, EW>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);

@@ -250,94 +250,7 @@ __global__ void __launch_bounds__(256) weight_group_sums_kernel(const uint32_t* 
   out[r] = (float)sum;
 }
 
-// out[m, n] = bf16( sum_s ws[s][m, n] + sum_g (sa[g, m] * adj[g, m]) * (sb[g, n] * wcs[g, n]) ), g ascending.
-// A thread owns a 4 x 4 block of outputs: the row factors are warp-uniform loads, the column factors and the
-// partial sums 16-byte loads (VEC: N % 4 == 0 and 16-byte aligned pointers).
-template <bool VEC>
-__global__ void __launch_bounds__(256) azp_finish_kernel(const float* __restrict__ ws, long long stride, int splits,
-                                                         const float* __restrict__ sa, const float* __restrict__ sb,
-                                                         const float* __restrict__ adj, const float* __restrict__ wcs,
-                                                         int G, long long M, long long N,
-                                                         __nv_bfloat16* __restrict__ out) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long long n0 = ((long long)blockIdx.x * 32 + lane) * 4;
-  const long long m0 = ((long long)blockIdx.y * 8 + warp) * 4;
-  if (n0 >= N || m0 >= M) return;
-  float corr[4][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) corr[i][j] = 0.0f;
-  for (int g = 0; g < G; ++g) {
-    float a[4], b[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const long long m = m0 + i;
-      a[i] = (m < M) ? __ldg(sa + (long long)g * M + m) * __ldg(adj + (long long)g * M + m) : 0.0f;
-    }
-    if (VEC) {
-      const float4 s4 = __ldg(reinterpret_cast<const float4*>(sb + (long long)g * N + n0));
-      const float4 c4 = __ldg(reinterpret_cast<const float4*>(wcs + (long long)g * N + n0));
-      b[0] = s4.x * c4.x; b[1] = s4.y * c4.y; b[2] = s4.z * c4.z; b[3] = s4.w * c4.w;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const long long n = n0 + j;
-        b[j] = (n < N) ? __ldg(sb + (long long)g * N + n) * __ldg(wcs + (long long)g * N + n) : 0.0f;
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) corr[i][j] = fmaf(a[i], b[j], corr[i][j]);
-  }
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const long long m = m0 + i;
-    if (m >= M) break;
-    const long long idx = m * N + n0;
-    if (VEC) {
-      float4 acc = *reinterpret_cast<const float4*>(ws + idx);
-      for (int s = 1; s < splits; ++s) {
-        const float4 v = *reinterpret_cast<const float4*>(ws + (long long)s * stride + idx);
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-      }
-      union { __nv_bfloat16 h[4]; uint2 u; } pk;
-      pk.h[0] = __float2bfloat16_rn(acc.x + corr[i][0]);
-      pk.h[1] = __float2bfloat16_rn(acc.y + corr[i][1]);
-      pk.h[2] = __float2bfloat16_rn(acc.z + corr[i][2]);
-      pk.h[3] = __float2bfloat16_rn(acc.w + corr[i][3]);
-      *reinterpret_cast<uint2*>(out + idx) = pk.u;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (n0 + j >= N) break;
-        float acc = ws[idx + j];
-        for (int s = 1; s < splits; ++s) acc += ws[(long long)s * stride + idx + j];
-        out[idx + j] = __float2bfloat16_rn(acc + corr[i][j]);
-      }
-    }
-  }
-}
-
 }  // namespace
-
-int launch_azp_finish(const float* ws, long long stride, int splits, const float* sa, const float* sb,
-                      const float* adj, const float* wcs, int G, long long M, long long N, void* out,
-                      cudaStream_t st) {
-  const bool vec = (N % 4 == 0) && (stride % 4 == 0) && aligned_to(ws, 16) && aligned_to(sb, 16) &&
-                   aligned_to(wcs, 16) && aligned_to(out, 8);
-  const dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + 31) / 32));
-  I4TC_REQUIRE(grid.y <= 65535u, I4TC_EINVAL, "M too large for the zero-point pass");
-  if (vec)
-    azp_finish_kernel<true><<<grid, 256, 0, st>>>(ws, stride, splits, sa, sb, adj, wcs, G, M, N,
-                                                  static_cast<__nv_bfloat16*>(out));
-  else
-    azp_finish_kernel<false><<<grid, 256, 0, st>>>(ws, stride, splits, sa, sb, adj, wcs, G, M, N,
-                                                   static_cast<__nv_bfloat16*>(out));
-  I4TC_CUDA(cudaGetLastError());
-  return I4TC_OK;
-}
 
 }  // namespace i4tc
 

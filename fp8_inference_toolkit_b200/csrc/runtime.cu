@@ -2,6 +2,7 @@
 // bounded waits write to, and the tensor-map cache.
 #include "gemm.cuh"
 #include <mutex>
+#include <vector>
 #include <cstring>
 
 namespace i4tc {
@@ -29,26 +30,55 @@ int device_info(int device, const DeviceInfo** out) {
   return I4TC_OK;
 }
 
-int split_workspace(int device, size_t bytes, float** out) {
+// ---- split-K workspaces ------------------------------------------------------------------
+// One grow-only arena per (device, stream): calls on different streams never share partial sums, and a pointer
+// that was handed out stays valid until i4tc_release_workspaces or process exit -- a CUDA graph captured earlier,
+// or a launch still in flight, may hold it.  Growth allocates a new, larger buffer and keeps the old ones.
+struct WsArena {
+  int device;
+  cudaStream_t stream;
+  float* cur = nullptr;
+  size_t cur_bytes = 0;
+  std::vector<void*> retired;   // smaller buffers handed out earlier
+};
+static std::vector<WsArena> g_arenas;
+static constexpr size_t kWsMinBytes = 16u << 20;
+
+static int arena_reserve(int device, cudaStream_t stream, size_t bytes, float** out) {
+  WsArena* a = nullptr;
+  for (auto& x : g_arenas)
+    if (x.device == device && x.stream == stream) a = &x;
+  if (a == nullptr) {
+    g_arenas.push_back(WsArena{device, stream});
+    a = &g_arenas.back();
+  }
+  if (a->cur_bytes < bytes) {
+    DeviceGuard guard(device);
+    I4TC_CUDA(guard.err);
+    size_t want = bytes < kWsMinBytes ? kWsMinBytes : bytes;
+    if (want < 2 * a->cur_bytes) want = 2 * a->cur_bytes;   // geometric growth bounds what the retired buffers hold
+    void* p = nullptr;
+    const cudaError_t e = cudaMalloc(&p, want);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(I4TC_EWORKSPACE,
+                  "the split-K workspace of this stream holds %zu bytes and %zu are needed, but cudaMalloc failed (%s); "
+                  "reserve it beforehand with i4tc_reserve_workspace (outside stream capture)",
+                  a->cur_bytes, bytes, cudaGetErrorName(e));
+    }
+    if (a->cur) a->retired.push_back(a->cur);
+    a->cur = static_cast<float*>(p);
+    a->cur_bytes = want;
+  }
+  if (out) *out = a->cur;
+  return I4TC_OK;
+}
+
+int split_workspace(int device, cudaStream_t stream, size_t bytes, float** out) {
   const DeviceInfo* cinfo;
   if (int rc = device_info(device, &cinfo)) return rc;
   std::lock_guard<std::mutex> lock(g_mutex);
-  DeviceInfo& d = g_info[device];
-  if (d.split_ws_bytes < bytes) {
-    DeviceGuard guard(device);
-    I4TC_CUDA(guard.err);
-    if (d.split_ws) {
-      I4TC_CUDA(cudaDeviceSynchronize());  // earlier launches may still read the old buffer
-      I4TC_CUDA(cudaFree(d.split_ws));
-      d.split_ws = nullptr;
-      d.split_ws_bytes = 0;
-    }
-    size_t want = bytes < (16u << 20) ? (16u << 20) : bytes;
-    I4TC_CUDA(cudaMalloc(&d.split_ws, want));
-    d.split_ws_bytes = want;
-  }
-  *out = d.split_ws;
-  return I4TC_OK;
+  return arena_reserve(device, stream, bytes, out);
 }
 
 // ---- tensor maps -------------------------------------------------------------------------
@@ -146,6 +176,35 @@ extern "C" int i4tc_sm_count(int device) {
   const DeviceInfo* info;
   if (int rc = device_info(device, &info)) return rc < 0 ? rc : -rc;
   return info->sm_count;
+}
+
+extern "C" int i4tc_reserve_workspace(int device, void* stream, int64_t bytes) {
+  I4TC_REQUIRE(bytes >= 0, I4TC_EINVAL, "negative size");
+  const DeviceInfo* info;
+  if (int rc = device_info(device, &info)) return rc;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return arena_reserve(device, static_cast<cudaStream_t>(stream), (size_t)bytes, nullptr);
+}
+
+extern "C" int64_t i4tc_workspace_bytes(int device, void* stream) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (auto& a : g_arenas)
+    if (a.device == device && a.stream == static_cast<cudaStream_t>(stream)) return (int64_t)a.cur_bytes;
+  return 0;
+}
+
+extern "C" int i4tc_release_workspaces(int device) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  I4TC_CUDA(cudaDeviceSynchronize());   // nothing in flight may still use a buffer
+  for (auto it = g_arenas.begin(); it != g_arenas.end();) {
+    if (it->device != device) { ++it; continue; }
+    for (void* p : it->retired) cudaFree(p);
+    if (it->cur) cudaFree(it->cur);
+    it = g_arenas.erase(it);
+  }
+  return I4TC_OK;
 }
 
 extern "C" int i4tc_check_status(int device, void* stream) {

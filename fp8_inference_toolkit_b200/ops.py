@@ -359,6 +359,21 @@ def set_epilogue_warps(warps: int = 0) -> None:
     check(lib.i4tc_set_epilogue_warps(warps), "set_epilogue_warps")
 
 
+def reserve_workspace(nbytes: int, device=None, stream=None) -> None:
+    """Make the split-K workspace of (device, stream) at least ``nbytes`` large now, so that no small-M GEMM on that
+    stream allocates later (call before capturing a CUDA graph).  Defaults: current device, its current stream."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    st = torch.cuda.current_stream(dev) if stream is None else stream
+    check(lib.i4tc_reserve_workspace(dev, st.cuda_stream, int(nbytes)), "reserve_workspace")
+
+
+def workspace_bytes(device=None, stream=None) -> int:
+    """Current size of the split-K workspace of (device, stream); 0 if none was needed yet."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    st = torch.cuda.current_stream(dev) if stream is None else stream
+    return int(lib.i4tc_workspace_bytes(dev, st.cuda_stream))
+
+
 def check_status(device=None) -> None:
     """Raise if any kernel gave up on a bounded wait since the last call (synchronises the stream)."""
     dev = torch.cuda.current_device() if device is None else torch.device(device).index

@@ -35,6 +35,7 @@ extern "C" {
 #define I4TC_EUNSUPPORTED (-3)/* combination not implemented                     */
 #define I4TC_EDEVICE (-4)     /* device is not compute capability 10.x           */
 #define I4TC_EKERNEL (-5)     /* a kernel reported a bounded-wait timeout        */
+#define I4TC_EWORKSPACE (-6)  /* the split-K workspace could not be grown        */
 
 /* element types of floating-point inputs / outputs */
 #define I4TC_BF16 0
@@ -60,9 +61,24 @@ int i4tc_set_tuning(int tile_n, int swap);
 /* Test / tuning hook for the small-M paths with scaled outputs (9..128 tokens): number of K ranges that
  * different thread blocks handle before a fixed-order reduction (0 = automatic, 1 = never split, 2..8 = forced;
  * per-channel results do not depend on it, per-group results only in the order fp32 terms are added).  The
- * partial sums live in a workspace owned by the library (one per device, grown on demand); calls on
- * different streams of one device that both split must not overlap. */
+ * partial sums live in a workspace owned by the library, see i4tc_reserve_workspace. */
 int i4tc_set_split_k(int splits);
+
+/* The split-K workspace.  The small-M GEMMs (9..128 tokens, scaled outputs) may cut K into up to 8 ranges whose
+ * fp32 partial sums (splits * M * N * 4 bytes, at most 4 KiB per output column) go to a buffer that the library
+ * owns, one per (device, stream): calls on different streams never share it.  A buffer that a call has used is never
+ * freed or moved afterwards -- a launch in flight or a CUDA graph captured earlier may still hold its address -- so
+ * when a stream needs more than it has, a larger buffer is allocated beside the old one (geometric growth, 16 MiB
+ * minimum).  That allocation is a cudaMalloc inside the GEMM call: to keep it out of a stream capture or a
+ * latency-critical loop, reserve the largest size beforehand with i4tc_reserve_workspace (any thread, outside
+ * capture; 100 MiB covers N = 24576).  If the allocation fails the GEMM call returns I4TC_EWORKSPACE and launches
+ * nothing.  i4tc_workspace_bytes reports the current size for a stream; i4tc_release_workspaces synchronises the
+ * device and frees every buffer of it (only when no captured graph that used them will be replayed).  Two replays
+ * of graphs captured on one stream that run concurrently on different streams share that stream's buffer and race.
+ * No reference counterpart. */
+int i4tc_reserve_workspace(int device, void* stream, int64_t bytes);
+int64_t i4tc_workspace_bytes(int device, void* stream);
+int i4tc_release_workspaces(int device);
 
 /* Test / tuning hook for large dense problems: whether pairs of thread blocks on two SMs share 256 x 256
  * tiles (-1 = automatic, 0 = never, 1 = whenever the problem allows it: 256-wide tiles, activations on the
@@ -159,9 +175,9 @@ int i4tc_gemm_grouped(const uint8_t* a, const uint8_t* b, const float* scale_a,
  *   out[m,n] = bf16( sum_g scale_a[g,m] * scale_b[g,n] * (acc_g[m,n] + azp_adj[g,m] * w_col_sum[g,n]) ).
  * Replaces cutlass_int4_fused_grouped_gemm_azp and its aliases _v5_azp / _v7_azp (int4_gemm.cu:4298, 3838,
  * 4149; epilogue term :1851-1858) and cutlass_int4_scaled_mm_azp_grouped (:994).  Same operands as
- * i4tc_gemm_grouped plus azp_adj [G, M] and w_col_sum [G, N] (fp32).  The tensor-core kernel leaves the fp32
- * sums of the first term in the library's workspace (M * N * 4 bytes) and a second kernel adds the rank-G
- * second term before the one rounding to bf16; the two terms are each summed in fp32, g ascending. */
+ * i4tc_gemm_grouped plus azp_adj [G, M] and w_col_sum [G, N] (fp32).  The term is added to each group's integer
+ * sum inside the epilogue of the tensor-core kernel, before the scales, in the reference's order
+ * ((acc + azp * wcs) * sx, then the fused multiply-add by sw); no workspace, no second kernel. */
 int i4tc_gemm_grouped_azp(const uint8_t* a, const uint8_t* b, const float* scale_a, const float* scale_b,
                           const float* azp_adj, const float* w_col_sum, void* out, int64_t M, int64_t N,
                           int64_t group_size, int64_t num_groups, int device, void* stream);

@@ -384,3 +384,41 @@ def test_reference_kernel_test_shapes(tc, ops, M, K, N):
     if M <= 32:
         part = ops.int4_grouped_partials(xp, wp, M, N, G)
         assert np.array_equal(part.cpu().numpy(), O.grouped_int_partials(xc, wc))
+
+
+def test_split_k_workspace_is_per_stream_and_never_moves(tc, ops):
+    """The split-K workspace belongs to one (device, stream); growing it keeps the buffer handed out before (a CUDA
+    graph replayed after the growth still computes the right thing), and a second stream gets its own."""
+    rng = np.random.RandomState(3)
+    M, N, G = 64, 512, 16
+    a, b = rand_codes(rng, (G, M, 128)), rand_codes(rng, (G, N, 128))
+    sa = dev_f32((rng.rand(G, M) + 0.01) * 0.1)
+    sb = dev_f32((rng.rand(G, N) + 0.01) * 0.01)
+    ap, bp = dev_packed(a), dev_packed(b)
+    ops.set_split_k(4)
+    side = torch.cuda.Stream()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    with torch.cuda.stream(side):
+        assert ops.workspace_bytes() == 0
+        ops.reserve_workspace(1 << 20)
+        first = ops.workspace_bytes()
+        assert first >= (16 << 20)
+        tc.cutlass_int4_fused_grouped_gemm(ap, bp, sa, sb, out, M, N, 128, G)   # warm-up outside capture
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            tc.cutlass_int4_fused_grouped_gemm(ap, bp, sa, sb, out, M, N, 128, G)
+        ops.reserve_workspace(first * 3)            # grows: a new buffer beside the one the graph holds
+        assert ops.workspace_bytes() >= first * 3
+        big = torch.full((int(first) // 4,), 7.0, device="cuda")   # would reuse freed memory if the old buffer had been freed
+        out.zero_()
+        g.replay()
+        side.synchronize()
+        del big
+    ops.set_split_k(0)
+    ops.check_status()
+    ref = O.linear_grouped(a, b, sa.cpu().numpy(), sb.cpu().numpy())
+    assert_close_bf16(out, ref, "graph replay after workspace growth")
+    other = torch.cuda.Stream()
+    with torch.cuda.stream(other):
+        assert ops.workspace_bytes() == 0               # another stream: its own (not yet needed) workspace

@@ -47,6 +47,65 @@ def test_linear_module_matches_oracle(per_channel):
     assert q2.quantized and torch.equal(q2(x.cuda()), q(x.cuda()))
 
 
+@pytest.mark.parametrize("flags", [
+    {"INT4TC_ASYMMETRIC": "1"},
+    {"INT4TC_CLIP_RATIO": "0.95"},
+    {"INT4TC_ASYMMETRIC": "1", "INT4TC_CLIP_RATIO": "0.95"},
+    {"INT4TC_CALIBRATION_STATS": "file"},
+    {"INT4TC_ASYMMETRIC": "1", "INT4TC_CLIP_RATIO": "0.95", "INT4TC_CALIBRATION_STATS": "file", "INT4TC_SQ_ALPHA": "0.6"},
+])
+def test_linear_module_enhanced_flags_match_oracle(monkeypatch, tmp_path, flags):
+    """The plugin's environment flags (asymmetric codes, clipping, SmoothQuant from a statistics file) reach the
+    kernels through W4A4Linear, one quantiser + one GEMM per forward, and each combination equals the oracle's
+    composition bit for bit (M > 128: the unsplit tensor-core path)."""
+    from fp8_inference_toolkit_b200 import synthetic
+    from fp8_inference_toolkit_b200.calibration import ActivationStatsCollector, apply_smoothing_to_weight, compute_smoothing_factors
+    from fp8_inference_toolkit_b200.linear import W4A4Linear
+
+    K, N, M = 512, 384, 160
+    w = synthetic.weights(N, K, 3)
+    x = (synthetic.activations(M, K, 4).float() + 0.75).to(torch.bfloat16)    # shifted: the asymmetric case
+    lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16)
+    lin.weight.data.copy_(w)
+    stats_file = None
+    if "INT4TC_CALIBRATION_STATS" in flags:
+        holder = torch.nn.Sequential()
+        holder.add_module("proj", lin)
+        col = ActivationStatsCollector(holder)
+        holder(x)
+        col.remove_hooks()
+        stats_file = str(tmp_path / "calib.pt")
+        col.save(stats_file)
+    for k, v in flags.items():
+        monkeypatch.setenv(k, stats_file if v == "file" else v)
+    q = W4A4Linear.from_linear(lin.cuda(), layer_name="proj")
+    y = q(x.cuda())
+    asym = flags.get("INT4TC_ASYMMETRIC") == "1"
+    clip = float(flags.get("INT4TC_CLIP_RATIO", "1.0"))
+    wq, sm = w, None
+    if stats_file is not None:
+        a = x.abs().amax(dim=0).float()
+        sm = compute_smoothing_factors(w, a, float(flags.get("INT4TC_SQ_ALPHA", "0.5"))).to(torch.bfloat16)
+        wq = apply_smoothing_to_weight(w, sm)
+        assert torch.equal(q.smooth_scale.cpu(), sm)
+    wc, ws = O.quant_grouped(wq, 128, "weight")
+    assert np.array_equal(q.weight_int4.cpu().numpy(), O.pack_int4(wc))
+    if asym:
+        xc, xs, adj = O.quant_asymmetric_grouped(x, 128, clip, sm)
+        wcs = O.weight_group_sums(wc)
+        assert np.array_equal(q.w_col_sum.cpu().numpy(), wcs)
+        ref = O.to_bf16(O.linear_grouped_azp_f32(xc, wc, xs, ws, adj, wcs))
+    else:
+        xin = x if sm is None else (x / sm)
+        xc, xs = O.quant_clipped_grouped(xin, 128, clip) if clip < 1.0 else O.quant_grouped(xin, 128, "activation")
+        ref = O.linear_grouped(xc, wc, xs, ws)
+    assert torch.equal(y.cpu(), ref)
+    sd = {k: v.cpu() for k, v in q.state_dict().items()}     # CPU tensors, as after torch.load
+    q2 = W4A4Linear(K, N, layer_name="proj", device="cuda")
+    q2.load_state_dict(sd)
+    assert q2.weight_int4.is_cuda and torch.equal(q2(x.cuda()), y)
+
+
 def test_env_flag_selects_mode(monkeypatch):
     from fp8_inference_toolkit_b200.linear import W4A4Int4TCLinearMethod
 
