@@ -142,12 +142,15 @@ def cpu_reference_step(rows: int, seed: int = 0):
         w = synthetic.weights(N, K, seed + 1 + i)
         G = K // GROUP
         wq = w.float().reshape(N, G, GROUP)
-        ws = (wq.abs().amax(dim=2).clamp(min=1e-12) / 7.0)
+        wa = wq.abs().amax(dim=2)
+        ws = torch.where(wa == 0, torch.ones_like(wa), wa / 7.0)                     # int4_quant.cu:267 (zero group: scale 1)
         wc = torch.clamp(torch.round(wq / ws.unsqueeze(2)), -8, 7).to(torch.int32)  # weights: load time, untimed
         t0 = time.perf_counter()
         xq = x.float().reshape(rows, G, GROUP)
-        xs = (xq.abs().amax(dim=2).clamp(min=1e-12) / 7.0)
-        xc = torch.clamp(torch.round(xq / xs.unsqueeze(2)), -8, 7).to(torch.int8)
+        xa = xq.abs().amax(dim=2)
+        xd = torch.where(xa == 0, torch.ones_like(xa), xa / 7.0)                     # codes come from the un-floored absmax / 7
+        xc = torch.clamp(torch.round(xq / xd.unsqueeze(2)), -8, 7).to(torch.int8)
+        xs = (xa / 7.0).clamp(min=1.0 / (7.0 * 512.0))                               # returned scale: floor of int4_quant.cu:97,142
         packed = (xc[..., 0::2] & 0x0F) | ((xc[..., 1::2] & 0x0F) << 4)  # noqa: F841  (the pack step)
         acc = torch.zeros(rows, N, dtype=torch.float32)
         xi = xc.to(torch.int32)
@@ -164,6 +167,8 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # only this rank works: give it every host thread (a launcher may have pinned OMP_NUM_THREADS to 1)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     cores = torch.get_num_threads()
     budget = 150.0  # seconds for the whole run
     t, ops = cpu_reference_step(2)
@@ -182,7 +187,7 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_sum / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s4*s4->s32, f32 dequant",
-        "data": "synthetic", "config": workload_config(args.m, 1),
+        "data": "synthetic", "config": workload_config(args.m, args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -309,11 +314,16 @@ def run_ours(args) -> None:
     int8_peak = 2.0 * peaks["bf16_tflops"]
     achieved = gemm_ops_rank / gemm_s / 1e12
 
-    # ---- e2e: host buffers through the linear module, copies inside the timed region
-    x_host = [synthetic.activations(M, K, seed=0).pin_memory() for _, K, _ in SHAPES]
+    # ---- e2e: host buffers through the linear module, copies inside the timed region.  The ranks share one host:
+    # each copies M / n rows of the activations from pinned memory and an all-gather over NVLink gives every rank
+    # the whole [M, K] (the GEMM itself stays free of collectives); each rank reads back its own output columns.
+    assert M % world == 0
+    m_loc = M // world
+    x_host = [synthetic.activations(M, K, seed=0)[rank * m_loc:(rank + 1) * m_loc].contiguous().pin_memory()
+              for _, K, _ in SHAPES]
     o_host = [torch.empty(M, l.out_features, dtype=torch.bfloat16).pin_memory() for l in layers]
-    h2d = sum(x.numel() * 2 for x in x_host)
-    d2h = sum(o.numel() * 2 for o in o_host)
+    h2d = sum(x.numel() * 2 for x in x_host) * world   # whole job
+    d2h = sum(o.numel() * 2 for o in o_host) * world
 
     copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     main = torch.cuda.current_stream(dev)
@@ -325,6 +335,10 @@ def run_ours(args) -> None:
         for i, lin in enumerate(layers):
             with torch.cuda.stream(copy_in):
                 xd = x_host[i].to(dev, non_blocking=True)
+                if world > 1:
+                    full = torch.empty(M, xd.shape[1], dtype=xd.dtype, device=dev)
+                    dist.all_gather_into_tensor(full, xd)
+                    xd = full
                 ready = torch.cuda.Event()
                 ready.record(copy_in)
             main.wait_event(ready)
@@ -354,6 +368,11 @@ def run_ours(args) -> None:
         e2e_s = tt.item()
     e2e_val = ops_per_step / e2e_s / 1e12
 
+    del x_host, o_host
+    for lin in layers:
+        lin.weight_int4 = None
+    del layers, xs_dev, outs
+    torch.cuda.empty_cache()
     moe_result = bench_moe(args, world, rank, dev, peaks)
     # the same layer with 4096 tokens per rank (weak scaling), where the exchange is no longer latency-bound
     moe_weak = bench_moe(args, world, rank, dev, peaks, weak=True) if world > 1 else None
@@ -366,7 +385,7 @@ def run_ours(args) -> None:
             "config": workload_config(M, world, per_channel), "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h * 1,
                     "ms_per_step": e2e_s * 1e3},
-            "gpu_launches": args.steps * 2 * len(SHAPES),
+            "gpu_launches": args.steps * 2 * len(SHAPES),   # timed region of `value`: quantise + GEMM per linear
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOPS",
                 "frac": achieved / int8_peak,
@@ -380,18 +399,32 @@ def run_ours(args) -> None:
                 "per_shape_us": {SHAPES[i][0]: statistics.mean(v) * 1e6 for i, v in per_shape.items()},
             },
         }
-        line["moe"] = moe_result
-        if moe_weak is not None:
-            line["moe_weak"] = moe_weak
-        if world == 1 and not args.no_sweep:
-            line["sweep"] = bench_sweep(dev, peaks)
         if world == 1:
+            torch.set_num_threads(max(1, os.cpu_count() or 1))
             t, cops = cpu_reference_step(16)
             t, cops = cpu_reference_step(16)
             line["cpu_baseline"] = {
                 "value": cops / t / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                 "sample": "16 of %d token rows of each of the 4 linears, one pass" % M,
             }
+        if world == 1 and not args.no_sweep:
+            sweep = bench_sweep(dev, peaks)
+            line["sweep"] = sweep
+            # the north-star bars of the sweep as scalars inside the roofline object
+            big = [r for r in sweep if r["M"] >= 1024]
+            line["roofline"]["sweep_min_frac_int8_peak_m1024_up"] = min(r["frac_int8_peak"] for r in big)
+            line["roofline"]["sweep_min_frac_hbm_m1"] = min(r["frac_hbm"] for r in sweep if r["M"] == 1)
+        # the other north-star workloads, smallest objects last so that they survive a truncated log
+        if moe_weak is not None:
+            line["moe_weak"] = moe_weak
+        line["moe"] = moe_result
+        if world == 1 and not args.no_extras:
+            line["prefill"] = bench_prefill(args, dev)
+            line["quant"] = bench_quant(dev, peaks)
+            line["roofline"]["quant_group_frac_hbm"] = line["quant"]["group"]["frac"]
+            line["roofline"]["quant_row_frac_hbm"] = line["quant"]["row"]["frac"]
+            line["roofline"]["prefill_tokens_per_s"] = line["prefill"]["value"]
+        line["roofline"]["moe_tokens_per_s"] = moe_result["value"]
         emit(line)
     if world > 1:
         dist.destroy_process_group()
@@ -465,7 +498,9 @@ def bench_sweep(dev, peaks) -> list:
 def bench_moe(args, world, rank, dev, peaks, weak: bool = False) -> dict:
     """MoE grouped W4A4 layer (BASELINE configs[3]): 128 experts, top-8, 4096 tokens, hidden 2048,
     intermediate 768, group-128; experts and tokens split evenly across ranks, all-to-all dispatch and
-    combine.  Timed from (token rows, expert ids, routing weights) to the combined bf16 output."""
+    combine.  Timed from (token rows, expert ids, routing weights) to the combined bf16 output.
+    Outside the timed region rank 0 checks its rows of the expert-parallel output against the single-GPU layer
+    over all tokens and all experts (which the GPU tests pin bit for bit to the CPU oracle)."""
     import torch.distributed as dist
 
     from fp8_inference_toolkit_b200 import moe, moe_ep, ops, synthetic
@@ -476,17 +511,21 @@ def bench_moe(args, world, rank, dev, peaks, weak: bool = False) -> dict:
     ids, w = moe.moe_route(logits.to(dev), k)
     sl = slice(rank * t_loc, (rank + 1) * t_loc)
     x_l, ids_l, w_l = x[sl].to(dev).contiguous(), ids[sl].contiguous(), w[sl].contiguous()
-    gu, dn = synthetic.moe_weights(e_loc, H, I, seed=10 + rank, device=dev)
-    mw = moe.MoEWeights.quantize(gu, dn)
-    del gu, dn
+
+    def rank_weights(r):
+        gu, dn = synthetic.moe_weights(e_loc, H, I, seed=10 + r, device=dev)
+        return moe.MoEWeights.quantize(gu, dn)
+
+    mw = rank_weights(rank)
+    ep = moe_ep.ExpertParallelMoE(mw, E, t_loc, k, H) if world > 1 else None
 
     def layer():
         if world == 1:
             return moe.moe_layer(x_l, ids_l, w_l, mw)
-        return moe_ep.moe_layer_ep(x_l, ids_l, w_l, mw, E)
+        return ep(x_l, ids_l, w_l)
 
     for _ in range(5):
-        layer()
+        out = layer()
     ops.check_status()
     torch.cuda.synchronize()
     if world > 1:
@@ -495,7 +534,7 @@ def bench_moe(args, world, rank, dev, peaks, weak: bool = False) -> dict:
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        layer()
+        out = layer()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
@@ -506,7 +545,7 @@ def bench_moe(args, world, rank, dev, peaks, weak: bool = False) -> dict:
     ops.check_status()
     ops_layer = T * k * (2 * H * 2 * I + 2 * I * H)
     int8_peak = 2.0 * peaks["bf16_tflops"] * world
-    return {
+    res = {
         "metric": "moe_w4a4_tokens_per_s", "scaling": "weak" if weak else "strong",
         "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "ms_per_layer": ms, "tops": ops_layer / (ms * 1e-3) / 1e12,
@@ -516,6 +555,135 @@ def bench_moe(args, world, rank, dev, peaks, weak: bool = False) -> dict:
                                % (T, e_loc, t_loc),
                    "timed": "sort + dispatch + gather-quantise + gate/up GEMM + SwiGLU-quantise + down GEMM + combine"},
     }
+    if world > 1:
+        res["stages_us"] = ep.stage_times_us(x_l, ids_l, w_l)
+        if ep.overflowed():
+            res["note"] = "a dispatch buffer overflowed in this run and the step was redone with exact split sizes"
+    else:
+        res["roofline"] = moe_roofline(moe, x_l, ids_l, w_l, mw, ms, ops_layer, peaks)
+    # ---- parity, outside the timed region (rank 0; the weak case holds world x the tokens and is checked the same way)
+    if rank == 0 and world > 1:
+        full = [rank_weights(r) for r in range(world)]
+        mw_all = moe.MoEWeights(torch.cat([f.gate_up_packed for f in full]), torch.cat([f.gate_up_scale for f in full]),
+                                torch.cat([f.down_packed for f in full]), torch.cat([f.down_scale for f in full]), E, H, I)
+        ref = moe.moe_layer(x.to(dev), ids, w, mw_all)[sl].float()
+        got = out.float()
+        denom = torch.maximum(ref.abs(), 1e-3 * ref.abs().max())
+        res["parity"] = {"checked_rows": int(ref.shape[0]), "against": "single-GPU layer over all tokens and experts",
+                         "max_rel": float(((got - ref).abs() / denom).max()),
+                         "cos": float(torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0)),
+                         "identical": bool(torch.equal(got, ref))}
+        del full, mw_all
+    if ep is not None:
+        ep.close()
+    return res
+
+
+def moe_roofline(moe, x, ids, w, mw, ms_layer, ops_layer, peaks) -> dict:
+    """Single-GPU MoE layer stage by stage (CUDA events around each launch group, mean of 10 passes)."""
+    T, k = ids.shape
+    names = ["sort", "gather_quant", "gemm_gate_up", "silu_quant", "gemm_down", "combine"]
+    acc = {n: 0.0 for n in names}
+    reps = 10
+    for it in range(reps + 2):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
+        ev[0].record()
+        sp, inv, off = moe.moe_sort_tokens(ids, mw.num_experts)
+        ev[1].record()
+        ap, asc = moe.moe_gather_quant(x, sp, k)
+        ev[2].record()
+        P = asc.shape[1]
+        h = torch.empty((P, 2 * mw.inter), dtype=torch.bfloat16, device=x.device)
+        moe.moe_w4a4_grouped_gemm(ap, asc, mw.gate_up_packed, mw.gate_up_scale, off, h, 2 * mw.inter, mw.hidden // 128,
+                                  mw.num_experts)
+        ev[3].record()
+        hp, hs = moe.moe_silu_mul_quant(h)
+        ev[4].record()
+        y = torch.empty((P, mw.hidden), dtype=torch.bfloat16, device=x.device)
+        moe.moe_w4a4_grouped_gemm(hp, hs, mw.down_packed, mw.down_scale, off, y, mw.hidden, mw.inter // 128, mw.num_experts)
+        ev[5].record()
+        moe.moe_combine(y, inv, w, T, k)
+        ev[6].record()
+        torch.cuda.synchronize()
+        if it >= 2:
+            for i, n in enumerate(names):
+                acc[n] += ev[i].elapsed_time(ev[i + 1]) * 1e3 / reps
+    gemm_us = acc["gemm_gate_up"] + acc["gemm_down"]
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    P = T * k
+    H, I = mw.hidden, mw.inter
+    # bytes a layer has to move once: token rows in, packed rows + scales between the stages, bf16 GEMM outputs, weights
+    byts = (T * H * 2 + P * (H // 2 + 4 * H // 128) * 2 + P * 2 * I * 2 * 2 + P * (I // 2 + 4 * I // 128) * 2
+            + P * H * 2 * 2 + T * H * 2 + mw.gate_up_packed.numel() + mw.down_packed.numel())
+    return {"bound": "tensor", "achieved": ops_layer / (gemm_us * 1e-6) / 1e12, "peak": int8_peak, "unit": "TOPS",
+            "frac": ops_layer / (gemm_us * 1e-6) / 1e12 / int8_peak, "kernel": "w4a4_gemm_kernel (grouped-tile scheduler), 2 launches",
+            "layer_frac_of_int8_peak": ops_layer / (ms_layer * 1e-3) / 1e12 / int8_peak,
+            "layer_bytes": byts, "layer_frac_of_hbm": byts / (ms_layer * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "stages_us": {n: round(v, 1) for n, v in acc.items()}, "gemm_share": gemm_us / sum(acc.values())}
+
+
+def bench_quant(dev, peaks, M: int = 16384, K: int = 12288, steps: int = 10) -> dict:
+    """BASELINE configs[2] at its largest shape: fused quantise+pack of bf16 [M, K] (1 % outlier channels x20), per-token
+    and per-group-128 scales; bytes per launch = 2MK + MK/2 + 4 M G (int4_native_tc/profile_bottleneck.py:121-148).
+    Two inputs of 403 MB alternate (larger than L2); CUDA events around every launch."""
+    import int4_native_tc as tc
+    from fp8_inference_toolkit_b200 import synthetic
+
+    xs = [synthetic.activations(M, K, seed=i, outlier_frac=0.01, device=dev) for i in range(2)]
+    fns = {"row": lambda x: tc.dynamic_int4_quant(x), "group": lambda x: tc.dynamic_int4_quant_grouped(x, GROUP)}
+    res = {}
+    for mode, fn in fns.items():
+        for i in range(4):
+            fn(xs[i & 1])
+        torch.cuda.synchronize()
+        evs = []
+        for i in range(steps):
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(xs[i & 1]); e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        us = statistics.mean(a.elapsed_time(b) for a, b in evs) * 1e3
+        byts = 2 * M * K + M * K // 2 + 4 * M * (1 if mode == "row" else K // GROUP)
+        res[mode] = {"us": us, "GBs": byts / us / 1e3, "frac": byts / us / 1e3 / peaks["hbm_gbs"], "bytes": byts}
+    res["config"] = {"workload": f"BASELINE configs[2]: fused quantise+pack, bf16 [{M},{K}]", "bound": "hbm",
+                     "peak_GBs": peaks["hbm_gbs"], "peak_source": f"copy bandwidth of MEASURED_PEAKS.json ({peaks['source']})"}
+    del xs
+    return res
+
+
+def bench_prefill(args, dev, steps: int = 2) -> dict:
+    """BASELINE configs[4]: Qwen3-8B-architecture prefill (36 layers, batch 32 x 512), all linears W4A4 group-128,
+    random-init weights; token ids come from pinned host memory and a slice of the result is read back each step."""
+    from fp8_inference_toolkit_b200 import ops
+    from fp8_inference_toolkit_b200.qwen3 import Qwen3Config, Qwen3Prefill
+
+    cfg = Qwen3Config(layers=args.layers)
+    model = Qwen3Prefill(cfg, dev)
+    B, S = args.batch, args.seq
+    ids_host = torch.randint(0, cfg.vocab, (B, S), generator=torch.Generator().manual_seed(0)).pin_memory()
+
+    def step():
+        y = model(ids_host.to(dev, non_blocking=True))
+        return y[:, -1, :8].float().cpu()
+
+    step()
+    ops.check_status()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_status()
+    ms = e0.elapsed_time(e1) / steps
+    lin_ops = 2 * B * S * cfg.layers * sum(N * K for _, K, N in SHAPES)
+    del model
+    torch.cuda.empty_cache()
+    return {"metric": "qwen3_8b_w4a4_prefill_tokens_per_s", "value": B * S / (ms * 1e-3), "unit": "tokens/s",
+            "ms_per_step": ms, "steps": steps, "linear_tops": lin_ops / (ms * 1e-3) / 1e12,
+            "config": {"workload": "BASELINE configs[4]: Qwen3-8B-shaped prefill, %d layers, batch %d x %d, W4A4 group-128, "
+                                   "bf16 attention" % (cfg.layers, B, S)}}
 
 
 def run_quant(args) -> None:
@@ -622,6 +790,7 @@ def main() -> None:
     ap.add_argument("--seq", type=int, default=512)
     ap.add_argument("--k", type=int, default=12288, help="row length for --workload quant")
     ap.add_argument("--no-sweep", action="store_true", help="skip the kernel-only M x shape sweep")
+    ap.add_argument("--no-extras", action="store_true", help="skip the quantise+pack and prefill objects of the default line")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)

@@ -160,6 +160,149 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Expert parallelism with fixed-capacity exchange buffers (no host synchronisation).
+//
+// A rank sorts its (token, slot) pairs by global expert id; sorted by expert is sorted by owner rank.  For every
+// destination rank d it fills a block of the send buffer: one header row, then up to `cap` quantised token rows
+// (G x 64 bytes of codes followed by G fp32 group scales) in sorted order.  Header (int32): [0] rows in the block,
+// [1] sorted position of the block's first row at the source, [2 .. 2 + e_loc) rows per local expert of d.
+// Blocks have a fixed size, so the all-to-all needs no split sizes from the device.  A destination that would get
+// more than `cap` rows raises the overflow flag (the counts are clipped so that every index stays in range); the
+// caller then repeats the step with exact split sizes.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) moe_ep_plan_kernel(const int32_t* __restrict__ expert_offsets,
+                                                         const int32_t* __restrict__ sorted_pairs, int P, int world,
+                                                         int e_loc, int cap, long long row_bytes,
+                                                         uint8_t* __restrict__ send_buf, int32_t* __restrict__ slot,
+                                                         int32_t* __restrict__ ret_row, unsigned int* overflow) {
+  if (blockIdx.x == 0) {
+    // headers: thread (d, e) pairs in a strided loop
+    for (int i = threadIdx.x; i < world * (e_loc + 2); i += blockDim.x) {
+      const int d = i / (e_loc + 2), f = i - d * (e_loc + 2);
+      const int start = expert_offsets[d * e_loc];
+      int32_t* hdr = reinterpret_cast<int32_t*>(send_buf + (long long)d * (1 + cap) * row_bytes);
+      if (f == 0) {
+        const int n = expert_offsets[(d + 1) * e_loc] - start;
+        hdr[0] = min(n, cap);
+        if (n > cap) atomicOr(overflow, 1u);
+      } else if (f == 1) {
+        hdr[1] = start;
+      } else {
+        const int e = d * e_loc + (f - 2);
+        const int a = min(expert_offsets[e] - start, cap), b = min(expert_offsets[e + 1] - start, cap);
+        hdr[f] = b - a;
+      }
+    }
+  }
+  const int total = expert_offsets[world * e_loc];
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < P; p += gridDim.x * blockDim.x) {
+    int s = -1;
+    if (p < total) {
+      int d = 0;
+      while (d + 1 < world && p >= expert_offsets[(d + 1) * e_loc]) ++d;
+      const int j = p - expert_offsets[d * e_loc];
+      if (j < cap) {
+        s = d * (1 + cap) + 1 + j;
+        ret_row[sorted_pairs[p]] = d * cap + j;
+      }
+    }
+    slot[p] = s;
+  }
+}
+
+// Receiver, step 1 (one block): read the `world` headers, build the local expert offsets and, per (source, expert),
+// where that run of rows starts in expert-sorted order and where it starts inside the source's block.
+// meta layout (int32): tot[world] | base[world][e_loc] | cum[world][e_loc + 1].
+__global__ void __launch_bounds__(256) moe_ep_offsets_kernel(const uint8_t* __restrict__ recv_buf, int world, int e_loc,
+                                                            int cap, long long row_bytes,
+                                                            int32_t* __restrict__ expert_offsets_loc,
+                                                            int32_t* __restrict__ meta, int32_t* __restrict__ rows_dev) {
+  __shared__ int s_off[kMaxExperts + 1];
+  int32_t* tot = meta;
+  int32_t* base = meta + world;
+  int32_t* cum = base + world * e_loc;
+  const int e = threadIdx.x;
+  int mine = 0;
+  if (e < e_loc)
+    for (int s = 0; s < world; ++s)
+      mine += reinterpret_cast<const int32_t*>(recv_buf + (long long)s * (1 + cap) * row_bytes)[2 + e];
+  if (e < kMaxExperts) s_off[e + 1] = (e < e_loc) ? mine : 0;
+  if (e == 0) s_off[0] = 0;
+  __syncthreads();
+  if (e == 0) {
+    for (int i = 1; i <= e_loc; ++i) s_off[i] += s_off[i - 1];
+    *rows_dev = s_off[e_loc];
+  }
+  __syncthreads();
+  if (e <= e_loc) expert_offsets_loc[e] = s_off[e];
+  if (e < e_loc) {
+    int run = s_off[e];
+    for (int s = 0; s < world; ++s) {
+      base[s * e_loc + e] = run;
+      run += reinterpret_cast<const int32_t*>(recv_buf + (long long)s * (1 + cap) * row_bytes)[2 + e];
+    }
+  }
+  if (e < world) {
+    const int32_t* hdr = reinterpret_cast<const int32_t*>(recv_buf + (long long)e * (1 + cap) * row_bytes);
+    int run = 0;
+    for (int i = 0; i < e_loc; ++i) {
+      cum[e * (e_loc + 1) + i] = run;
+      run += hdr[2 + i];
+    }
+    cum[e * (e_loc + 1) + e_loc] = run;
+    tot[e] = min(min(hdr[0], run), cap);
+  }
+}
+
+// Receiver, step 2: one warp per received row (source s, index j): find its local expert, hence its position in
+// expert-sorted order, and move codes and scales into the group-major layout the grouped GEMM reads.
+__global__ void __launch_bounds__(256) moe_ep_scatter_kernel(const uint8_t* __restrict__ recv_buf, int world, int e_loc,
+                                                            int cap, long long row_bytes, int G, long long r_max,
+                                                            const int32_t* __restrict__ meta,
+                                                            uint8_t* __restrict__ ap, float* __restrict__ asc,
+                                                            int32_t* __restrict__ pos_of) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + warp;
+  if (row >= (long long)world * cap) return;
+  const int s = (int)(row / cap), j = (int)(row - (long long)s * cap);
+  const int32_t* tot = meta;
+  const int32_t* base = meta + world;
+  const int32_t* cum = base + world * e_loc + s * (e_loc + 1);
+  if (j >= tot[s]) {
+    if (lane == 0) pos_of[row] = -1;
+    return;
+  }
+  int lo = 0, hi = e_loc - 1;   // last expert whose run starts at or before j
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cum[mid] <= j) lo = mid; else hi = mid - 1;
+  }
+  const long long pos = base[s * e_loc + lo] + (j - cum[lo]);
+  const uint8_t* src = recv_buf + ((long long)s * (1 + cap) + 1 + j) * row_bytes;
+  for (int c = lane; c < G * 4; c += 32) {     // 16-byte chunks of the codes: group c / 4, quarter c % 4
+    const uint4 v = *reinterpret_cast<const uint4*>(src + (long long)c * 16);
+    *reinterpret_cast<uint4*>(ap + ((long long)(c >> 2) * r_max + pos) * 64 + (c & 3) * 16) = v;
+  }
+  const float* ssrc = reinterpret_cast<const float*>(src + (long long)G * 64);
+  for (int g = lane; g < G; g += 32) asc[(long long)g * r_max + pos] = ssrc[g];
+  if (lane == 0) pos_of[row] = (int32_t)pos;
+}
+
+// Expert outputs back into the order each source sent its rows in: ret_send[s][j] = y[pos_of[s][j]].
+__global__ void __launch_bounds__(256) moe_ep_pack_return_kernel(const __nv_bfloat16* __restrict__ y,
+                                                                const int32_t* __restrict__ pos_of, long long rows,
+                                                                int H, __nv_bfloat16* __restrict__ ret_send) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const int pos = pos_of[row];
+  if (pos < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(y + (long long)pos * H);
+  uint4* dst = reinterpret_cast<uint4*>(ret_send + row * H);
+  for (int c = lane; c < H / 8; c += 32) dst[c] = __ldg(src + c);
+}
+
 int moe_sort_launch(const int32_t* ids, int64_t P, int64_t E, int32_t* sorted_pairs, int32_t* inv_pairs,
                     int32_t* expert_offsets, int32_t* scratch, cudaStream_t st) {
   const int chunks = (int)((P + kSortChunk - 1) / kSortChunk);
@@ -277,6 +420,68 @@ extern "C" int i4tc_moe_sort_noalloc(const int32_t* expert_ids, int64_t num_pair
   // Nothing in the scratch has to start at zero: the histogram pass writes every entry that the
   // scan and scatter passes of this call read, so the previous call's contents are never seen.
   return moe_sort_launch(expert_ids, num_pairs, num_experts, sorted_pairs, inv_pairs, expert_offsets, scratch, st);
+}
+
+extern "C" int i4tc_moe_ep_plan(const int32_t* expert_offsets, const int32_t* sorted_pairs, int64_t num_pairs,
+                                int64_t num_experts, int64_t world, int64_t cap, int64_t row_bytes, void* send_buf,
+                                int32_t* slot, int32_t* ret_row, unsigned int* overflow, int device, void* stream) {
+  I4TC_REQUIRE(world > 0 && num_experts > 0 && num_experts % world == 0 && num_experts <= kMaxExperts, I4TC_EINVAL,
+               "experts must divide evenly across ranks (at most %d experts)", kMaxExperts);
+  I4TC_REQUIRE(cap > 0 && cap < (1 << 24) && num_pairs >= 0 && num_pairs < (1ll << 31), I4TC_EINVAL, "bad capacity or size");
+  const int64_t e_loc = num_experts / world;
+  I4TC_REQUIRE(row_bytes % 16 == 0 && row_bytes >= 4 * (2 + e_loc), I4TC_EINVAL,
+               "a buffer row must be a multiple of 16 bytes and hold the %lld header integers", (long long)(2 + e_loc));
+  I4TC_REQUIRE(expert_offsets && send_buf && slot && ret_row && overflow && (sorted_pairs || num_pairs == 0), I4TC_EINVAL,
+               "null pointer");
+  I4TC_REQUIRE(aligned_to(send_buf, 16), I4TC_EALIGN, "send buffer must be 16-byte aligned");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // pairs the sort left out (ids outside [0, E)) and pairs beyond the capacity have no row on the way back
+  if (num_pairs > 0) I4TC_CUDA(cudaMemsetAsync(ret_row, 0xFF, num_pairs * sizeof(int32_t), st));
+  int64_t blocks = (num_pairs + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 1024) blocks = 1024;
+  moe_ep_plan_kernel<<<(unsigned)blocks, 256, 0, st>>>(expert_offsets, sorted_pairs, (int)num_pairs, (int)world, (int)e_loc,
+                                                       (int)cap, row_bytes, static_cast<uint8_t*>(send_buf), slot, ret_row,
+                                                       overflow);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+extern "C" int64_t i4tc_moe_ep_meta_ints(int64_t world, int64_t e_loc) { return world + world * e_loc + world * (e_loc + 1); }
+
+extern "C" int i4tc_moe_ep_unpack(const void* recv_buf, int64_t world, int64_t e_loc, int64_t cap, int64_t row_bytes,
+                                  int64_t num_groups, uint8_t* a_packed, float* a_scale, int32_t* expert_offsets_loc,
+                                  int32_t* pos_of, int32_t* meta, int32_t* rows_dev, int device, void* stream) {
+  I4TC_REQUIRE(world > 0 && world <= 256 && e_loc > 0 && e_loc <= kMaxExperts && cap > 0 && num_groups > 0, I4TC_EINVAL, "bad sizes");
+  I4TC_REQUIRE(row_bytes == num_groups * 68, I4TC_EINVAL, "a row is 64 bytes of codes and one fp32 scale per group");
+  I4TC_REQUIRE(recv_buf && a_packed && a_scale && expert_offsets_loc && pos_of && meta && rows_dev, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(aligned_to(recv_buf, 16) && aligned_to(a_packed, 16), I4TC_EALIGN, "buffers must be 16-byte aligned");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint8_t* rb = static_cast<const uint8_t*>(recv_buf);
+  moe_ep_offsets_kernel<<<1, 256, 0, st>>>(rb, (int)world, (int)e_loc, (int)cap, row_bytes, expert_offsets_loc, meta, rows_dev);
+  const long long rows = world * cap;
+  moe_ep_scatter_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(rb, (int)world, (int)e_loc, (int)cap, row_bytes,
+                                                                  (int)num_groups, rows, meta, a_packed, a_scale, pos_of);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_moe_ep_pack_return(const void* y, const int32_t* pos_of, int64_t rows, int64_t H, void* ret_send,
+                                       int device, void* stream) {
+  I4TC_REQUIRE(rows >= 0 && H > 0 && H % 8 == 0, I4TC_EINVAL, "H must be a positive multiple of 8");
+  if (rows == 0) return I4TC_OK;
+  I4TC_REQUIRE(y && pos_of && ret_send, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(aligned_to(y, 16) && aligned_to(ret_send, 16), I4TC_EALIGN, "buffers must be 16-byte aligned");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  moe_ep_pack_return_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y), pos_of, rows, (int)H, static_cast<__nv_bfloat16*>(ret_send));
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
 }
 
 extern "C" int i4tc_moe_combine(const void* y, const int32_t* inv_pairs, const float* w, int64_t T, int64_t top_k,

@@ -312,16 +312,34 @@ __device__ __forceinline__ float absmax_of<__nv_bfloat16>(const Vec8<__nv_bfloat
 // log2(LPG) shuffles, its reciprocal is formed once per lane, and each lane leaves 16 packed bytes
 // with one 128-bit store.  The block walks `segs_per_block` segments of its rows and loads segment
 // s+1 while it quantises segment s.
-template <typename T, int LPG, int MODE, bool GIVEN>
+// OUTMAP (expert-parallel MoE): output row r goes to row out.row_map[r] (skipped when negative) of a layout given by
+// byte / float strides instead of the group-major default, and rows at or beyond *out.rows_dev are skipped.
+struct QuantOutMap {
+  const int32_t* row_map;   // nullptr: identity
+  const int32_t* rows_dev;  // nullptr: all `rows`
+  long long pk_gstride, pk_rstride;   // bytes between groups / rows of the packed output
+  long long sc_gstride, sc_rstride;   // floats between groups / rows of the scale output
+};
+
+template <typename T, int LPG, int MODE, bool GIVEN, bool OUTMAP = false>
 __global__ void __launch_bounds__(256) quant_grouped_kernel(
     const T* __restrict__ x, int64_t rows, int K, int64_t ldx, const int32_t* __restrict__ row_index,
     int index_div, int64_t src_rows, const float* __restrict__ given_scale, uint8_t* __restrict__ packed,
-    float* __restrict__ scale, int role, int segs_per_block, const T* __restrict__ aux, float eps) {
+    float* __restrict__ scale, int role, int segs_per_block, const T* __restrict__ aux, float eps,
+    QuantOutMap out = QuantOutMap()) {
   constexpr int GS = LPG * kQLane;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t r0 = (int64_t)blockIdx.x * kQRows;
   const int64_t r = r0 + warp;
-  const bool row_ok = r < rows;
+  bool row_ok = r < rows;
+  int64_t orow = r;
+  if (OUTMAP) {
+    if (out.rows_dev != nullptr && r >= (int64_t)__ldg(out.rows_dev)) row_ok = false;
+    if (row_ok && out.row_map != nullptr) {
+      orow = __ldg(out.row_map + r);
+      if (orow < 0) row_ok = false;
+    }
+  }
   const int nseg = (K + kQSeg - 1) / kQSeg;
   const int seg_begin = blockIdx.y * segs_per_block;
   const int seg_end = min(nseg, seg_begin + segs_per_block);
@@ -375,7 +393,10 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
       q = make_recip<true>(absmax);
       // one lane per group writes the scale (the IEEE division absmax / 7 happens here, off the
       // per-element path); neighbouring rows fill the same 32-byte sector from other warps
-      if (ok && (lane % LPG) == 0) scale[(int64_t)g * rows + r] = scale_out(absmax, role);
+      if (ok && (lane % LPG) == 0) {
+        if (OUTMAP) scale[(int64_t)g * out.sc_gstride + orow * out.sc_rstride] = scale_out(absmax, role);
+        else scale[(int64_t)g * rows + r] = scale_out(absmax, role);
+      }
     }
     if (ok) {
       const bool zero = !GIVEN && absmax == 0.f;
@@ -384,7 +405,8 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
       w.y = pack8<T, GIVEN>(cur[1], q, zero);
       w.z = pack8<T, GIVEN>(cur[2], q, zero);
       w.w = pack8<T, GIVEN>(cur[3], q, zero);
-      uint8_t* dst = packed + ((int64_t)g * rows + r) * (GS / 2) + (lane % LPG) * 16;
+      uint8_t* dst = OUTMAP ? packed + (int64_t)g * out.pk_gstride + orow * out.pk_rstride + (lane % LPG) * 16
+                            : packed + ((int64_t)g * rows + r) * (GS / 2) + (lane % LPG) * 16;
       *reinterpret_cast<uint4*>(dst) = w;
     }
 #pragma unroll
@@ -544,6 +566,25 @@ static int launch_grouped_t(const T* x, int64_t rows, int64_t K, int64_t ldx, in
   return I4TC_OK;
 }
 
+// Mapped-output launches (bf16 input, group size 128): MODE 1 = gather rows through row_index, MODE 2 = SwiGLU first.
+template <int MODE>
+static int launch_grouped_mapped(const __nv_bfloat16* x, int64_t rows, int64_t K, int64_t ldx, const int32_t* row_index,
+                                 int index_div, int64_t src_rows, uint8_t* packed, float* scale, const QuantOutMap& out,
+                                 cudaStream_t st) {
+  if (rows == 0 || K == 0) return I4TC_OK;
+  const int64_t row_blocks = (rows + kQRows - 1) / kQRows;
+  const int nseg = (int)((K + kQSeg - 1) / kQSeg);
+  int spb = nseg;
+  if (row_blocks < 2048) spb = (int)((int64_t)nseg * row_blocks / 2048);
+  if (spb < 1) spb = 1;
+  dim3 grid((unsigned)row_blocks, (unsigned)((nseg + spb - 1) / spb));
+  quant_grouped_kernel<__nv_bfloat16, 4, MODE, false, true><<<grid, 256, 0, st>>>(
+      x, rows, (int)K, ldx, row_index, index_div, src_rows, nullptr, packed, scale, I4TC_ROLE_ACTIVATION, spb, nullptr, 0.f,
+      out);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
 static int check_vec_input(const void* x, int dtype, int64_t ldx, const char* who) {
   const size_t es = dtype == I4TC_FP32 ? 4 : 2;
   I4TC_REQUIRE(aligned_to(x, 16) && (ldx * es) % 16 == 0, I4TC_EALIGN,
@@ -671,6 +712,53 @@ extern "C" int i4tc_moe_gather_quant(const void* x, int dtype, int64_t num_token
   I4TC_REQUIRE(sorted_pairs || num_pairs == 0, I4TC_EINVAL, "null sorted_pairs");
   return launch_grouped<1, false>(x, dtype, num_pairs, K, ldx, 128, sorted_pairs, (int)top_k, nullptr, packed,
                                   scale, I4TC_ROLE_ACTIVATION, device, stream, nullptr, 0.f, num_tokens);
+}
+
+extern "C" int i4tc_moe_ep_dispatch_quant(const void* x, int64_t num_tokens, int64_t K, int64_t ldx,
+                                          const int32_t* sorted_pairs, int64_t num_pairs, int64_t top_k,
+                                          const int32_t* slot, void* send_buf, int64_t row_bytes, int device,
+                                          void* stream) {
+  I4TC_REQUIRE(top_k > 0 && top_k < (1 << 20) && num_tokens >= 0 && num_pairs >= 0, I4TC_EINVAL, "bad sizes");
+  I4TC_REQUIRE(K > 0 && K % 128 == 0 && row_bytes == (K / 128) * 68, I4TC_EINVAL,
+               "a row is 64 bytes of codes and one fp32 scale per 128 values");
+  if (num_pairs == 0) return I4TC_OK;
+  I4TC_REQUIRE(x && sorted_pairs && slot && send_buf, I4TC_EINVAL, "null pointer");
+  if (int rc = check_vec_input(x, I4TC_BF16, ldx, "moe_ep_dispatch_quant")) return rc;
+  I4TC_REQUIRE(aligned_to(send_buf, 16), I4TC_EALIGN, "send buffer must be 16-byte aligned");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  const int64_t G = K / 128;
+  QuantOutMap out;
+  out.row_map = slot;
+  out.rows_dev = nullptr;
+  out.pk_gstride = 64;
+  out.pk_rstride = row_bytes;
+  out.sc_gstride = 1;
+  out.sc_rstride = row_bytes / 4;
+  uint8_t* base = static_cast<uint8_t*>(send_buf);
+  return launch_grouped_mapped<1>(static_cast<const __nv_bfloat16*>(x), num_pairs, K, ldx, sorted_pairs, (int)top_k,
+                                  num_tokens, base, reinterpret_cast<float*>(base + G * 64), out,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int i4tc_moe_silu_mul_quant_rows(const void* h, int64_t max_rows, const int32_t* rows_dev, int64_t I,
+                                            uint8_t* packed, float* scale, int device, void* stream) {
+  I4TC_REQUIRE(max_rows >= 0 && I > 0 && I % 128 == 0, I4TC_EINVAL, "intermediate size must be a positive multiple of 128");
+  if (max_rows == 0) return I4TC_OK;
+  I4TC_REQUIRE(h && rows_dev && packed && scale, I4TC_EINVAL, "null pointer");
+  if (int rc = check_vec_input(h, I4TC_BF16, 2 * I, "moe_silu_mul_quant_rows")) return rc;
+  I4TC_REQUIRE(aligned_to(packed, 16), I4TC_EALIGN, "packed output must be 16-byte aligned");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  QuantOutMap out;
+  out.row_map = nullptr;
+  out.rows_dev = rows_dev;
+  out.pk_gstride = max_rows * 64;
+  out.pk_rstride = 64;
+  out.sc_gstride = max_rows;
+  out.sc_rstride = 1;
+  return launch_grouped_mapped<2>(static_cast<const __nv_bfloat16*>(h), max_rows, I, 2 * I, nullptr, 1, 0, packed, scale,
+                                  out, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int i4tc_moe_silu_mul_quant(const void* h, int64_t P, int64_t I, uint8_t* packed, float* scale,

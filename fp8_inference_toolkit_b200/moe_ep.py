@@ -133,3 +133,259 @@ def moe_layer_ep(x: torch.Tensor, expert_ids: torch.Tensor, expert_w: torch.Tens
         y_rows = rows.new_empty((0, x.shape[1]))
     y_back = exchange(y_rows, plan.recv_splits, plan.send_splits, group)
     return combine_fn(y_back, plan.inv_pairs, expert_w, T, k)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Fixed-capacity exchange: the same layer without any host synchronisation
+# ------------------------------------------------------------------------------------------------------------------
+# ``moe_layer_ep`` above needs the split sizes of its all-to-alls on the host, i.e. one device -> host round trip per
+# layer, and moves rows with torch indexing kernels.  The protocol below gives every (source, destination) pair a
+# block of fixed size instead: one header row (row counts per local expert of the destination) followed by up to
+# ``cap`` rows in the source's sorted order.  Blocks of equal size need no split sizes; the receiver derives every
+# position from the headers on the device.  A destination that would get more than ``cap`` rows raises an overflow
+# word that the caller reads after the layer (like the kernels' status word); the step is then repeated through
+# ``moe_layer_ep``, so no token is ever dropped.
+#
+# ``plan_reference`` / ``unpack_reference`` state the bookkeeping in plain torch (any device); the CUDA kernels
+# (``i4tc_moe_ep_plan``, ``i4tc_moe_ep_unpack``) are tested against them, and ``moe_layer_ep_fixed`` runs the whole
+# protocol with them among CPU ranks.
+
+def ep_capacity(pairs_per_rank: int, world: int, capacity_factor: float = 1.0) -> int:
+    """Rows a rank may send to one destination: the mean, times ``capacity_factor``, plus eight standard deviations of
+    a uniform routing and a constant, rounded up to a multiple of 8."""
+    mean = pairs_per_rank / world
+    cap = mean * capacity_factor + 8.0 * mean ** 0.5 + 32.0
+    return int(-(-cap // 8) * 8)
+
+
+def plan_reference(expert_offsets: torch.Tensor, sorted_pairs: torch.Tensor, world: int, cap: int):
+    """Headers, buffer rows and return rows of one dispatch, as ``i4tc_moe_ep_plan`` computes them.
+
+    Returns ``(headers int32 [world, 2 + e_loc], slot int32 [P], ret_row int32 [P], overflow bool)``."""
+    off = expert_offsets.to(torch.int64).cpu()
+    E = off.numel() - 1
+    e_loc = E // world
+    P = sorted_pairs.numel()
+    hdr = torch.zeros(world, 2 + e_loc, dtype=torch.int32)
+    slot = torch.full((P,), -1, dtype=torch.int32)
+    ret_row = torch.full((P,), -1, dtype=torch.int32)
+    overflow = False
+    sp = sorted_pairs.cpu()
+    for d in range(world):
+        start, end = int(off[d * e_loc]), int(off[(d + 1) * e_loc])
+        n = end - start
+        overflow |= n > cap
+        hdr[d, 0] = min(n, cap)
+        hdr[d, 1] = start
+        for e in range(e_loc):
+            a = min(int(off[d * e_loc + e]) - start, cap)
+            b = min(int(off[d * e_loc + e + 1]) - start, cap)
+            hdr[d, 2 + e] = b - a
+        for j in range(min(n, cap)):
+            slot[start + j] = d * (1 + cap) + 1 + j
+            ret_row[int(sp[start + j])] = d * cap + j
+    return hdr, slot, ret_row, overflow
+
+
+def unpack_reference(headers: torch.Tensor, cap: int):
+    """From the ``world`` received headers ([world, 2 + e_loc], one per source): local expert offsets and the
+    expert-sorted position of every received row, as ``i4tc_moe_ep_unpack`` computes them.
+
+    Returns ``(expert_offsets_loc int32 [e_loc + 1], pos_of int32 [world * cap], rows int)``."""
+    h = headers.to(torch.int64).cpu()
+    world, e_loc = h.shape[0], h.shape[1] - 2
+    cnt = h[:, 2:]
+    off = torch.zeros(e_loc + 1, dtype=torch.int64)
+    off[1:] = torch.cumsum(cnt.sum(0), 0)
+    pos_of = torch.full((world * cap,), -1, dtype=torch.int32)
+    for s in range(world):
+        j = 0
+        for e in range(e_loc):
+            base = int(off[e]) + int(cnt[:s, e].sum())
+            for i in range(int(cnt[s, e])):
+                if j < min(int(h[s, 0]), cap):
+                    pos_of[s * cap + j] = base + i
+                j += 1
+    return off.to(torch.int32), pos_of, int(off[-1])
+
+
+def moe_layer_ep_fixed(x, expert_ids, expert_w, num_experts: int, cap: int, sort_fn, expert_fn, combine_fn, group=None):
+    """The fixed-capacity protocol in plain torch (rows travel unquantised): the CPU statement of what
+    ``ExpertParallelMoE`` does with kernels.  ``expert_fn(rows_sorted, expert_offsets_loc)`` maps expert-sorted rows to
+    outputs.  Returns ``(out, overflow)``; on overflow ``out`` is incomplete and the caller must redo the step."""
+    world = dist.get_world_size(group)
+    T, k = expert_ids.shape
+    H = x.shape[1]
+    sorted_pairs, inv_pairs, offsets = sort_fn(expert_ids, num_experts)
+    hdr, slot, ret_row, overflow = plan_reference(offsets, sorted_pairs, world, cap)
+    e_loc = num_experts // world
+    width = max(H, 2 + e_loc)
+    send = torch.zeros(world, 1 + cap, width, dtype=torch.float32)
+    send[:, 0, :2 + e_loc] = hdr.float()
+    ok = slot >= 0
+    rows = x.float()[torch.div(sorted_pairs[ok].long(), k, rounding_mode="floor")]
+    send.view(-1, width)[slot[ok].long(), :H] = rows
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv.view(-1), send.view(-1), group=group)
+    off_loc, pos_of, R = unpack_reference(recv[:, 0, :2 + e_loc].to(torch.int32), cap)
+    got = pos_of >= 0
+    rows_sorted = torch.zeros(R, H)
+    body = recv[:, 1:, :H].reshape(world * cap, H)
+    rows_sorted[pos_of[got].long()] = body[got]
+    y = expert_fn(rows_sorted, off_loc)
+    ret_send = torch.zeros(world * cap, y.shape[1])
+    ret_send[got] = y[pos_of[got].long()]
+    ret_recv = torch.empty_like(ret_send)
+    dist.all_to_all_single(ret_recv.view(-1), ret_send.view(-1), group=group)
+    flag = torch.tensor([1.0 if overflow else 0.0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)     # every rank learns of an overflow anywhere
+    return combine_fn(ret_recv, ret_row, expert_w, T, k), bool(flag.item() > 0)
+
+
+class ExpertParallelMoE:
+    """Expert-parallel MoE layer on CUDA with fixed-capacity exchange buffers: no device -> host round trip, no torch
+    indexing kernels; rows travel quantised (68 bytes per 128 values).  Buffers are allocated once for
+    ``tokens_per_rank`` tokens and reused by every call (intermediate results of a call are overwritten by the next).
+
+    ``out = layer(x, expert_ids, expert_w)``; afterwards ``layer.overflowed()`` tells whether any rank ran out of
+    capacity in a call since the last check (it synchronises and reduces the flag over the ranks), in which case the
+    affected outputs are incomplete and the step must be redone through ``moe_layer_ep``.  With ``check_each_call=True``
+    the layer does that itself, at the price of one host synchronisation per call."""
+
+    def __init__(self, weights, num_experts: int, tokens_per_rank: int, top_k: int, hidden: int, group=None,
+                 capacity_factor: float = 1.0, check_each_call: bool = False, world: int | None = None,
+                 rank: int | None = None, cap: int | None = None):
+        from . import moe as _moe
+        from ._cabi import lib
+
+        self._moe, self._lib = _moe, lib
+        self.group = group
+        # `world` / `rank` are only given by tests that play several ranks in one process (and exchange the blocks
+        # themselves); normally they come from the process group
+        self.world = dist.get_world_size(group) if world is None else world
+        self.rank = dist.get_rank(group) if rank is None else rank
+        self.weights = weights
+        self.E, self.k, self.H, self.T = num_experts, top_k, hidden, tokens_per_rank
+        assert num_experts % self.world == 0 and hidden % 128 == 0
+        self.e_loc = num_experts // self.world
+        self.G = hidden // 128
+        self.row_bytes = self.G * 68
+        assert self.row_bytes >= 4 * (2 + self.e_loc), "hidden size too small for the header of this many experts"
+        self.P = tokens_per_rank * top_k
+        self.cap = ep_capacity(self.P, self.world, capacity_factor) if cap is None else cap
+        self.check_each_call = check_each_call
+        dev = weights.gate_up_packed.device
+        self.dev = dev
+        W, cap, G, H, I = self.world, self.cap, self.G, hidden, weights.inter
+        R = W * cap
+        self.r_max = R
+        u8, i32, f32, bf16 = torch.uint8, torch.int32, torch.float32, torch.bfloat16
+        self.send = torch.zeros(W * (1 + cap) * self.row_bytes, dtype=u8, device=dev)
+        self.recv = torch.zeros_like(self.send)
+        self.slot = torch.empty(self.P, dtype=i32, device=dev)
+        self.ret_row = torch.empty(self.P, dtype=i32, device=dev)
+        self.overflow = torch.zeros(1, dtype=i32, device=dev)
+        self.meta = torch.empty(int(lib.i4tc_moe_ep_meta_ints(W, self.e_loc)), dtype=i32, device=dev)
+        self.rows_dev = torch.zeros(1, dtype=i32, device=dev)
+        self.pos_of = torch.empty(R, dtype=i32, device=dev)
+        self.ap = torch.zeros(G, R, 64, dtype=u8, device=dev)
+        self.asc = torch.zeros(G, R, dtype=f32, device=dev)
+        self.off_loc = torch.zeros(self.e_loc + 1, dtype=i32, device=dev)
+        self.h = torch.zeros(R, 2 * I, dtype=bf16, device=dev)
+        self.hp = torch.zeros(I // 128, R, 64, dtype=u8, device=dev)
+        self.hs = torch.zeros(I // 128, R, dtype=f32, device=dev)
+        self.y = torch.zeros(R, H, dtype=bf16, device=dev)
+        self.ret_send = torch.zeros(R, H, dtype=bf16, device=dev)
+        self.ret_recv = torch.zeros(R, H, dtype=bf16, device=dev)
+        self.sorted_pairs = torch.empty(self.P, dtype=i32, device=dev)
+        self.inv_pairs = torch.empty(self.P, dtype=i32, device=dev)
+        self.offsets = torch.empty(num_experts + 1, dtype=i32, device=dev)
+        self.sort_scratch = torch.empty(max(int(lib.i4tc_moe_sort_scratch_bytes(self.P, num_experts)), 4), dtype=u8, device=dev)
+
+    # -- stages -------------------------------------------------------------------------------------------------
+    def _prepare(self, x, expert_ids):
+        from ._cabi import check
+        lib, d, st = self._lib, self.dev.index, torch.cuda.current_stream(self.dev).cuda_stream
+        ids = expert_ids.contiguous().view(-1)
+        assert ids.numel() == self.P and x.shape == (self.T, self.H) and x.dtype == torch.bfloat16 and x.is_contiguous()
+        check(lib.i4tc_moe_sort(ids.data_ptr(), self.P, self.E, self.sorted_pairs.data_ptr(), self.inv_pairs.data_ptr(),
+                                self.offsets.data_ptr(), self.sort_scratch.data_ptr(), self.sort_scratch.numel(), d, st),
+              "moe_sort")
+        check(lib.i4tc_moe_ep_plan(self.offsets.data_ptr(), self.sorted_pairs.data_ptr(), self.P, self.E, self.world,
+                                   self.cap, self.row_bytes, self.send.data_ptr(), self.slot.data_ptr(),
+                                   self.ret_row.data_ptr(), self.overflow.data_ptr(), d, st), "moe_ep_plan")
+        check(lib.i4tc_moe_ep_dispatch_quant(x.data_ptr(), self.T, self.H, x.stride(0), self.sorted_pairs.data_ptr(),
+                                             self.P, self.k, self.slot.data_ptr(), self.send.data_ptr(), self.row_bytes,
+                                             d, st), "moe_ep_dispatch_quant")
+
+    def _unpack(self):
+        from ._cabi import check
+        lib, d, st = self._lib, self.dev.index, torch.cuda.current_stream(self.dev).cuda_stream
+        check(lib.i4tc_moe_ep_unpack(self.recv.data_ptr(), self.world, self.e_loc, self.cap, self.row_bytes, self.G,
+                                     self.ap.data_ptr(), self.asc.data_ptr(), self.off_loc.data_ptr(),
+                                     self.pos_of.data_ptr(), self.meta.data_ptr(), self.rows_dev.data_ptr(), d, st),
+              "moe_ep_unpack")
+
+    def _experts(self):
+        from ._cabi import check
+        lib, d, st = self._lib, self.dev.index, torch.cuda.current_stream(self.dev).cuda_stream
+        w, m = self.weights, self._moe
+        m.moe_w4a4_grouped_gemm(self.ap, self.asc, w.gate_up_packed, w.gate_up_scale, self.off_loc, self.h, 2 * w.inter,
+                                self.G, self.e_loc)
+        check(lib.i4tc_moe_silu_mul_quant_rows(self.h.data_ptr(), self.r_max, self.rows_dev.data_ptr(), w.inter,
+                                               self.hp.data_ptr(), self.hs.data_ptr(), d, st), "moe_silu_mul_quant_rows")
+        m.moe_w4a4_grouped_gemm(self.hp, self.hs, w.down_packed, w.down_scale, self.off_loc, self.y, self.H,
+                                w.inter // 128, self.e_loc)
+
+    def _pack_return(self):
+        from ._cabi import check
+        lib, d, st = self._lib, self.dev.index, torch.cuda.current_stream(self.dev).cuda_stream
+        check(lib.i4tc_moe_ep_pack_return(self.y.data_ptr(), self.pos_of.data_ptr(), self.r_max, self.H,
+                                          self.ret_send.data_ptr(), d, st), "moe_ep_pack_return")
+
+    def _stages(self, x, expert_ids, expert_w):
+        yield "sort_plan_quantise", lambda: self._prepare(x, expert_ids)
+        yield "dispatch_all_to_all", lambda: dist.all_to_all_single(self.recv, self.send, group=self.group)
+        yield "unpack", self._unpack
+        yield "experts", self._experts
+        yield "pack_return", self._pack_return
+        yield "combine_all_to_all", lambda: dist.all_to_all_single(self.ret_recv.view(-1), self.ret_send.view(-1), group=self.group)
+        yield "combine", lambda: self._moe.moe_combine(self.ret_recv, self.ret_row, expert_w.contiguous(), self.T, self.k)
+
+    def __call__(self, x: torch.Tensor, expert_ids: torch.Tensor, expert_w: torch.Tensor) -> torch.Tensor:
+        out = None
+        for _, fn in self._stages(x, expert_ids, expert_w):
+            out = fn()
+        if self.check_each_call and self.overflowed():
+            out = moe_layer_ep(x, expert_ids, expert_w, self.weights, self.E, group=self.group)
+        return out
+
+    def overflowed(self) -> bool:
+        """True if any rank exceeded its capacity in a call since the last check (collective: every rank must call it)."""
+        flag = self.overflow.clone()
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        hit = bool(flag.item() != 0)
+        self.overflow.zero_()
+        return hit
+
+    def stage_times_us(self, x, expert_ids, expert_w, reps: int = 10) -> dict:
+        """Mean device time of each stage (CUDA events; a stage's wait for the slowest rank is part of its exchange)."""
+        acc = {}
+        for it in range(reps + 2):
+            evs, names = [torch.cuda.Event(enable_timing=True)], []
+            evs[0].record()
+            for name, fn in self._stages(x, expert_ids, expert_w):
+                fn()
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                evs.append(e)
+                names.append(name)
+            torch.cuda.synchronize()
+            if it >= 2:
+                for i, n in enumerate(names):
+                    acc[n] = acc.get(n, 0.0) + evs[i].elapsed_time(evs[i + 1]) * 1e3 / reps
+        return {n: round(v, 1) for n, v in acc.items()}
+
+    def close(self) -> None:
+        for n in ("send", "recv", "ap", "asc", "h", "hp", "hs", "y", "ret_send", "ret_recv"):
+            setattr(self, n, None)

@@ -254,6 +254,40 @@ int i4tc_rmsnorm_quant_grouped(const void* x, int64_t rows, int64_t K, int64_t l
 int i4tc_moe_silu_mul_quant(const void* h, int64_t P, int64_t I, uint8_t* packed, float* scale,
                             int device, void* stream);
 
+/* ---- expert parallelism with fixed-capacity exchange buffers (no counterpart in the reference) ----
+ *
+ * One layer on a rank: i4tc_moe_sort (by global expert id) -> i4tc_moe_ep_plan -> i4tc_moe_ep_dispatch_quant ->
+ * all-to-all of the send buffer (equal blocks, so no split sizes ever leave the device) -> i4tc_moe_ep_unpack ->
+ * i4tc_moe_grouped_gemm / i4tc_moe_silu_mul_quant_rows / i4tc_moe_grouped_gemm -> i4tc_moe_ep_pack_return ->
+ * all-to-all back -> i4tc_moe_combine with ret_row as the row index.
+ *
+ * Buffers.  send / recv: `world` blocks of (1 + cap) rows of row_bytes = (H / 128) * 68 bytes: a header row, then up
+ * to cap token rows (64 bytes of codes and one fp32 scale per group of 128), in the source's sorted order.
+ * slot [num_pairs]: buffer row of each sorted position (-1: beyond the capacity).  ret_row [num_pairs]: for every
+ * (token, slot) pair the row of the returned [world * cap, H] buffer that holds its expert output (-1: none).
+ * overflow: device word, bit 0 set when a destination would have received more than cap rows -- the layer's result
+ * is then incomplete and the caller repeats the step with exact split sizes; nothing is ever read or written out of
+ * range.  meta: int32 scratch of i4tc_moe_ep_meta_ints(world, e_loc) entries.  rows_dev: device int32, rows received. */
+int i4tc_moe_ep_plan(const int32_t* expert_offsets, const int32_t* sorted_pairs, int64_t num_pairs,
+                     int64_t num_experts, int64_t world, int64_t cap, int64_t row_bytes, void* send_buf,
+                     int32_t* slot, int32_t* ret_row, unsigned int* overflow, int device, void* stream);
+int i4tc_moe_ep_dispatch_quant(const void* x, int64_t num_tokens, int64_t K, int64_t ldx,
+                               const int32_t* sorted_pairs, int64_t num_pairs, int64_t top_k,
+                               const int32_t* slot, void* send_buf, int64_t row_bytes, int device, void* stream);
+int64_t i4tc_moe_ep_meta_ints(int64_t world, int64_t e_loc);
+/* a_packed [G, world * cap, 64], a_scale [G, world * cap]: received rows in expert-sorted order (rows past *rows_dev
+ * are not written); expert_offsets_loc [e_loc + 1]; pos_of [world * cap]: sorted position of received row (s, j). */
+int i4tc_moe_ep_unpack(const void* recv_buf, int64_t world, int64_t e_loc, int64_t cap, int64_t row_bytes,
+                       int64_t num_groups, uint8_t* a_packed, float* a_scale, int32_t* expert_offsets_loc,
+                       int32_t* pos_of, int32_t* meta, int32_t* rows_dev, int device, void* stream);
+/* i4tc_moe_silu_mul_quant over the first *rows_dev of max_rows rows (the count stays on the device). */
+int i4tc_moe_silu_mul_quant_rows(const void* h, int64_t max_rows, const int32_t* rows_dev, int64_t I,
+                                 uint8_t* packed, float* scale, int device, void* stream);
+/* ret_send[row, :] = y[pos_of[row], :] for the `rows` = world * cap buffer rows (bf16 [.., H]); rows without a
+ * received token (pos_of < 0) are left as they are. */
+int i4tc_moe_ep_pack_return(const void* y, const int32_t* pos_of, int64_t rows, int64_t H, void* ret_send,
+                            int device, void* stream);
+
 /* out[t, :] = bf16( sum_j w[t, j] * y[inv_pairs[t*top_k + j], :] ), j ascending, fp32 sum.
  * y bf16 [P, H]; inv_pairs[pair] = sorted position of that pair. */
 int i4tc_moe_combine(const void* y, const int32_t* inv_pairs, const float* w, int64_t T,

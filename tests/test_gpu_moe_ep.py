@@ -17,6 +17,89 @@ def _free_port():
     return p
 
 
+def _setup_logical_ranks(world, cap=None, T=256, H=512, I=256, E=16, k=4, seed=0):
+    from fp8_inference_toolkit_b200 import moe, moe_ep, synthetic
+
+    x, logits = synthetic.moe_inputs(T, H, E, k, seed=seed, device="cuda")
+    gu, dn = synthetic.moe_weights(E, H, I, seed=seed + 1, device="cuda")
+    ids, w = moe.moe_route(logits, k)
+    ids[5, 1] = -1   # a padded pair
+    full = moe.MoEWeights.quantize(gu, dn)
+    e_loc, t_loc = E // world, T // world
+    layers = []
+    for r in range(world):
+        sl = slice(r * e_loc, (r + 1) * e_loc)
+        mine = moe.MoEWeights(full.gate_up_packed[sl].contiguous(), full.gate_up_scale[sl].contiguous(),
+                              full.down_packed[sl].contiguous(), full.down_scale[sl].contiguous(), e_loc, H, I)
+        layers.append(moe_ep.ExpertParallelMoE(mine, E, t_loc, k, H, world=world, rank=r, cap=cap))
+    return x, ids, w, full, layers, t_loc
+
+
+def _swap(layers, send_name, recv_name, rows_per_block):
+    """What the all-to-all does, among ranks played by one process: block d of rank s's send buffer becomes block s of
+    rank d's receive buffer."""
+    world = len(layers)
+    for s, ls in enumerate(layers):
+        src = getattr(ls, send_name).view(world, -1)
+        for d, ld in enumerate(layers):
+            getattr(ld, recv_name).view(world, -1)[s].copy_(src[d])
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_fixed_capacity_layer_kernels_one_gpu(world):
+    """The expert-parallel layer's kernels with the ranks played one after the other on a single GPU (the exchange is
+    a copy): plan and unpack agree with their plain-torch statements, and the combined output of all ranks is the
+    single-GPU layer's, bit for bit."""
+    from fp8_inference_toolkit_b200 import moe, moe_ep, ops
+
+    x, ids, w, full, layers, t_loc = _setup_logical_ranks(world)
+    for r, l in enumerate(layers):
+        ts = slice(r * t_loc, (r + 1) * t_loc)
+        l._prepare(x[ts].contiguous(), ids[ts].contiguous())
+        hdr, slot, ret_row, overflow = moe_ep.plan_reference(l.offsets, l.sorted_pairs, world, l.cap)
+        assert not overflow and int(l.overflow.item()) == 0
+        assert torch.equal(l.slot.cpu(), slot) and torch.equal(l.ret_row.cpu(), ret_row)
+        got_hdr = l.send.view(world, 1 + l.cap, l.row_bytes)[:, 0, :4 * (2 + l.e_loc)].contiguous().view(torch.int32)
+        assert torch.equal(got_hdr.cpu(), hdr)
+    _swap(layers, "send", "recv", None)
+    for l in layers:
+        l._unpack()
+        hdrs = l.recv.view(world, 1 + l.cap, l.row_bytes)[:, 0, :4 * (2 + l.e_loc)].contiguous().view(torch.int32)
+        off_loc, pos_of, R = moe_ep.unpack_reference(hdrs.cpu(), l.cap)
+        assert torch.equal(l.off_loc.cpu(), off_loc) and torch.equal(l.pos_of.cpu(), pos_of) and int(l.rows_dev.item()) == R
+        l._experts()
+        l._pack_return()
+    _swap(layers, "ret_send", "ret_recv", None)
+    ops.check_status()
+    out = torch.cat([moe.moe_combine(l.ret_recv, l.ret_row, w[r * t_loc:(r + 1) * t_loc].contiguous(), t_loc, l.k)
+                     for r, l in enumerate(layers)])
+    ref = moe.moe_layer(x, ids, w, full)
+    assert torch.equal(out, ref)
+
+
+def test_fixed_capacity_overflow_flag_one_gpu():
+    """A capacity that is too small: the flag is raised, every index stays in range (no fault, status clean), and the
+    rows that did fit are still placed consistently."""
+    from fp8_inference_toolkit_b200 import moe_ep, ops
+
+    x, ids, w, full, layers, t_loc = _setup_logical_ranks(2, cap=64)
+    for r, l in enumerate(layers):
+        ts = slice(r * t_loc, (r + 1) * t_loc)
+        l._prepare(x[ts].contiguous(), ids[ts].contiguous())
+        hdr, slot, ret_row, overflow = moe_ep.plan_reference(l.offsets, l.sorted_pairs, 2, l.cap)
+        assert overflow and int(l.overflow.item()) == 1
+        assert torch.equal(l.slot.cpu(), slot) and torch.equal(l.ret_row.cpu(), ret_row)
+    _swap(layers, "send", "recv", None)
+    for l in layers:
+        l._unpack()
+        hdrs = l.recv.view(2, 1 + l.cap, l.row_bytes)[:, 0, :4 * (2 + l.e_loc)].contiguous().view(torch.int32)
+        off_loc, pos_of, R = moe_ep.unpack_reference(hdrs.cpu(), l.cap)
+        assert torch.equal(l.pos_of.cpu(), pos_of) and int(l.rows_dev.item()) == R
+        l._experts()
+        l._pack_return()
+    ops.check_status()
+
+
 def _worker(rank, world, port):
     import torch.distributed as dist
 
@@ -42,6 +125,15 @@ def _worker(rank, world, port):
                                   quantized_dispatch=quantized)
         ops.check_status()
         assert torch.equal(out, ref[ts]), (quantized, (out.float() - ref[ts].float()).abs().max().item())
+    # the fixed-capacity layer (no host synchronisation): the same bits again, twice in a row (buffers are reused)
+    layer = moe_ep.ExpertParallelMoE(mine, E, t_loc, k, H)
+    for _ in range(2):
+        out = layer(x[ts].contiguous(), ids[ts].contiguous(), w[ts].contiguous())
+        ops.check_status()
+        assert torch.equal(out, ref[ts])
+    assert not layer.overflowed()
+    tiny = moe_ep.ExpertParallelMoE(mine, E, t_loc, k, H, cap=64, check_each_call=True)   # overflows: redone exactly
+    assert torch.equal(tiny(x[ts].contiguous(), ids[ts].contiguous(), w[ts].contiguous()), ref[ts])
     dist.barrier()
     dist.destroy_process_group()
 
