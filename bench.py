@@ -517,7 +517,7 @@ def bench_moe(args, world, rank, dev, peaks, weak: bool = False) -> dict:
         return moe.MoEWeights.quantize(gu, dn)
 
     mw = rank_weights(rank)
-    ep = moe_ep.ExpertParallelMoE(mw, E, t_loc, k, H) if world > 1 else None
+    ep = moe_ep.ExpertParallelMoE(mw, E, t_loc, k, H, transport=args.ep_transport) if world > 1 else None
 
     def layer():
         if world == 1:
@@ -556,6 +556,10 @@ def bench_moe(args, world, rank, dev, peaks, weak: bool = False) -> dict:
                    "timed": "sort + dispatch + gather-quantise + gate/up GEMM + SwiGLU-quantise + down GEMM + combine"},
     }
     if world > 1:
+        res["transport"] = ep.transport + (" (rows stored straight into the destination rank's buffer over NVLink, device-side "
+                                           "flags)" if ep.transport == "peer" else " (two all_to_all_single of fixed-size blocks)")
+        if getattr(ep, "peer_error", None):
+            res["peer_transport_unavailable"] = ep.peer_error[:200]
         res["stages_us"] = ep.stage_times_us(x_l, ids_l, w_l)
         if ep.overflowed():
             res["note"] = "a dispatch buffer overflowed in this run and the step was redone with exact split sizes"
@@ -790,6 +794,8 @@ def main() -> None:
     ap.add_argument("--seq", type=int, default=512)
     ap.add_argument("--k", type=int, default=12288, help="row length for --workload quant")
     ap.add_argument("--no-sweep", action="store_true", help="skip the kernel-only M x shape sweep")
+    ap.add_argument("--ep-transport", default="auto", choices=["auto", "nccl", "peer"],
+                    help="exchange of the expert-parallel MoE layer: NCCL all-to-all of fixed-size blocks, or peer stores")
     ap.add_argument("--no-extras", action="store_true", help="skip the quantise+pack and prefill objects of the default line")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)

@@ -48,12 +48,14 @@ SIGNATURES = {
     "i4tc_moe_sort_noalloc_max_scratch_ints": (_l, []),
     "i4tc_moe_sort_noalloc": (_i, [_p, _l, _l, _p, _p, _p, _i, _p]),
     "i4tc_moe_sort_noalloc_prepare": (_i, [_i]),
-    "i4tc_moe_ep_plan": (_i, [_p, _p, _l, _l, _l, _l, _l, _p, _p, _p, _p, _i, _p]),
-    "i4tc_moe_ep_dispatch_quant": (_i, [_p, _l, _l, _l, _p, _l, _l, _p, _p, _l, _i, _p]),
+    "i4tc_moe_ep_plan": (_i, [_p, _p, _l, _l, _l, _l, _l, _p, _p, _p, _p, _p, _l, _i, _p]),
+    "i4tc_moe_ep_dispatch_quant": (_i, [_p, _l, _l, _l, _p, _l, _l, _p, _p, _l, _p, _l, _l, _i, _p]),
+    "i4tc_peer_signal": (_i, [_p, _l, C.c_uint32, _i, _p]),
+    "i4tc_peer_wait": (_i, [_p, _l, C.c_uint32, _i, _p]),
     "i4tc_moe_ep_meta_ints": (_l, [_l, _l]),
     "i4tc_moe_ep_unpack": (_i, [_p, _l, _l, _l, _l, _l, _p, _p, _p, _p, _p, _p, _i, _p]),
     "i4tc_moe_silu_mul_quant_rows": (_i, [_p, _l, _p, _l, _p, _p, _i, _p]),
-    "i4tc_moe_ep_pack_return": (_i, [_p, _p, _l, _l, _p, _i, _p]),
+    "i4tc_moe_ep_pack_return": (_i, [_p, _p, _l, _l, _p, _p, _p, _l, _l, _l, _i, _p]),
     "i4tc_moe_gather_quant": (_i, [_p, _i, _l, _l, _l, _p, _l, _l, _p, _p, _i, _p]),
     "i4tc_moe_grouped_gemm": (_i, [_p, _p, _p, _p, _p, _p, _l, _l, _l, _l, _i, _p]),
     "i4tc_moe_silu_mul_quant": (_i, [_p, _l, _l, _p, _p, _i, _p]),

@@ -175,13 +175,18 @@ __global__ void __launch_bounds__(256) moe_ep_plan_kernel(const int32_t* __restr
                                                          const int32_t* __restrict__ sorted_pairs, int P, int world,
                                                          int e_loc, int cap, long long row_bytes,
                                                          uint8_t* __restrict__ send_buf, int32_t* __restrict__ slot,
-                                                         int32_t* __restrict__ ret_row, unsigned int* overflow) {
+                                                         int32_t* __restrict__ ret_row, unsigned int* overflow,
+                                                         const unsigned long long* __restrict__ peer_bases, int my_rank) {
   if (blockIdx.x == 0) {
-    // headers: thread (d, e) pairs in a strided loop
+    // headers: thread (d, e) pairs in a strided loop; with peer destinations the header of destination d is written
+    // straight into block `my_rank` of d's receive buffer
     for (int i = threadIdx.x; i < world * (e_loc + 2); i += blockDim.x) {
       const int d = i / (e_loc + 2), f = i - d * (e_loc + 2);
       const int start = expert_offsets[d * e_loc];
-      int32_t* hdr = reinterpret_cast<int32_t*>(send_buf + (long long)d * (1 + cap) * row_bytes);
+      int32_t* hdr = (peer_bases != nullptr)
+                         ? reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(peer_bases[d]) +
+                                                      (long long)my_rank * (1 + cap) * row_bytes)
+                         : reinterpret_cast<int32_t*>(send_buf + (long long)d * (1 + cap) * row_bytes);
       if (f == 0) {
         const int n = expert_offsets[(d + 1) * e_loc] - start;
         hdr[0] = min(n, cap);
@@ -213,7 +218,8 @@ __global__ void __launch_bounds__(256) moe_ep_plan_kernel(const int32_t* __restr
 
 // Receiver, step 1 (one block): read the `world` headers, build the local expert offsets and, per (source, expert),
 // where that run of rows starts in expert-sorted order and where it starts inside the source's block.
-// meta layout (int32): tot[world] | base[world][e_loc] | cum[world][e_loc + 1].
+// meta layout (int32): tot[world] | base[world][e_loc] | cum[world][e_loc + 1] | start[world] (sorted position, at the
+// source, of the first row of its block).
 __global__ void __launch_bounds__(256) moe_ep_offsets_kernel(const uint8_t* __restrict__ recv_buf, int world, int e_loc,
                                                             int cap, long long row_bytes,
                                                             int32_t* __restrict__ expert_offsets_loc,
@@ -252,6 +258,7 @@ __global__ void __launch_bounds__(256) moe_ep_offsets_kernel(const uint8_t* __re
     }
     cum[e * (e_loc + 1) + e_loc] = run;
     tot[e] = min(min(hdr[0], run), cap);
+    cum[world * (e_loc + 1) + e] = hdr[1];   // start[e]
   }
 }
 
@@ -289,10 +296,13 @@ __global__ void __launch_bounds__(256) moe_ep_scatter_kernel(const uint8_t* __re
   if (lane == 0) pos_of[row] = (int32_t)pos;
 }
 
-// Expert outputs back into the order each source sent its rows in: ret_send[s][j] = y[pos_of[s][j]].
+// Expert outputs back into the order each source sent its rows in: ret_send[s][j] = y[pos_of[s][j]].  With peer
+// destinations row (s, j) goes straight to row start[s] + j of source s's return buffer (its own sorted order).
 __global__ void __launch_bounds__(256) moe_ep_pack_return_kernel(const __nv_bfloat16* __restrict__ y,
                                                                 const int32_t* __restrict__ pos_of, long long rows,
-                                                                int H, __nv_bfloat16* __restrict__ ret_send) {
+                                                                int H, __nv_bfloat16* __restrict__ ret_send,
+                                                                const unsigned long long* __restrict__ peer_bases,
+                                                                const int32_t* __restrict__ start, int cap) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * 8 + warp;
   if (row >= rows) return;
@@ -300,7 +310,45 @@ __global__ void __launch_bounds__(256) moe_ep_pack_return_kernel(const __nv_bflo
   if (pos < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(y + (long long)pos * H);
   uint4* dst = reinterpret_cast<uint4*>(ret_send + row * H);
+  if (peer_bases != nullptr) {
+    const int s = (int)(row / cap), j = (int)(row - (long long)s * cap);
+    dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_bases[s]) + ((long long)start[s] + j) * H);
+  }
   for (int c = lane; c < H / 8; c += 32) dst[c] = __ldg(src + c);
+}
+
+// Cross-GPU completion flags.  A rank that has finished writing into its peers' buffers (all earlier work of its
+// stream) stores a growing epoch number into its slot of every peer's flag array; a rank that is about to read its
+// own buffer waits until every slot has reached the epoch.  The wait is bounded: after two seconds it sets bit 1 of
+// the status word and lets the stream go on.
+__global__ void peer_signal_kernel(const unsigned long long* __restrict__ flag_addrs, int world, unsigned int epoch) {
+  __threadfence_system();
+  if ((int)threadIdx.x < world) {
+    volatile unsigned int* f = reinterpret_cast<volatile unsigned int*>(flag_addrs[threadIdx.x]);
+    *f = epoch;
+  }
+  __threadfence_system();
+}
+
+__global__ void peer_wait_kernel(const unsigned int* __restrict__ flags, int world, unsigned int epoch,
+                                 unsigned int* status) {
+  if ((int)threadIdx.x < world) {
+    const volatile unsigned int* f = flags + threadIdx.x;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    unsigned int spins = 0;
+    while ((int)(*f - epoch) < 0) {
+      if ((++spins & 255u) == 0) {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 2000000000ull) {
+          atomicOr(status, 2u);
+          break;
+        }
+      }
+    }
+  }
+  __threadfence_system();
 }
 
 int moe_sort_launch(const int32_t* ids, int64_t P, int64_t E, int32_t* sorted_pairs, int32_t* inv_pairs,
@@ -424,15 +472,17 @@ extern "C" int i4tc_moe_sort_noalloc(const int32_t* expert_ids, int64_t num_pair
 
 extern "C" int i4tc_moe_ep_plan(const int32_t* expert_offsets, const int32_t* sorted_pairs, int64_t num_pairs,
                                 int64_t num_experts, int64_t world, int64_t cap, int64_t row_bytes, void* send_buf,
-                                int32_t* slot, int32_t* ret_row, unsigned int* overflow, int device, void* stream) {
+                                int32_t* slot, int32_t* ret_row, unsigned int* overflow, const uint64_t* peer_bases,
+                                int64_t my_rank, int device, void* stream) {
   I4TC_REQUIRE(world > 0 && num_experts > 0 && num_experts % world == 0 && num_experts <= kMaxExperts, I4TC_EINVAL,
                "experts must divide evenly across ranks (at most %d experts)", kMaxExperts);
   I4TC_REQUIRE(cap > 0 && cap < (1 << 24) && num_pairs >= 0 && num_pairs < (1ll << 31), I4TC_EINVAL, "bad capacity or size");
   const int64_t e_loc = num_experts / world;
   I4TC_REQUIRE(row_bytes % 16 == 0 && row_bytes >= 4 * (2 + e_loc), I4TC_EINVAL,
                "a buffer row must be a multiple of 16 bytes and hold the %lld header integers", (long long)(2 + e_loc));
-  I4TC_REQUIRE(expert_offsets && send_buf && slot && ret_row && overflow && (sorted_pairs || num_pairs == 0), I4TC_EINVAL,
-               "null pointer");
+  I4TC_REQUIRE(expert_offsets && (send_buf || peer_bases) && slot && ret_row && overflow &&
+                   (sorted_pairs || num_pairs == 0), I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(my_rank >= 0 && my_rank < world, I4TC_EINVAL, "rank out of range");
   I4TC_REQUIRE(aligned_to(send_buf, 16), I4TC_EALIGN, "send buffer must be 16-byte aligned");
   DeviceGuard guard(device);
   I4TC_CUDA(guard.err);
@@ -444,12 +494,15 @@ extern "C" int i4tc_moe_ep_plan(const int32_t* expert_offsets, const int32_t* so
   if (blocks > 1024) blocks = 1024;
   moe_ep_plan_kernel<<<(unsigned)blocks, 256, 0, st>>>(expert_offsets, sorted_pairs, (int)num_pairs, (int)world, (int)e_loc,
                                                        (int)cap, row_bytes, static_cast<uint8_t*>(send_buf), slot, ret_row,
-                                                       overflow);
+                                                       overflow, reinterpret_cast<const unsigned long long*>(peer_bases),
+                                                       (int)my_rank);
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
 }
 
-extern "C" int64_t i4tc_moe_ep_meta_ints(int64_t world, int64_t e_loc) { return world + world * e_loc + world * (e_loc + 1); }
+extern "C" int64_t i4tc_moe_ep_meta_ints(int64_t world, int64_t e_loc) {
+  return world + world * e_loc + world * (e_loc + 1) + world;
+}
 
 extern "C" int i4tc_moe_ep_unpack(const void* recv_buf, int64_t world, int64_t e_loc, int64_t cap, int64_t row_bytes,
                                   int64_t num_groups, uint8_t* a_packed, float* a_scale, int32_t* expert_offsets_loc,
@@ -471,15 +524,41 @@ extern "C" int i4tc_moe_ep_unpack(const void* recv_buf, int64_t world, int64_t e
 }
 
 extern "C" int i4tc_moe_ep_pack_return(const void* y, const int32_t* pos_of, int64_t rows, int64_t H, void* ret_send,
-                                       int device, void* stream) {
+                                       const uint64_t* peer_bases, const int32_t* meta, int64_t world, int64_t e_loc,
+                                       int64_t cap, int device, void* stream) {
   I4TC_REQUIRE(rows >= 0 && H > 0 && H % 8 == 0, I4TC_EINVAL, "H must be a positive multiple of 8");
   if (rows == 0) return I4TC_OK;
-  I4TC_REQUIRE(y && pos_of && ret_send, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(y && pos_of && (ret_send || peer_bases), I4TC_EINVAL, "null pointer");
   I4TC_REQUIRE(aligned_to(y, 16) && aligned_to(ret_send, 16), I4TC_EALIGN, "buffers must be 16-byte aligned");
+  I4TC_REQUIRE(peer_bases == nullptr || (meta && world > 0 && e_loc > 0 && cap > 0 && rows == world * cap), I4TC_EINVAL,
+               "peer destinations need the unpack scratch and the block geometry");
   DeviceGuard guard(device);
   I4TC_CUDA(guard.err);
+  const int32_t* start = peer_bases ? meta + world + world * e_loc + world * (e_loc + 1) : nullptr;
   moe_ep_pack_return_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(y), pos_of, rows, (int)H, static_cast<__nv_bfloat16*>(ret_send));
+      static_cast<const __nv_bfloat16*>(y), pos_of, rows, (int)H, static_cast<__nv_bfloat16*>(ret_send),
+      reinterpret_cast<const unsigned long long*>(peer_bases), start, (int)(cap > 0 ? cap : 1));
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_peer_signal(const uint64_t* flag_addrs, int64_t world, uint32_t epoch, int device, void* stream) {
+  I4TC_REQUIRE(flag_addrs && world > 0 && world <= 256, I4TC_EINVAL, "bad arguments");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  peer_signal_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const unsigned long long*>(flag_addrs), (int)world, epoch);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_peer_wait(const uint32_t* flags, int64_t world, uint32_t epoch, int device, void* stream) {
+  I4TC_REQUIRE(flags && world > 0 && world <= 256, I4TC_EINVAL, "bad arguments");
+  const DeviceInfo* info;
+  if (int rc = device_info(device, &info)) return rc;
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  peer_wait_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(flags, (int)world, epoch, info->status);
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
 }

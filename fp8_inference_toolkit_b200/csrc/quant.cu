@@ -319,6 +319,13 @@ struct QuantOutMap {
   const int32_t* rows_dev;  // nullptr: all `rows`
   long long pk_gstride, pk_rstride;   // bytes between groups / rows of the packed output
   long long sc_gstride, sc_rstride;   // floats between groups / rows of the scale output
+  // Peer destinations (nullptr: one local buffer).  Mapped row m lies in block m / block_rows; that block's rows go
+  // to the buffer at dest_bases[block] (another GPU's memory, written with plain stores over NVLink), where this
+  // rank's block is number my_block: row my_block * block_rows + m % block_rows.  scale_offset = bytes from a row's
+  // codes to its scales.
+  const unsigned long long* dest_bases;
+  int block_rows, my_block;
+  long long scale_offset;
 };
 
 template <typename T, int LPG, int MODE, bool GIVEN, bool OUTMAP = false>
@@ -326,7 +333,7 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
     const T* __restrict__ x, int64_t rows, int K, int64_t ldx, const int32_t* __restrict__ row_index,
     int index_div, int64_t src_rows, const float* __restrict__ given_scale, uint8_t* __restrict__ packed,
     float* __restrict__ scale, int role, int segs_per_block, const T* __restrict__ aux, float eps,
-    QuantOutMap out = QuantOutMap()) {
+    QuantOutMap out = QuantOutMap{nullptr, nullptr, 0, 0, 0, 0, nullptr, 1, 0, 0}) {
   constexpr int GS = LPG * kQLane;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t r0 = (int64_t)blockIdx.x * kQRows;
@@ -394,8 +401,18 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
       // one lane per group writes the scale (the IEEE division absmax / 7 happens here, off the
       // per-element path); neighbouring rows fill the same 32-byte sector from other warps
       if (ok && (lane % LPG) == 0) {
-        if (OUTMAP) scale[(int64_t)g * out.sc_gstride + orow * out.sc_rstride] = scale_out(absmax, role);
-        else scale[(int64_t)g * rows + r] = scale_out(absmax, role);
+        if (OUTMAP) {
+          float* sdst = scale + (int64_t)g * out.sc_gstride + orow * out.sc_rstride;
+          if (out.dest_bases != nullptr) {
+            const int blk = (int)(orow / out.block_rows);
+            const int64_t prow = (int64_t)out.my_block * out.block_rows + (orow - (int64_t)blk * out.block_rows);
+            sdst = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(out.dest_bases[blk]) + prow * out.pk_rstride +
+                                            out.scale_offset) + (int64_t)g * out.sc_gstride;
+          }
+          *sdst = scale_out(absmax, role);
+        } else {
+          scale[(int64_t)g * rows + r] = scale_out(absmax, role);
+        }
       }
     }
     if (ok) {
@@ -407,6 +424,12 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
       w.w = pack8<T, GIVEN>(cur[3], q, zero);
       uint8_t* dst = OUTMAP ? packed + (int64_t)g * out.pk_gstride + orow * out.pk_rstride + (lane % LPG) * 16
                             : packed + ((int64_t)g * rows + r) * (GS / 2) + (lane % LPG) * 16;
+      if (OUTMAP && out.dest_bases != nullptr) {
+        const int blk = (int)(orow / out.block_rows);
+        const int64_t prow = (int64_t)out.my_block * out.block_rows + (orow - (int64_t)blk * out.block_rows);
+        dst = reinterpret_cast<uint8_t*>(out.dest_bases[blk]) + prow * out.pk_rstride + (int64_t)g * out.pk_gstride +
+              (lane % LPG) * 16;
+      }
       *reinterpret_cast<uint4*>(dst) = w;
     }
 #pragma unroll
@@ -716,15 +739,17 @@ extern "C" int i4tc_moe_gather_quant(const void* x, int dtype, int64_t num_token
 
 extern "C" int i4tc_moe_ep_dispatch_quant(const void* x, int64_t num_tokens, int64_t K, int64_t ldx,
                                           const int32_t* sorted_pairs, int64_t num_pairs, int64_t top_k,
-                                          const int32_t* slot, void* send_buf, int64_t row_bytes, int device,
+                                          const int32_t* slot, void* send_buf, int64_t row_bytes,
+                                          const uint64_t* peer_bases, int64_t cap, int64_t my_rank, int device,
                                           void* stream) {
   I4TC_REQUIRE(top_k > 0 && top_k < (1 << 20) && num_tokens >= 0 && num_pairs >= 0, I4TC_EINVAL, "bad sizes");
   I4TC_REQUIRE(K > 0 && K % 128 == 0 && row_bytes == (K / 128) * 68, I4TC_EINVAL,
                "a row is 64 bytes of codes and one fp32 scale per 128 values");
   if (num_pairs == 0) return I4TC_OK;
-  I4TC_REQUIRE(x && sorted_pairs && slot && send_buf, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(x && sorted_pairs && slot && (send_buf || peer_bases), I4TC_EINVAL, "null pointer");
   if (int rc = check_vec_input(x, I4TC_BF16, ldx, "moe_ep_dispatch_quant")) return rc;
   I4TC_REQUIRE(aligned_to(send_buf, 16), I4TC_EALIGN, "send buffer must be 16-byte aligned");
+  I4TC_REQUIRE(peer_bases == nullptr || (cap > 0 && my_rank >= 0), I4TC_EINVAL, "peer destinations need cap and the rank");
   DeviceGuard guard(device);
   I4TC_CUDA(guard.err);
   const int64_t G = K / 128;
@@ -735,6 +760,10 @@ extern "C" int i4tc_moe_ep_dispatch_quant(const void* x, int64_t num_tokens, int
   out.pk_rstride = row_bytes;
   out.sc_gstride = 1;
   out.sc_rstride = row_bytes / 4;
+  out.dest_bases = reinterpret_cast<const unsigned long long*>(peer_bases);
+  out.block_rows = (int)(1 + cap);
+  out.my_block = (int)my_rank;
+  out.scale_offset = G * 64;
   uint8_t* base = static_cast<uint8_t*>(send_buf);
   return launch_grouped_mapped<1>(static_cast<const __nv_bfloat16*>(x), num_pairs, K, ldx, sorted_pairs, (int)top_k,
                                   num_tokens, base, reinterpret_cast<float*>(base + G * 64), out,
@@ -757,6 +786,10 @@ extern "C" int i4tc_moe_silu_mul_quant_rows(const void* h, int64_t max_rows, con
   out.pk_rstride = 64;
   out.sc_gstride = max_rows;
   out.sc_rstride = 1;
+  out.dest_bases = nullptr;
+  out.block_rows = 1;
+  out.my_block = 0;
+  out.scale_offset = 0;
   return launch_grouped_mapped<2>(static_cast<const __nv_bfloat16*>(h), max_rows, I, 2 * I, nullptr, 1, 0, packed, scale,
                                   out, static_cast<cudaStream_t>(stream));
 }

@@ -247,6 +247,13 @@ class ExpertParallelMoE:
     indexing kernels; rows travel quantised (68 bytes per 128 values).  Buffers are allocated once for
     ``tokens_per_rank`` tokens and reused by every call (intermediate results of a call are overwritten by the next).
 
+    ``transport``: ``"nccl"`` exchanges the fixed-size blocks with two ``all_to_all_single`` calls; ``"peer"`` maps
+    every rank's receive and return buffers into the others' address space (``torch.distributed._symmetric_memory``)
+    and lets the quantise and return kernels store rows straight into the destination's buffer over NVLink, ordered by
+    device-side flags with bounded waits -- no collective at all, no capacity padding on the wire, and the return
+    rows land in the source's own sorted order; ``"auto"`` (default) takes ``"peer"`` when symmetric memory can be
+    set up for the group and ``"nccl"`` otherwise.
+
     ``out = layer(x, expert_ids, expert_w)``; afterwards ``layer.overflowed()`` tells whether any rank ran out of
     capacity in a call since the last check (it synchronises and reduces the flag over the ranks), in which case the
     affected outputs are incomplete and the step must be redone through ``moe_layer_ep``.  With ``check_each_call=True``
@@ -254,7 +261,7 @@ class ExpertParallelMoE:
 
     def __init__(self, weights, num_experts: int, tokens_per_rank: int, top_k: int, hidden: int, group=None,
                  capacity_factor: float = 1.0, check_each_call: bool = False, world: int | None = None,
-                 rank: int | None = None, cap: int | None = None):
+                 rank: int | None = None, cap: int | None = None, transport: str = "auto"):
         from . import moe as _moe
         from ._cabi import lib
 
@@ -282,6 +289,15 @@ class ExpertParallelMoE:
         u8, i32, f32, bf16 = torch.uint8, torch.int32, torch.float32, torch.bfloat16
         self.send = torch.zeros(W * (1 + cap) * self.row_bytes, dtype=u8, device=dev)
         self.recv = torch.zeros_like(self.send)
+        self.transport = "nccl"
+        self.epoch = 0
+        if transport in ("auto", "peer") and world is None and self.world > 1:
+            try:
+                self._setup_peer()
+            except Exception as exc:   # symmetric memory not available for this group: keep the collective transport
+                if transport == "peer":
+                    raise
+                self.peer_error = repr(exc)
         self.slot = torch.empty(self.P, dtype=i32, device=dev)
         self.ret_row = torch.empty(self.P, dtype=i32, device=dev)
         self.overflow = torch.zeros(1, dtype=i32, device=dev)
@@ -302,21 +318,69 @@ class ExpertParallelMoE:
         self.offsets = torch.empty(num_experts + 1, dtype=i32, device=dev)
         self.sort_scratch = torch.empty(max(int(lib.i4tc_moe_sort_scratch_bytes(self.P, num_experts)), 4), dtype=u8, device=dev)
 
+    def _setup_peer(self):
+        """One symmetric allocation per rank: [receive blocks | return rows in this rank's sorted order | flags]."""
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer mappings only
+        import torch.distributed._symmetric_memory as symm_mem
+
+        def up(n):
+            return (n + 255) // 256 * 256
+
+        W = self.world
+        recv_bytes = up(W * (1 + self.cap) * self.row_bytes)
+        ret_bytes = up(self.P * self.H * 2)
+        total = recv_bytes + ret_bytes + 256
+        buf = symm_mem.empty(total, dtype=torch.uint8, device=self.dev)
+        buf.zero_()
+        hdl = symm_mem.rendezvous(buf, dist.group.WORLD if self.group is None else self.group)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        i64 = torch.int64
+        self._symm, self._hdl = buf, hdl
+        self.recv = buf[:W * (1 + self.cap) * self.row_bytes]
+        self.ret_local = buf[recv_bytes:recv_bytes + self.P * self.H * 2].view(torch.bfloat16).view(self.P, self.H)
+        flags = buf[recv_bytes + ret_bytes:recv_bytes + ret_bytes + 256].view(torch.int32)
+        self.flags_dispatch, self.flags_return = flags[:W], flags[32:32 + W]
+        assert W <= 32
+        self.recv_bases = torch.tensor(ptrs, dtype=i64, device=self.dev)
+        self.ret_bases = torch.tensor([p + recv_bytes for p in ptrs], dtype=i64, device=self.dev)
+        fbase = recv_bytes + ret_bytes
+        self.flag_addrs_dispatch = torch.tensor([p + fbase + 4 * self.rank for p in ptrs], dtype=i64, device=self.dev)
+        self.flag_addrs_return = torch.tensor([p + fbase + 128 + 4 * self.rank for p in ptrs], dtype=i64, device=self.dev)
+        torch.cuda.synchronize(self.dev)
+        dist.barrier(group=self.group)    # every rank's flags are zero before anyone signals
+        self.transport = "peer"
+        self.send = None
+
     # -- stages -------------------------------------------------------------------------------------------------
     def _prepare(self, x, expert_ids):
         from ._cabi import check
         lib, d, st = self._lib, self.dev.index, torch.cuda.current_stream(self.dev).cuda_stream
         ids = expert_ids.contiguous().view(-1)
         assert ids.numel() == self.P and x.shape == (self.T, self.H) and x.dtype == torch.bfloat16 and x.is_contiguous()
+        peer = self.transport == "peer"
+        bases = self.recv_bases.data_ptr() if peer else None
+        send = None if peer else self.send.data_ptr()
         check(lib.i4tc_moe_sort(ids.data_ptr(), self.P, self.E, self.sorted_pairs.data_ptr(), self.inv_pairs.data_ptr(),
                                 self.offsets.data_ptr(), self.sort_scratch.data_ptr(), self.sort_scratch.numel(), d, st),
               "moe_sort")
         check(lib.i4tc_moe_ep_plan(self.offsets.data_ptr(), self.sorted_pairs.data_ptr(), self.P, self.E, self.world,
-                                   self.cap, self.row_bytes, self.send.data_ptr(), self.slot.data_ptr(),
-                                   self.ret_row.data_ptr(), self.overflow.data_ptr(), d, st), "moe_ep_plan")
+                                   self.cap, self.row_bytes, send, self.slot.data_ptr(), self.ret_row.data_ptr(),
+                                   self.overflow.data_ptr(), bases, self.rank, d, st), "moe_ep_plan")
         check(lib.i4tc_moe_ep_dispatch_quant(x.data_ptr(), self.T, self.H, x.stride(0), self.sorted_pairs.data_ptr(),
-                                             self.P, self.k, self.slot.data_ptr(), self.send.data_ptr(), self.row_bytes,
-                                             d, st), "moe_ep_dispatch_quant")
+                                             self.P, self.k, self.slot.data_ptr(), send, self.row_bytes, bases, self.cap,
+                                             self.rank, d, st), "moe_ep_dispatch_quant")
+
+    def _signal(self, addrs):
+        from ._cabi import check
+        check(self._lib.i4tc_peer_signal(addrs.data_ptr(), self.world, self.epoch, self.dev.index,
+                                         torch.cuda.current_stream(self.dev).cuda_stream), "peer_signal")
+
+    def _wait(self, flags):
+        from ._cabi import check
+        check(self._lib.i4tc_peer_wait(flags.data_ptr(), self.world, self.epoch, self.dev.index,
+                                       torch.cuda.current_stream(self.dev).cuda_stream), "peer_wait")
 
     def _unpack(self):
         from ._cabi import check
@@ -340,10 +404,25 @@ class ExpertParallelMoE:
     def _pack_return(self):
         from ._cabi import check
         lib, d, st = self._lib, self.dev.index, torch.cuda.current_stream(self.dev).cuda_stream
-        check(lib.i4tc_moe_ep_pack_return(self.y.data_ptr(), self.pos_of.data_ptr(), self.r_max, self.H,
-                                          self.ret_send.data_ptr(), d, st), "moe_ep_pack_return")
+        if self.transport == "peer":
+            check(lib.i4tc_moe_ep_pack_return(self.y.data_ptr(), self.pos_of.data_ptr(), self.r_max, self.H, None,
+                                              self.ret_bases.data_ptr(), self.meta.data_ptr(), self.world, self.e_loc,
+                                              self.cap, d, st), "moe_ep_pack_return")
+        else:
+            check(lib.i4tc_moe_ep_pack_return(self.y.data_ptr(), self.pos_of.data_ptr(), self.r_max, self.H,
+                                              self.ret_send.data_ptr(), None, None, 0, 0, 0, d, st), "moe_ep_pack_return")
 
     def _stages(self, x, expert_ids, expert_w):
+        if self.transport == "peer":
+            self.epoch += 1
+            yield "sort_plan_quantise_store", lambda: (self._prepare(x, expert_ids), self._signal(self.flag_addrs_dispatch))
+            yield "wait_rows", lambda: self._wait(self.flags_dispatch)
+            yield "unpack", self._unpack
+            yield "experts", self._experts
+            yield "return_store", lambda: (self._pack_return(), self._signal(self.flag_addrs_return))
+            yield "wait_returns", lambda: self._wait(self.flags_return)
+            yield "combine", lambda: self._moe.moe_combine(self.ret_local, self.inv_pairs, expert_w.contiguous(), self.T, self.k)
+            return
         yield "sort_plan_quantise", lambda: self._prepare(x, expert_ids)
         yield "dispatch_all_to_all", lambda: dist.all_to_all_single(self.recv, self.send, group=self.group)
         yield "unpack", self._unpack
@@ -387,5 +466,8 @@ class ExpertParallelMoE:
         return {n: round(v, 1) for n, v in acc.items()}
 
     def close(self) -> None:
-        for n in ("send", "recv", "ap", "asc", "h", "hp", "hs", "y", "ret_send", "ret_recv"):
+        if self.transport == "peer":
+            torch.cuda.synchronize(self.dev)
+            dist.barrier(group=self.group)   # nobody still writes into a buffer that is about to go
+        for n in ("send", "recv", "ap", "asc", "h", "hp", "hs", "y", "ret_send", "ret_recv", "ret_local", "_symm", "_hdl"):
             setattr(self, n, None)

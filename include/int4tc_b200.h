@@ -267,13 +267,30 @@ int i4tc_moe_silu_mul_quant(const void* h, int64_t P, int64_t I, uint8_t* packed
  * (token, slot) pair the row of the returned [world * cap, H] buffer that holds its expert output (-1: none).
  * overflow: device word, bit 0 set when a destination would have received more than cap rows -- the layer's result
  * is then incomplete and the caller repeats the step with exact split sizes; nothing is ever read or written out of
- * range.  meta: int32 scratch of i4tc_moe_ep_meta_ints(world, e_loc) entries.  rows_dev: device int32, rows received. */
+ * range.  meta: int32 scratch of i4tc_moe_ep_meta_ints(world, e_loc) entries.  rows_dev: device int32, rows received.
+ *
+ * Peer destinations.  Where the ranks' receive and return buffers are mapped into the address space of every other rank
+ * (symmetric memory over NVLink), peer_bases [world] (device array of addresses: the receive buffer of rank d for the
+ * plan and dispatch calls, the return buffer [num_pairs, H] of rank s for the pack_return call) makes the kernels store
+ * rows straight into the buffer of the destination -- block `my_rank` of the receive buffer of d, row (start + j) of the
+ * return buffer of s, i.e. the sorted order of the source, so that the source combines with inv_pairs as on one GPU -- and
+ * no all-to-all is needed; the ranks order their accesses with i4tc_peer_signal / i4tc_peer_wait.  With
+ * peer_bases = NULL everything goes to the local send buffers as described above. */
 int i4tc_moe_ep_plan(const int32_t* expert_offsets, const int32_t* sorted_pairs, int64_t num_pairs,
                      int64_t num_experts, int64_t world, int64_t cap, int64_t row_bytes, void* send_buf,
-                     int32_t* slot, int32_t* ret_row, unsigned int* overflow, int device, void* stream);
+                     int32_t* slot, int32_t* ret_row, unsigned int* overflow, const uint64_t* peer_bases,
+                     int64_t my_rank, int device, void* stream);
 int i4tc_moe_ep_dispatch_quant(const void* x, int64_t num_tokens, int64_t K, int64_t ldx,
                                const int32_t* sorted_pairs, int64_t num_pairs, int64_t top_k,
-                               const int32_t* slot, void* send_buf, int64_t row_bytes, int device, void* stream);
+                               const int32_t* slot, void* send_buf, int64_t row_bytes,
+                               const uint64_t* peer_bases, int64_t cap, int64_t my_rank, int device, void* stream);
+/* flag_addrs [world] (device array): address, in the flag array of every rank, of the slot that belongs to this rank.
+ * Once all earlier work of `stream` is done the slot receives `epoch` (system-scope release).  i4tc_peer_wait makes
+ * `stream` wait until all `world` slots of the local array `flags` have reached `epoch`; after two seconds it gives
+ * up, sets bit 1 of the status word (i4tc_check_status) and lets the stream continue.  Epochs grow by one per
+ * exchange; waiting and signalling kernels of different ranks run on different GPUs. */
+int i4tc_peer_signal(const uint64_t* flag_addrs, int64_t world, uint32_t epoch, int device, void* stream);
+int i4tc_peer_wait(const uint32_t* flags, int64_t world, uint32_t epoch, int device, void* stream);
 int64_t i4tc_moe_ep_meta_ints(int64_t world, int64_t e_loc);
 /* a_packed [G, world * cap, 64], a_scale [G, world * cap]: received rows in expert-sorted order (rows past *rows_dev
  * are not written); expert_offsets_loc [e_loc + 1]; pos_of [world * cap]: sorted position of received row (s, j). */
@@ -286,7 +303,8 @@ int i4tc_moe_silu_mul_quant_rows(const void* h, int64_t max_rows, const int32_t*
 /* ret_send[row, :] = y[pos_of[row], :] for the `rows` = world * cap buffer rows (bf16 [.., H]); rows without a
  * received token (pos_of < 0) are left as they are. */
 int i4tc_moe_ep_pack_return(const void* y, const int32_t* pos_of, int64_t rows, int64_t H, void* ret_send,
-                            int device, void* stream);
+                            const uint64_t* peer_bases, const int32_t* meta, int64_t world, int64_t e_loc,
+                            int64_t cap, int device, void* stream);
 
 /* out[t, :] = bf16( sum_j w[t, j] * y[inv_pairs[t*top_k + j], :] ), j ascending, fp32 sum.
  * y bf16 [P, H]; inv_pairs[pair] = sorted position of that pair. */

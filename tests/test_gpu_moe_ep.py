@@ -126,13 +126,16 @@ def _worker(rank, world, port):
         ops.check_status()
         assert torch.equal(out, ref[ts]), (quantized, (out.float() - ref[ts].float()).abs().max().item())
     # the fixed-capacity layer (no host synchronisation): the same bits again, twice in a row (buffers are reused)
-    layer = moe_ep.ExpertParallelMoE(mine, E, t_loc, k, H)
-    for _ in range(2):
-        out = layer(x[ts].contiguous(), ids[ts].contiguous(), w[ts].contiguous())
-        ops.check_status()
-        assert torch.equal(out, ref[ts])
-    assert not layer.overflowed()
-    tiny = moe_ep.ExpertParallelMoE(mine, E, t_loc, k, H, cap=64, check_each_call=True)   # overflows: redone exactly
+    for transport in ("nccl", "peer"):
+        layer = moe_ep.ExpertParallelMoE(mine, E, t_loc, k, H, transport=transport)
+        assert layer.transport == transport
+        for _ in range(3):
+            out = layer(x[ts].contiguous(), ids[ts].contiguous(), w[ts].contiguous())
+            ops.check_status()
+            assert torch.equal(out, ref[ts]), transport
+        assert not layer.overflowed()
+        layer.close()
+    tiny = moe_ep.ExpertParallelMoE(mine, E, t_loc, k, H, cap=64, check_each_call=True, transport="nccl")   # overflows: redone exactly
     assert torch.equal(tiny(x[ts].contiguous(), ids[ts].contiguous(), w[ts].contiguous()), ref[ts])
     dist.barrier()
     dist.destroy_process_group()
