@@ -40,6 +40,8 @@ SIGNATURES = {
     "i4tc_unpack_int4_to_int8": (_i, [_p, _l, _l, _p, _i, _p]),
     "i4tc_gemm_int32": (_i, [_p, _p, _p, _l, _l, _l, _i, _p]),
     "i4tc_gemm_scaled": (_i, [_p, _p, _p, _p, _p, _i, _l, _l, _l, _i, _p]),
+    "i4tc_gemm_w4a8_scaled": (_i, [_p, _p, _p, _p, _p, _i, _l, _l, _l, _i, _p]),
+    "i4tc_quant_rowwise_int8": (_i, [_p, _i, _l, _l, _l, _p, _p, _i, _p]),
     "i4tc_gemm_grouped": (_i, [_p, _p, _p, _p, _p, _l, _l, _l, _l, _i, _p]),
     "i4tc_gemm_grouped_azp": (_i, [_p, _p, _p, _p, _p, _p, _p, _l, _l, _l, _l, _i, _p]),
     "i4tc_gemm_grouped_int32": (_i, [_p, _p, _p, _l, _l, _l, _i, _p]),

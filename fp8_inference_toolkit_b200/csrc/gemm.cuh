@@ -23,6 +23,10 @@ struct GemmParams {
   int p_rowmajor;    // 1: P tensor map is 2-D [rows, K/2] (x = g*64); 0: 3-D [G', rows, 64] (z = g)
   int q_rowmajor;
   int swap;          // output element (p, q) is out[q, p] instead of out[p, q]
+  int i8_operands;   // 1: both operands are int8 already ([rows, K] row-major): TMA loads them straight into the
+                     //    swizzled int8 stages and nothing is converted (W4A8: int8 activations, int4 weights held as int8)
+  float acc_unit;    // what one unit of the int32 accumulator is worth: 1/256 for packed int4 operands (both carry
+                     //    16 x code), 1 for int8 operands
   int epi_mode;      // EpiMode
   int out_dtype;     // I4TC_BF16 / I4TC_FP16 / I4TC_INT32
   const float* sp;   // P-side scales, element (g, p) at sp[g * sp_gstride + p]
@@ -75,5 +79,8 @@ int launch_w4a4_gemv(const uint8_t* x, const uint8_t* w, const float* sx, const 
 // rowmajor: 2-D view [rows, row_bytes]; otherwise 3-D view [slabs, rows, 64].
 int get_tensor_map(int device, const void* base, bool rowmajor, long long rows, long long row_bytes_or_slabs,
                    int box_rows, CUtensorMap* out);
+// Tensor map over int8 data [rows, K] (row pitch K bytes): boxes of 128 bytes (one K group) x box_rows, written to
+// shared memory in the 128-byte swizzle the MMA descriptors expect; bytes past K read as zero.
+int get_tensor_map_i8(int device, const void* base, long long rows, long long K, int box_rows, CUtensorMap* out);
 
 }  // namespace i4tc

@@ -80,6 +80,7 @@ struct DenseArgs {
   // zero-point term (per-group mode only): group g adds azp_adj[g, m] * w_col_sum[g, n] to its integer sum
   const float* azp_adj = nullptr;
   const float* w_col_sum = nullptr;
+  bool i8_operands = false;   // a and b are int8 [rows, K] (W4A8): no conversion, accumulator unit 1
 };
 
 static int run_dense(const DenseArgs& d, int device, void* stream) {
@@ -92,7 +93,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   I4TC_REQUIRE(d.M < (1ll << 31) - 256 && d.N < (1ll << 31) - 256, I4TC_EINVAL, "M or N too large");
 
   // a handful of tokens: stream the weights through the CUDA cores instead (unless a test pins the tile shape)
-  if (g_force_bn == 0 && g_force_swap < 0 && g_force_splits == 0 && d.azp_adj == nullptr &&
+  if (g_force_bn == 0 && g_force_swap < 0 && g_force_splits == 0 && d.azp_adj == nullptr && !d.i8_operands &&
       gemv_applicable(d.M, d.N, (long long)d.G * 128, d.epi_mode) && (!d.rowmajor || d.K == (long long)d.G * 128))
     return launch_w4a4_gemv(d.a, d.b, d.sa, d.sb, d.out, d.out_dtype, d.M, d.N, d.G, d.rowmajor, d.epi_mode,
                             info->sm_count, static_cast<cudaStream_t>(stream));
@@ -103,6 +104,8 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   memset(&p, 0, sizeof(p));
   p.G = d.G;
   p.swap = sh.swap ? 1 : 0;
+  p.i8_operands = d.i8_operands ? 1 : 0;
+  p.acc_unit = d.i8_operands ? 1.0f : 1.0f / 256.0f;
   p.epi_mode = d.epi_mode;
   p.out_dtype = d.out_dtype;
   p.out = d.out;
@@ -139,7 +142,8 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   // in fp32 for per-channel scales (bit-identical to the unsplit result).
   p.splits = 1;
   p.groups_per_split = d.G;
-  if ((d.epi_mode == EPI_GROUP || d.epi_mode == EPI_CHANNEL) && d.M <= 128 && g_force_splits != 1) {
+  // (int8 operands: sums of a K range can exceed 2^24, so they are never parked in fp32)
+  if ((d.epi_mode == EPI_GROUP || d.epi_mode == EPI_CHANNEL) && d.M <= 128 && g_force_splits != 1 && !d.i8_operands) {
     // cost in microseconds: waves x groups per range x ~0.65 us per group handshake, plus writing and
     // reading the fp32 partial sums at ~6 TB/s and one more launch
     int best_s = 1;
@@ -179,9 +183,13 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   if (pair && g_cta_pairs < 0 && !g_pairs_launchable) pair = false;
   CUtensorMap tmP, tmQ;
   const long long extent = d.rowmajor ? d.K / 2 : (long long)d.G;
-  if (int rc = get_tensor_map(device, pbase, d.rowmajor, prow, extent, 128, &tmP)) return rc;
+  auto operand_map = [&](const uint8_t* base, long long rows, int box_rows, CUtensorMap* out) -> int {
+    if (d.i8_operands) return get_tensor_map_i8(device, base, rows, d.K, box_rows, out);
+    return get_tensor_map(device, base, d.rowmajor, rows, extent, box_rows, out);
+  };
+  if (int rc = operand_map(pbase, prow, 128, &tmP)) return rc;
   if (pair) {
-    if (int rc = get_tensor_map(device, qbase, d.rowmajor, qrow, extent, 128, &tmQ)) return rc;
+    if (int rc = operand_map(qbase, qrow, 128, &tmQ)) return rc;
     GemmParams pp = p;
     pp.num_p_tiles = (int)((prow + 255) / 256);
     const int grid = 2 * (int)(pair_tiles < clusters_max ? pair_tiles : clusters_max);
@@ -193,7 +201,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
     cudaGetLastError();
     g_pairs_launchable = false;
   }
-  if (int rc = get_tensor_map(device, qbase, d.rowmajor, qrow, extent, sh.bn, &tmQ)) return rc;
+  if (int rc = operand_map(qbase, qrow, sh.bn, &tmQ)) return rc;
   const long long items = tiles * p.splits;
   const int grid = (int)(items < info->sm_count ? items : info->sm_count);
   if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, false, epi_warps_for(d.epi_mode), static_cast<cudaStream_t>(stream))) return rc;
@@ -267,6 +275,21 @@ extern "C" int i4tc_gemm_scaled(const uint8_t* a, const uint8_t* b, const float*
   return run_dense(d, device, stream);
 }
 
+extern "C" int i4tc_gemm_w4a8_scaled(const int8_t* a, const int8_t* b, const float* scale_a, const float* scale_b,
+                                     void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int device,
+                                     void* stream) {
+  I4TC_REQUIRE(K > 0 && K % 32 == 0, I4TC_EINVAL, "K must be multiple of 32 for INT8 alignment");
+  I4TC_REQUIRE(K <= 65536, I4TC_EINVAL, "K must not exceed 65536");
+  I4TC_REQUIRE(out_dtype == I4TC_BF16 || out_dtype == I4TC_FP16, I4TC_EUNSUPPORTED, "out must be bf16 or fp16");
+  int rc = check_dense_common(a, b, out, M, N);
+  if (rc) return rc < 0 ? rc : I4TC_OK;
+  I4TC_REQUIRE(scale_a && scale_b, I4TC_EINVAL, "null scale pointer");
+  DenseArgs d{reinterpret_cast<const uint8_t*>(a), reinterpret_cast<const uint8_t*>(b), scale_a, scale_b, out, out_dtype,
+              M, N, (int)((K + 127) / 128), true, K, EPI_CHANNEL};
+  d.i8_operands = true;
+  return run_dense(d, device, stream);
+}
+
 extern "C" int i4tc_gemm_grouped(const uint8_t* a, const uint8_t* b, const float* scale_a, const float* scale_b,
                                  void* out, int64_t M, int64_t N, int64_t group_size, int64_t num_groups,
                                  int device, void* stream) {
@@ -329,6 +352,7 @@ extern "C" int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, con
   p.Q_rows = (int)N;
   p.G = (int)num_groups;
   p.epi_mode = EPI_GROUP;
+  p.acc_unit = 1.0f / 256.0f;
   p.out_dtype = I4TC_BF16;
   p.sp = scale_a;
   p.sq = scale_b;

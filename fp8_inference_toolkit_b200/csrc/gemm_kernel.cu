@@ -366,7 +366,7 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
   // order of the two multiplies: normal (p = m): (acc * sp) * sq ; swapped (p = n): (acc * sq) * sp.
   // The accumulators are 256 x the integer sums; 2^-8 rides on the row-side scale (exact in both orders).
   constexpr bool pq_order = !SWAP;
-  constexpr float kInv256 = 1.0f / 256.0f;
+  const float kInv256 = p.acc_unit;   // 2^-8 for packed int4 operands (both carry 16 x code)
   constexpr uint32_t NS = AZP ? kNS / 2 : kNS;                       // scale stages in the ring
   constexpr int STAGE_F = (AZP ? 2 : 1) * (C::SCALE_STAGE / 4);      // floats per stage
 
@@ -536,7 +536,7 @@ __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* s
   const int col_base = part * CW;
   const int lq = lane & 3, lr = lane >> 2;
   float* sq_s = reinterpret_cast<float*>(smem + C::OFF_SQ) + ew * CW;
-  constexpr float kInv256 = 1.0f / 256.0f;
+  const float kInv256 = p.acc_unit;   // 2^-8 for packed int4 operands, 1 for int8 operands
   // normal: columns are n, so the column scale (scale_b) multiplies first; swapped: rows are n.
   // The first multiplier also carries the 2^-8 that undoes the x16 operand scaling (exact).
   constexpr bool q_first = !SWAP;
@@ -755,6 +755,26 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     TileInfo ti;
     uint32_t it = 0;
     bool ok = true;
+    if (p.i8_operands) {
+      // int8 operands: the tiles land in the swizzled int8 stages themselves (the tensor maps swizzle); the stage is
+      // free again when the MMAs that read it have completed
+      while (ok && sched.template next<BN>(p, ti)) {
+        for (int g = ti.g0; g < ti.g1; ++g, ++it) {
+          const uint32_t s = it % C::NI, ph = (it / C::NI) & 1u;
+          ok = wait_bar(bar_i8_empty + s * 8, ph ^ 1u, abort_flag);
+          if (!ok) break;
+          if (lane == 0) {
+            const uint32_t full = bar_pk_full + s * 8;
+            const uint32_t dstP = sbase + C::OFF_I8 + s * (C::I8_P + C::I8_Q);
+            const uint32_t dstQ = dstP + C::I8_P;
+            mbar_arrive_expect_tx(full, C::I8_P + C::I8_Q);
+            tma_load_2d(dstP, &tmP, full, g * kI8Row, ti.p0);
+            tma_load_2d(dstQ, &tmQ, full, g * kI8Row, ti.q0 + (int)rank * C::QR);
+          }
+          __syncwarp();
+        }
+      }
+    } else {
     while (ok && sched.template next<BN>(p, ti)) {
       for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         const uint32_t s = it % C::NP, ph = (it / C::NP) & 1u;
@@ -774,12 +794,14 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         __syncwarp();
       }
     }
+    }
     if (!ok) {
       // aborting: wait (bounded) for copies that may still be in flight into this CTA's shared memory
-      const uint32_t n = it < (uint32_t)C::NP ? it : (uint32_t)C::NP;
+      const uint32_t depth = p.i8_operands ? (uint32_t)C::NI : (uint32_t)C::NP;
+      const uint32_t n = it < depth ? it : depth;
       for (uint32_t j = it - n; j < it; ++j) {
         const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(bar_pk_full + (j % C::NP) * 8, (j / C::NP) & 1u)) {
+        while (!mbar_try_wait(bar_pk_full + (j % depth) * 8, (j / depth) & 1u)) {
           if (globaltimer_ns() - t0 > 100000000ull) break;
         }
       }
@@ -887,6 +909,17 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     TileInfo ti;
     uint32_t it = 0;
     bool ok = true;
+    if (p.i8_operands) {
+      // nothing to convert: these warps only pass "tile landed" on to the MMA thread (in a CTA pair: the leader's)
+      while (ok && sched.template next<BN>(p, ti)) {
+        for (int g = ti.g0; g < ti.g1; ++g, ++it) {
+          const uint32_t si = it % C::NI, phi = (it / C::NI) & 1u;
+          ok = wait_bar(bar_pk_full + si * 8, phi, abort_flag);
+          if (!ok) break;
+          if (lane == 0) arrive_bar<CG>(arr_i8_full + si * 8);
+        }
+      }
+    } else
     while (ok && sched.template next<BN>(p, ti)) {
       for (int g = ti.g0; g < ti.g1; ++g, ++it) {
         const uint32_t sp_ = it % C::NP, php = (it / C::NP) & 1u;

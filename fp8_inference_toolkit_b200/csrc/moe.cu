@@ -314,7 +314,21 @@ __global__ void __launch_bounds__(256) moe_ep_pack_return_kernel(const __nv_bflo
     const int s = (int)(row / cap), j = (int)(row - (long long)s * cap);
     dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_bases[s]) + ((long long)start[s] + j) * H);
   }
-  for (int c = lane; c < H / 8; c += 32) dst[c] = __ldg(src + c);
+  // four 16-byte loads in flight per lane before the (possibly remote) stores
+  const int n = H / 8;
+  for (int c0 = 0; c0 < n; c0 += 128) {
+    uint4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = c0 + i * 32 + lane;
+      if (c < n) v[i] = __ldg(src + c);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = c0 + i * 32 + lane;
+      if (c < n) dst[c] = v[i];
+    }
+  }
 }
 
 // Cross-GPU completion flags.  A rank that has finished writing into its peers' buffers (all earlier work of its

@@ -252,9 +252,87 @@ __global__ void __launch_bounds__(256) weight_group_sums_kernel(const uint32_t* 
 
 }  // namespace
 
+// Per-token symmetric int8: scale = max(absmax / 127, 1 / (127 * 512)); q = clamp(rint(x / (absmax / 127)), -128, 127)
+// with IEEE division (the reproducible form of the reference's x * (127 / absmax)).  One block per row; the second pass
+// over the row hits L1 / L2.
+template <typename T>
+__global__ void __launch_bounds__(256) quant_int8_rowwise_kernel(const T* __restrict__ x, int K, int64_t ldx,
+                                                                 int8_t* __restrict__ q, float* __restrict__ scale) {
+  __shared__ float s_max[8];
+  const int64_t r = blockIdx.x;
+  const T* src = x + r * ldx;
+  int8_t* dst = q + r * (int64_t)K;
+  float m = 0.f;
+  const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0) &&
+                   sizeof(T) == 2;
+  if (vec) {
+    for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+      const uint4 u = *reinterpret_cast<const uint4*>(src + k);
+      const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(to_f32(e[i])));
+    }
+  } else {
+    for (int k = threadIdx.x; k < K; k += 256) m = fmaxf(m, fabsf(to_f32(src[k])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = s_max[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, s_max[i]);
+  const float s = __fdiv_rn(m, 127.0f);
+  if (threadIdx.x == 0) scale[r] = fmaxf(s, 1.0f / (127.0f * 512.0f));
+  auto code = [&](float v) -> int {
+    if (m == 0.f) return 0;
+    const float t = fminf(fmaxf(rintf(__fdiv_rn(v, s)), -128.0f), 127.0f);
+    return (int)t;
+  };
+  if (vec) {
+    for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+      const uint4 u = *reinterpret_cast<const uint4*>(src + k);
+      const T* e = reinterpret_cast<const T*>(&u);
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        lo |= ((uint32_t)code(to_f32(e[i])) & 0xFFu) << (8 * i);
+        hi |= ((uint32_t)code(to_f32(e[i + 4])) & 0xFFu) << (8 * i);
+      }
+      *reinterpret_cast<uint2*>(dst + k) = make_uint2(lo, hi);
+    }
+  } else {
+    for (int k = threadIdx.x; k < K; k += 256) dst[k] = (int8_t)code(to_f32(src[k]));
+  }
+}
+
 }  // namespace i4tc
 
 using namespace i4tc;
+
+extern "C" int i4tc_quant_rowwise_int8(const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx, int8_t* q,
+                                       float* scale, int device, void* stream) {
+  I4TC_REQUIRE(rows >= 0 && K >= 0 && K < (1ll << 31) && rows < (1ll << 31), I4TC_EINVAL, "bad sizes");
+  if (rows == 0 || K == 0) return I4TC_OK;
+  I4TC_REQUIRE(x && q && scale, I4TC_EINVAL, "null pointer");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case I4TC_BF16:
+      quant_int8_rowwise_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), (int)K, ldx, q, scale);
+      break;
+    case I4TC_FP16:
+      quant_int8_rowwise_kernel<__half><<<(unsigned)rows, 256, 0, st>>>(static_cast<const __half*>(x), (int)K, ldx, q, scale);
+      break;
+    case I4TC_FP32:
+      quant_int8_rowwise_kernel<float><<<(unsigned)rows, 256, 0, st>>>(static_cast<const float*>(x), (int)K, ldx, q, scale);
+      break;
+    default: return fail(I4TC_EUNSUPPORTED, "unsupported input dtype %d", dtype);
+  }
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
 
 extern "C" int i4tc_quant_clipped_grouped(const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx,
                                           int64_t group_size, double clip_ratio, uint8_t* packed, float* scale,

@@ -103,7 +103,7 @@ static EncodeTiledFn encode_fn() {
 struct MapKey {
   const void* base;
   long long rows, extent;
-  int box_rows, rowmajor, device;
+  int box_rows, rowmajor, device;   // rowmajor: 0 = group-major packed, 1 = row-major packed, 2 = row-major int8 (swizzled)
   bool operator==(const MapKey& o) const {
     return base == o.base && rows == o.rows && extent == o.extent && box_rows == o.box_rows &&
            rowmajor == o.rowmajor && device == o.device;
@@ -154,6 +154,37 @@ int get_tensor_map(int device, const void* base, bool rowmajor, long long rows, 
            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   }
+  I4TC_REQUIRE(r == CUDA_SUCCESS, I4TC_EINVAL, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  MapEntry& e = g_maps[g_map_next];
+  g_map_next = (g_map_next + 1) % kMapCache;
+  e.key = key;
+  e.map = m;
+  e.used = true;
+  *out = m;
+  return I4TC_OK;
+}
+
+int get_tensor_map_i8(int device, const void* base, long long rows, long long K, int box_rows, CUtensorMap* out) {
+  I4TC_REQUIRE(aligned_to(base, 16), I4TC_EALIGN, "int8 operand must be 16-byte aligned");
+  I4TC_REQUIRE(rows > 0 && K > 0 && rows < (1ll << 31), I4TC_EINVAL, "bad operand shape");
+  I4TC_REQUIRE(K % 16 == 0, I4TC_EALIGN, "K must be a multiple of 16 for int8 operands");
+  MapKey key{base, rows, K, box_rows, 2, device};
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (int i = 0; i < kMapCache; ++i)
+    if (g_maps[i].used && g_maps[i].key == key) {
+      *out = g_maps[i].map;
+      return I4TC_OK;
+    }
+  EncodeTiledFn fn = encode_fn();
+  I4TC_REQUIRE(fn != nullptr, I4TC_EDEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap m;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K};
+  cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   I4TC_REQUIRE(r == CUDA_SUCCESS, I4TC_EINVAL, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   MapEntry& e = g_maps[g_map_next];
   g_map_next = (g_map_next + 1) % kMapCache;

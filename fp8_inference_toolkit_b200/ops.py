@@ -271,6 +271,41 @@ def cutlass_int4_scaled_mm(a_packed, b_packed, scale_a, scale_b, out, M: int, N:
           "cutlass_int4_scaled_mm")
 
 
+def dynamic_int8_quant(input: torch.Tensor):
+    """[M,K] float -> (int8 [M,K], fp32 scale [M]): per-token symmetric int8, ``scale = max(absmax / 127, 1/(127*512))``.
+    Reference: ``int4_quant.cu:511`` (kernel ``:432``)."""
+    _cuda2d(input, "input")
+    x = _float_input(input, "input")
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    scale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    check(lib.i4tc_quant_rowwise_int8(x.data_ptr(), _DTYPES[x.dtype], M, K, x.stride(0), q.data_ptr(), scale.data_ptr(),
+                                      _dev(x), _stream(x)), "dynamic_int8_quant")
+    return q, scale
+
+
+def cutlass_w4a8_scaled_mm(a, b_int8, scale_a, scale_b, out, M: int, N: int, K: int) -> None:
+    """``out[m,n] = cast((sum_k a[m,k] * b_int8[n,k]) * scale_b[n] * scale_a[m])`` with int8 ``a`` [M,K] and the int4
+    weight held as int8 ``b_int8`` [N,K] (``unpack_int4_to_int8``).  Reference: ``int4_gemm.cu:874-899``."""
+    _require(a.is_cuda and b_int8.is_cuda, "Inputs must be CUDA")
+    _require(scale_a.is_cuda and scale_b.is_cuda, "Scales must be CUDA")
+    _require(out.is_cuda, "Output must be CUDA")
+    _require(K % 32 == 0, "K must be multiple of 32 for INT8 alignment")
+    _require(a.dtype == torch.int8, "a must be int8")
+    _require(b_int8.dtype == torch.int8, "b_int8 must be int8")
+    _require(out.dtype in (torch.bfloat16, torch.float16),
+             "cutlass_w4a8_scaled_mm: unsupported output dtype, must be bfloat16 or float16")
+    _same_device(a, b_int8, scale_a, scale_b, out)
+    _require(a.is_contiguous() and a.numel() == M * K, "a must be a contiguous [M,K] tensor")
+    _require(b_int8.is_contiguous() and b_int8.numel() == N * K, "b_int8 must be a contiguous [N,K] tensor")
+    _require(out.is_contiguous() and out.numel() == M * N, "out must be a contiguous [M,N] tensor")
+    _f32(scale_a, "scale_a", M)
+    _f32(scale_b, "scale_b", N)
+    check(lib.i4tc_gemm_w4a8_scaled(a.data_ptr(), b_int8.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(),
+                                    out.data_ptr(), _DTYPES[out.dtype], M, N, K, _dev(out), _stream(out)),
+          "cutlass_w4a8_scaled_mm")
+
+
 def cutlass_int4_fused_grouped_gemm(a_packed, b_packed, scale_a, scale_b, out, M: int, N: int,
                                     group_size: int, num_groups: int) -> None:
     """Per-group-128 fused linear into the caller's bf16 ``out`` [M,N].

@@ -1,13 +1,11 @@
-"""Ops of the reference surface that are outside the W4A4 hot path (W4A8, W4A16, FP8 and
-int8-activation variants; ``int4_native_tc/int4_native_tc/__init__.py:86-122``).  They are exported so
+"""Ops of the reference surface that are outside the W4A4 hot path (grouped W4A8, W4A16, FP8 and
+grouped int8-activation variants; ``int4_native_tc/int4_native_tc/__init__.py:86-122``).  They are exported so
 that ``from int4_native_tc import *`` keeps working, and raise when called."""
 from __future__ import annotations
 
 UNPORTED = [
-    "cutlass_w4a8_scaled_mm",
     "cutlass_w4a16_mm_grouped",
     "cutlass_w4a8_scaled_mm_grouped",
-    "dynamic_int8_quant",
     "dequant_int4_to_bf16",
     "dequant_int4_to_fp16",
     "dynamic_int8_quant_grouped",

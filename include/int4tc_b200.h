@@ -161,6 +161,19 @@ int i4tc_gemm_scaled(const uint8_t* a, const uint8_t* b, const float* scale_a,
                      const float* scale_b, void* out, int out_dtype, int64_t M, int64_t N,
                      int64_t K, int device, void* stream);
 
+/* W4A8: int8 activations x int4 weights held as int8 (the output of i4tc_unpack_int4_to_int8), both [rows, K]
+ * row-major; out[m,n] = cast((int32 acc * scale_b[n]) * scale_a[m]).  Replaces cutlass_w4a8_scaled_mm
+ * (int4_native_tc/csrc/int4_gemm.cu:874-899, kernel instantiation :284-378).  K must be a multiple of 32 (as
+ * int4_gemm.cu:885); a and b 16-byte aligned.  The operands go by TMA straight into the swizzled int8 stages of the
+ * tensor-core kernel (nothing is converted). */
+int i4tc_gemm_w4a8_scaled(const int8_t* a, const int8_t* b, const float* scale_a, const float* scale_b,
+                          void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int device, void* stream);
+
+/* Per-token symmetric int8 quantise: q int8 [rows, K], scale fp32 [rows] = max(absmax / 127, 1 / (127 * 512)).
+ * Replaces dynamic_int8_quant (int4_native_tc/csrc/int4_quant.cu:432-537). */
+int i4tc_quant_rowwise_int8(const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx, int8_t* q,
+                            float* scale, int device, void* stream);
+
 /* Per-group-128 fused linear:
  *   out[m,n] = bf16( sum_g (float(acc_g[m,n]) * scale_a[g,m]) * scale_b[g,n] ), g ascending.
  * a: [G, M, 64], b: [G, N, 64] group-major packed; scale_a [G,M]; scale_b [G,N]; out bf16 [M,N].

@@ -4,6 +4,8 @@ from fp8_inference_toolkit_b200.ops import (  # noqa: F401
     cutlass_int4_gemm,
     cutlass_int4_scaled_mm,
     cutlass_int4_scaled_mm_grouped,
+    cutlass_w4a8_scaled_mm,
+    dynamic_int8_quant,
     cutlass_int4_fused_grouped_gemm,
     cutlass_int4_fused_grouped_gemm_v5,
     cutlass_int4_fused_grouped_gemm_v7,

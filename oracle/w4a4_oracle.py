@@ -310,6 +310,34 @@ def linear_per_channel(a_codes, b_codes, scale_a, scale_b) -> torch.Tensor:
     return to_bf16(dequant_per_channel(int_gemm(a_codes, b_codes), scale_a, scale_b))
 
 
+#: int8 activation scale floor, ``int4_native_tc/csrc/int4_quant.cu:423``
+K_MIN_SCALE_INT8 = F32(1.0) / (F32(127.0) * F32(512.0))
+
+
+def quant_rowwise_int8(x):
+    """Per-token symmetric int8 (``dynamic_int8_quant``, ``int4_quant.cu:432-537``): ``scale = max(absmax / 127,
+    1 / (127 * 512))`` (``:473``), ``q = clamp(rint(x / (absmax / 127)), -128, 127)``, zero rows give zero codes.
+    The kernel multiplies by ``127 / absmax`` under fast-math (``:477,486``); as for the int4 quantisers the
+    IEEE-reproducible division form is used here.  **Parity unpinned** (the reference's tests check this op only
+    through loose end-to-end errors, ``test_correctness.py:589-615``).  Returns (int8 [R,K], fp32 [R])."""
+    xf = _to_f32(x)
+    absmax = np.abs(xf).max(axis=1) if xf.shape[1] else np.zeros(xf.shape[0], F32)
+    s = (absmax.astype(F32) / F32(127.0)).astype(F32)
+    safe = np.where(s == 0, F32(1.0), s).astype(F32)
+    q = np.clip(np.rint((xf / safe[:, None]).astype(F32)), -128.0, 127.0)
+    q = np.where((s == 0)[:, None], F32(0.0), q)
+    return q.astype(np.int8), np.maximum(s, K_MIN_SCALE_INT8).astype(F32)
+
+
+def linear_w4a8(a_int8, b_int8, scale_a, scale_b, dtype=torch.bfloat16) -> torch.Tensor:
+    """W4A8 linear (``cutlass_w4a8_scaled_mm``, ``int4_gemm.cu:874-899``): exact int32 product of int8 activations and
+    int4 weights held as int8 (``test_correctness.py:564``), then ``(float(acc) * scale_b[n]) * scale_a[m]`` in fp32
+    (the scaled epilogue shared with the W4A4 op, ``int4_gemm.cu:137-150``), cast to ``dtype``."""
+    acc = (np.asarray(a_int8).astype(np.int64) @ np.asarray(b_int8).astype(np.int64).T).astype(np.int32)
+    f = dequant_per_channel(acc, scale_a, scale_b)
+    return torch.from_numpy(np.ascontiguousarray(f, dtype=F32)).to(dtype)
+
+
 def linear_grouped_f32(a_codes, b_codes, scale_a, scale_b) -> np.ndarray:
     """Per-group W4A4 linear before the final cast.  ``a_codes`` [G,M,gs],
     ``b_codes`` [G,N,gs], scales [G,M] / [G,N].  fp32 accumulation in ascending

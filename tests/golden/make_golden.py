@@ -24,6 +24,9 @@ kat_native_matmul.npz      benchmark/verify_int4_matmul_precision.py:16-29 (int3
                            followed by fp32 scales) on a 16x512x64 case
 kat_quant_formula.npz      benchmark/benchmark_w4a8fp8.py:200-204 per-group weight quantiser
                            formula applied to a 32x512 bf16 matrix
+kat_w4a8_8x256x64.npz      int4_native_tc/test_correctness.py:551-566 (seed 88): int8 activations x int4
+                           weights, the int32 product and the scaled fp32 reference of the test's own CPU
+                           lines (executed from the reference file); scales from RandomState(89)
 """
 from __future__ import annotations
 
@@ -132,6 +135,21 @@ def main() -> None:
         w_bf16_bits=w_bf16.view(torch.int16).numpy(),
         codes=w_int4.to(torch.int8).numpy(),  # [N, G, GS]
         scale=g_scale.numpy(),  # [N, G]
+    )
+    # -- W4A8: the CPU lines of the reference's own test, executed from its source ------------------------
+    src = open(os.path.join(ref, "int4_native_tc", "test_correctness.py"), encoding="utf-8").read().splitlines()
+    body = [ln.strip() for ln in src[552:566]]          # test_w4a8_scaled_gemm: inputs and CPU reference
+    wanted = [ln for ln in body if ln.startswith(("M, K, N", "rng =", "a_int8 =", "b_int4 =", "acc =", "ref ="))]
+    env = {"np": np}
+    srng = np.random.RandomState(89)
+    for ln in wanted:
+        if ln.startswith("acc ="):
+            env["scale_a"] = srng.rand(env["M"]).astype(np.float32) * 0.01
+            env["scale_b"] = srng.rand(env["N"]).astype(np.float32) * 0.1
+        exec(ln, env)
+    np.savez_compressed(
+        os.path.join(HERE, "kat_w4a8_8x256x64.npz"),
+        a=env["a_int8"], b=env["b_int4"], scale_a=env["scale_a"], scale_b=env["scale_b"], acc=env["acc"], ref=env["ref"],
     )
     print("golden vectors written to", HERE)
 

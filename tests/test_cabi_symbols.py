@@ -52,7 +52,7 @@ def test_ops_reject_cpu_tensors(lib_built):
     with pytest.raises(RuntimeError, match="CUDA"):
         int4_native_tc.static_int4_weight_quant_grouped(torch.zeros(2, 128), 128)
     with pytest.raises(NotImplementedError):
-        int4_native_tc.cutlass_w4a8_scaled_mm()
+        int4_native_tc.cutlass_w4a8_scaled_mm_grouped()
     # the whole reference surface is importable
     import int4_native_tc_ops
 

@@ -124,3 +124,22 @@ def test_moe_sort_and_layer_shapes():
     order, off = O.moe_sort(ids, 4)
     assert off.tolist() == [0, 2, 5, 8, 8]
     assert order.tolist() == [1, 4, 2, 5, 7, 0, 3, 6]
+
+
+def test_w4a8_golden(golden_dir):
+    """int8 x int4-as-int8 product and scaled epilogue against the vector made by executing the CPU lines of the
+    reference's own test (int4_native_tc/test_correctness.py:551-566)."""
+    z = np.load(os.path.join(golden_dir, "kat_w4a8_8x256x64.npz"))
+    acc = (z["a"].astype(np.int64) @ z["b"].astype(np.int64).T).astype(np.int32)
+    assert np.array_equal(acc, z["acc"])
+    out = O.linear_w4a8(z["a"], z["b"], z["scale_a"], z["scale_b"], torch.float32).numpy()
+    # the test multiplies by scale_a first, the kernel's epilogue by scale_b first: the same up to fp32 rounding
+    np.testing.assert_allclose(out, z["ref"], rtol=3e-7, atol=0)
+
+
+def test_int8_quantiser_formula():
+    x = torch.tensor([[0.0, 0.0, 0.0, 0.0], [1.0, -2.0, 0.5, 127.0], [1e-9, -1e-9, 0.0, 5e-10]], dtype=torch.float32)
+    q, s = O.quant_rowwise_int8(x)
+    assert np.array_equal(q[0], [0, 0, 0, 0]) and s[0] == O.K_MIN_SCALE_INT8
+    assert np.array_equal(q[1], [1, -2, 0, 127]) and s[1] == np.float32(1.0)
+    assert np.array_equal(q[2], [127, -127, 0, 64]) and s[2] == O.K_MIN_SCALE_INT8   # codes from the un-floored absmax
