@@ -485,13 +485,23 @@ def bench_sweep(dev, peaks) -> list:
                    for _ in range(reps) for w in wr_]
             tch = graph_time(fns)
             del wr_, fns
+            # W4A8 of the same shape: int8 activations x int4 weights held as int8 (per-token / per-channel scales)
+            t8 = None
+            if M >= 16:
+                w8_ = [torch.randint(-8, 8, (N, K), dtype=torch.int8, device=dev) for _ in range(max(1, copies // 2))]
+                x8 = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev)
+                fns = [(lambda w=w: tc.cutlass_w4a8_scaled_mm(x8, w, sa1, sb1, out, M, N, K)) for _ in range(reps) for w in w8_]
+                t8 = graph_time(fns)
+                del w8_, fns
             ops_ = 2.0 * M * N * K
             byts = gemm_bytes(M, N, K)
             out_rows.append({"M": M, "shape": name, "K": K, "N": N, "us": t * 1e6, "tops": ops_ / t / 1e12,
                              "gbs": byts / t / 1e9, "frac_int8_peak": ops_ / t / 1e12 / int8_peak,
                              "frac_hbm": byts / t / 1e9 / peaks["hbm_gbs"],
                              "per_channel_us": tch * 1e6, "per_channel_tops": ops_ / tch / 1e12,
-                             "per_channel_frac_int8_peak": ops_ / tch / 1e12 / int8_peak})
+                             "per_channel_frac_int8_peak": ops_ / tch / 1e12 / int8_peak,
+                             "w4a8_us": None if t8 is None else t8 * 1e6,
+                             "w4a8_tops": None if t8 is None else ops_ / t8 / 1e12})
     return out_rows
 
 

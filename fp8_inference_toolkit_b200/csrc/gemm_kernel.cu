@@ -23,8 +23,8 @@
 // The MMA thread's loop is the serial path of the kernel (an MMA costs it ~50 cycles, a commit ~48, a barrier probe
 // 150-200), so it does the least possible per K group: two overlapped probes (operands converted, accumulator free),
 // four MMAs and ONE commit.  With a flush per group that commit's barrier tells the converters "stage free" and the
-// epilogue "accumulator full" at once; in a CTA pair it arrives in both CTAs (tcgen05.commit multicast).  The scale
-// stages are waited for by the epilogue warps, not by this thread.
+// epilogue "accumulator full" at once; in a CTA pair it arrives in both CTAs (tcgen05.commit multicast).  With
+// per-group scales, where the epilogue warps are the busy ones, this thread also waits for the group's scale stage.
 // CG = 2: two CTAs on neighbouring SMs share a 256 x 256 tile (tcgen05.mma.cta_group::2 issued by the first
 // one); each stages and converts its own 128 rows of P and only half of the Q rows.
 // Every wait is bounded: on expiry the kernel sets bit 0 of the status word, all roles leave
@@ -87,7 +87,7 @@ struct Cfg {
   static constexpr int SCALE_STAGE = (kBM + BN) * 4;                  // bytes
   static constexpr int SQ_BYTES = (kNS * SCALE_STAGE > EW * COLS_PER_WARP * 4) ? kNS * SCALE_STAGE : EW * COLS_PER_WARP * 4;
   static constexpr int OFF_BAR = OFF_SQ + SQ_BYTES;
-  static constexpr int NUM_BARS = 2 * NP + 2 * NI + 2 * NT + 2 * kNS;
+  static constexpr int NUM_BARS = 2 * NP + 2 * NI + 2 * NT + 3 * kNS;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;              // tmem ptr, abort flag
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;              // + alignment slack
 };
@@ -393,16 +393,9 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
       const uint32_t buf = flush % C::NT;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
       if (!pre) {
-        const uint32_t b_done = bar_done + (flush % C::NI) * 8, p_done = (flush / C::NI) & 1u;
-        const uint32_t b_sc = bar_sc_full + ss * 8, p_sc = (flush / NS) & 1u;
-        // both probes in flight together; the one-at-a-time waits run only if something is missing
-        const bool ready = mbar_test_wait(b_sc, p_sc) & mbar_test_wait(b_done, p_done);
-        if (!__all_sync(0xffffffffu, ready)) {
-          ok = wait_bar(b_done, p_done, abort_flag);
-          if (!ok) break;
-          ok = wait_bar(b_sc, p_sc, abort_flag);
-          if (!ok) break;
-        }
+        // (the MMA thread waited for this group's scale stage before it issued the group)
+        ok = wait_bar(bar_done + (flush % C::NI) * 8, (flush / C::NI) & 1u, abort_flag);
+        if (!ok) break;
         tc_fence_after_sync();
         if (PIPE) tmem_ld_16x256b_x4(taddr, rb[0]);
       }
@@ -434,8 +427,7 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
           pre = false;
           if (g + 1 < ti.g1) {
             const uint32_t nf = flush + 1;
-            const bool ready = mbar_test_wait(bar_done + (nf % C::NI) * 8, (nf / C::NI) & 1u) &
-                               mbar_test_wait(bar_sc_full + (nf % NS) * 8, (nf / NS) & 1u);
+            const bool ready = mbar_test_wait(bar_done + (nf % C::NI) * 8, (nf / C::NI) & 1u);
             if (__all_sync(0xffffffffu, ready)) {
               tc_fence_after_sync();
               if (PIPE) tmem_ld_16x256b_x4(tmem_base + ((uint32_t)(quad * 32) << 16) + (nf % C::NT) * BN + col_base, rb[0]);
@@ -714,6 +706,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
   const uint32_t bar_tm_empty = bar_tm_full + C::NT * 8;
   const uint32_t bar_sc_full = bar_tm_empty + C::NT * 8;
   const uint32_t bar_sc_empty = bar_sc_full + kNS * 8;
+  const uint32_t bar_sc_peer = bar_sc_empty + kNS * 8;   // leader only: the second CTA's scale stage has landed
   // where converters and epilogue warps arrive: the leader's barriers (shared::cluster addresses for CG = 2)
   const uint32_t arr_i8_full = (CG == 2) ? mapa_shared(bar_i8_full, 0) : bar_i8_full;
   const uint32_t arr_tm_empty = (CG == 2) ? mapa_shared(bar_tm_empty, 0) : bar_tm_empty;
@@ -725,7 +718,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     for (int i = 0; i < C::NI; ++i) { mbar_init(bar_i8_full + i * 8, kConvWarps * CG); mbar_init(bar_i8_empty + i * 8, 1); }
     for (int i = 0; i < C::NT; ++i) { mbar_init(bar_tm_full + i * 8, 1); mbar_init(bar_tm_empty + i * 8, EW * CG); }
     for (int i = 0; i < kNS; ++i) {
-      mbar_init(bar_sc_full + i * 8, 32); mbar_init(bar_sc_empty + i * 8, EW);
+      mbar_init(bar_sc_full + i * 8, 32); mbar_init(bar_sc_empty + i * 8, EW); mbar_init(bar_sc_peer + i * 8, 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -812,6 +805,7 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
     // pays a vote and a reconvergence (~250 cycles) per K group for nothing.
     if (leader && lane == 0) {
     constexpr uint32_t idesc = make_idesc<BN, CG>();
+    const uint32_t sc_ring = (p.zp != nullptr) ? kNS / 2 : kNS;   // scale stages in the ring (see epilogue_group)
     SchedT<CG> sched;
     TileInfo ti;
     uint32_t it = 0, flush = 0;
@@ -823,9 +817,16 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         const uint32_t buf = flush % C::NT;
         const uint32_t s = it % C::NI, ph = (it / C::NI) & 1u;
         const uint32_t b_tm = bar_tm_empty + buf * 8, p_tm = ((flush / C::NT) & 1u) ^ 1u;
-        // both probes back to back -- their latencies overlap -- and the one-at-a-time waits only if something is missing
+        // Per-group scales: this thread also waits for the group's scale stage (in a CTA pair: both CTAs' stages), so
+        // that "group done" vouches for the scales and the epilogue warps -- the busy ones in that mode -- wait once.
+        const bool need_sc = p.epi_mode == EPI_GROUP;
+        const uint32_t sc_slot = flush % sc_ring, p_sc = (flush / sc_ring) & 1u;
+        const uint32_t b_sc = bar_sc_full + sc_slot * 8, b_pe = bar_sc_peer + sc_slot * 8;
+        // all probes back to back -- their latencies overlap -- and the one-at-a-time waits only if something is missing
         bool ready = mbar_test_wait(bar_i8_full + s * 8, ph);
         if (first) ready &= mbar_test_wait(b_tm, p_tm);
+        if (need_sc) ready &= mbar_test_wait(b_sc, p_sc);
+        if (need_sc && CG == 2) ready &= mbar_test_wait(b_pe, p_sc);
         if (!ready) {
           if (first) {
             ok = wait_bar_thread(b_tm, p_tm, abort_flag);
@@ -833,6 +834,14 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
           }
           ok = wait_bar_thread(bar_i8_full + s * 8, ph, abort_flag);
           if (!ok) break;
+          if (need_sc) {
+            ok = wait_bar_thread(b_sc, p_sc, abort_flag);
+            if (!ok) break;
+            if (CG == 2) {
+              ok = wait_bar_thread(b_pe, p_sc, abort_flag);
+              if (!ok) break;
+            }
+          }
         }
         tc_fence_after_sync();
         {
@@ -859,6 +868,23 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
         if (last) ++flush;
       }
     }
+    } else if (!leader && CG == 2 && p.epi_mode == EPI_GROUP) {
+      // second CTA of a pair: this warp has no MMAs to issue; it tells the leader when a scale stage of this
+      // CTA has landed, so that the leader's "group done" vouches for both CTAs' scales
+      const uint32_t arr_sc_peer = mapa_shared(bar_sc_peer, 0);
+      const uint32_t sc_ring = (p.zp != nullptr) ? kNS / 2 : kNS;
+      SchedT<CG> sched;
+      TileInfo ti;
+      uint32_t it = 0;
+      bool ok = true;
+      while (ok && sched.template next<BN>(p, ti)) {
+        for (int g = ti.g0; g < ti.g1; ++g, ++it) {
+          ok = wait_bar(bar_sc_full + (it % sc_ring) * 8, (it / sc_ring) & 1u, abort_flag);
+          if (!ok) break;
+          if (lane == 0) mbar_arrive_cluster(arr_sc_peer + (it % sc_ring) * 8);
+          __syncwarp();
+        }
+      }
     }
     __syncwarp();   // the issuing thread rejoins its warp before the block-wide teardown
   } else if (p.epi_mode == EPI_GROUP) {

@@ -324,10 +324,13 @@ def test_config1_quantised_linear(tc, ops, M, shape):
     wc, wso = O.quant_grouped(w, 128, "weight")
     assert np.array_equal(xp.cpu().numpy(), O.pack_int4(xc))
     assert np.array_equal(wp.cpu().numpy(), O.pack_int4(wc))
-    ref = O.linear_grouped(xc, wc, xso, wso)
-    assert_close_bf16(out, ref, f"{shape} M={M}")
+    # every row up to 128 tokens; 48 sampled rows at M = 1024 (the oracle's exact fused multiply-add is slow)
+    rows = np.arange(M) if M <= 128 else np.sort(np.random.RandomState(M).choice(M, 48, replace=False))
+    ref = O.linear_grouped(xc[:, rows], wc, xso[:, rows], wso)
+    got = out[torch.from_numpy(rows).cuda()]
+    assert_close_bf16(got, ref, f"{shape} M={M}")
     if M > 128:
-        assert torch.equal(out.cpu(), ref)   # unsplit tensor-core path: the oracle's operations in the oracle's order
+        assert torch.equal(got.cpu(), ref)   # unsplit tensor-core path: the oracle's operations in the oracle's order
 
 
 @pytest.mark.parametrize("shape", ["qkv", "o", "gate_up", "down"])
