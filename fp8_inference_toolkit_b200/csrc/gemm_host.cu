@@ -24,17 +24,31 @@ static int epi_warps_for(int epi_mode) {
 struct Shape {
   int bn;
   bool swap;
+  bool pair;   // 256-row tiles on pairs of SMs (bn 256 or 192)
 };
 
-// Picks the tile width and operand orientation.  Up to 64 tokens the weights go on the 128-row side of
-// the MMA (so that no tensor-core rows are wasted on padding and more CTAs stream weights);
-// otherwise the width with the fewest (cost-weighted) waves over the SMs wins.
-static Shape choose_shape(long long M, long long N, int sms, bool allow_swap, bool group_mode) {
+// Picks the tile width, the operand orientation and whether pairs of SMs share 256-row tiles.  Up to 64 tokens the
+// weights go on the 128-row side of the MMA (so that no tensor-core rows are wasted on padding and more CTAs stream
+// weights); otherwise the candidate with the fewest cost-weighted waves wins.  Weights = measured time per output
+// column relative to 256-wide pair tiles at M = 8192 (per-group | per-channel epilogue): 192-wide pair tiles 1.10 | 1.30,
+// 256-wide single tiles 1.05 | 1.20, 128-wide single tiles 1.25 | 1.45.
+static Shape choose_shape(long long M, long long N, int sms, bool allow_swap, bool group_mode, bool pairs_allowed) {
   Shape s;
+  s.pair = false;
   s.swap = allow_swap && M <= 64;
   if (const int fs = g_force_swap.load(); fs >= 0 && allow_swap) s.swap = fs != 0;
+  const int force_pairs = g_cta_pairs.load();
   if (const int fb = g_force_bn.load()) {
     s.bn = fb;
+    // a forced width keeps the old rule for pairs: at least 512 rows and pair tiles that fill the machine about as
+    // well as single tiles would
+    if (!s.swap && pairs_allowed && (fb == 256 || fb == 192)) {
+      const long long t1 = ((M + 127) / 128) * ((N + fb - 1) / fb), t2 = ((M + 255) / 256) * ((N + fb - 1) / fb);
+      const int pairs = sms / 2;
+      const double eff1 = (double)t1 / (double)(((t1 + sms - 1) / sms) * sms);
+      const double eff2 = pairs > 0 ? (double)t2 / (double)(((t2 + pairs - 1) / pairs) * pairs) : 0.0;
+      s.pair = (M >= 512 && eff2 >= 0.9 * eff1 && force_pairs != 0) || force_pairs == 1 || fb == 192;
+    }
     return s;
   }
   if (s.swap) {
@@ -47,19 +61,22 @@ static Shape choose_shape(long long M, long long N, int sms, bool allow_swap, bo
     s.bn = N >= 16384 ? 256 : 128;
     return s;
   }
-  (void)group_mode;
-  const long long mt = (M + 127) / 128;
+  struct Cand { int bn; bool pair; double w_group, w_channel; };
+  const Cand cands[4] = {{256, true, 1.00, 1.00}, {192, true, 1.10, 1.30}, {256, false, 1.05, 1.20}, {128, false, 1.25, 1.45}};
   double best = 1e30;
   s.bn = 256;
-  const int cands[2] = {256, 128};
-  for (int c = 0; c < 2; ++c) {
-    const int bn = cands[c];
-    const long long tiles = mt * ((N + bn - 1) / bn);
-    const long long waves = (tiles + sms - 1) / sms;
-    const double cost = (double)waves * bn * (bn == 128 ? 1.2 : 1.0);   // 128-wide tiles: measured 15-20 % more time per column
+  for (const Cand& c : cands) {
+    if (c.pair && (!pairs_allowed || M < 512 || sms < 2 || force_pairs == 0)) continue;
+    if (!c.pair && force_pairs == 1 && pairs_allowed) continue;
+    const long long rows = c.pair ? (M + 255) / 256 : (M + 127) / 128;
+    const long long units = c.pair ? sms / 2 : sms;
+    const long long tiles = rows * ((N + c.bn - 1) / c.bn);
+    const long long waves = (tiles + units - 1) / units;
+    const double cost = (double)waves * c.bn * (group_mode ? c.w_group : c.w_channel);
     if (cost < best) {
       best = cost;
-      s.bn = bn;
+      s.bn = c.bn;
+      s.pair = c.pair;
     }
   }
   return s;
@@ -99,7 +116,9 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
                             info->sm_count, static_cast<cudaStream_t>(stream));
 
   const bool group_mode = d.epi_mode == EPI_GROUP || d.epi_mode == EPI_GROUP_INT32;
-  const Shape sh = choose_shape(d.M, d.N, info->sm_count, true, group_mode);
+  const bool pairs_allowed = (d.epi_mode == EPI_CHANNEL || d.epi_mode == EPI_GROUP) && g_pairs_launchable.load();
+  Shape sh = choose_shape(d.M, d.N, info->sm_count, true, group_mode, pairs_allowed);
+  I4TC_REQUIRE(sh.bn != 192 || sh.pair, I4TC_EINVAL, "192-wide tiles need a dense problem with scaled outputs (SM pairs)");
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.G = d.G;
@@ -166,21 +185,11 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
     }
   }
 
-  // CTA pairs (256 x 256 tiles on two SMs): each SM converts and stages a third less per unit of MMA work.
-  // Worth it once the 256-row tiles fill the SM pairs about as well as the 128-row tiles fill the SMs.
-  bool pair = false;
+  // CTA pairs (256-row tiles on two SMs): each SM converts and stages a third less per unit of MMA work
+  // (measured at M = 8192: +18-21 % with the one-flush per-channel epilogue, +4-5 % with the per-group one).
+  bool pair = sh.pair && !sh.swap && p.splits == 1 && info->sm_count >= 2;
   const int clusters_max = info->sm_count / 2;
   const long long pair_tiles = ((prow + 255) / 256) * p.num_q_tiles;
-  if (!sh.swap && sh.bn == 256 && p.splits == 1 && clusters_max > 0 &&
-      (d.epi_mode == EPI_CHANNEL || d.epi_mode == EPI_GROUP)) {
-    const double eff1 = (double)tiles / (double)(((tiles + info->sm_count - 1) / info->sm_count) * info->sm_count);
-    const double eff2 = (double)pair_tiles / (double)(((pair_tiles + clusters_max - 1) / clusters_max) * clusters_max);
-    // measured at M = 8192: +18-21 % with the one-flush per-channel epilogue, +4-5 % with the per-group one
-    pair = prow >= 512 && eff2 >= 0.9 * eff1;
-    if (g_cta_pairs == 0) pair = false;
-    if (g_cta_pairs == 1) pair = true;
-  }
-  if (pair && g_cta_pairs < 0 && !g_pairs_launchable) pair = false;
   CUtensorMap tmP, tmQ;
   const long long extent = d.rowmajor ? d.K / 2 : (long long)d.G;
   auto operand_map = [&](const uint8_t* base, long long rows, int box_rows, CUtensorMap* out) -> int {
@@ -189,7 +198,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   };
   if (int rc = operand_map(pbase, prow, 128, &tmP)) return rc;
   if (pair) {
-    if (int rc = operand_map(qbase, qrow, 128, &tmQ)) return rc;
+    if (int rc = operand_map(qbase, qrow, sh.bn / 2, &tmQ)) return rc;   // each CTA of a pair stages half of the Q tile
     GemmParams pp = p;
     pp.num_p_tiles = (int)((prow + 255) / 256);
     const int grid = 2 * (int)(pair_tiles < clusters_max ? pair_tiles : clusters_max);
@@ -200,9 +209,13 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
     // was refused before anything ran; remember it and use single thread blocks from now on
     cudaGetLastError();
     g_pairs_launchable = false;
+    if (sh.bn == 192) {   // that width exists on pairs only: fall back to 256-wide single tiles
+      sh.bn = 256;
+      p.num_q_tiles = (int)((qrow + sh.bn - 1) / sh.bn);
+    }
   }
   if (int rc = operand_map(qbase, qrow, sh.bn, &tmQ)) return rc;
-  const long long items = tiles * p.splits;
+  const long long items = (long long)p.num_p_tiles * p.num_q_tiles * p.splits;
   const int grid = (int)(items < info->sm_count ? items : info->sm_count);
   if (int rc = launch_w4a4_gemm(p, tmP, tmQ, sh.bn, grid, false, epi_warps_for(d.epi_mode), static_cast<cudaStream_t>(stream))) return rc;
   if (p.splits > 1) {
@@ -226,8 +239,8 @@ static int check_dense_common(const void* a, const void* b, const void* out, lon
 using namespace i4tc;
 
 extern "C" int i4tc_set_tuning(int tile_n, int swap) {
-  I4TC_REQUIRE(tile_n == 0 || tile_n == 64 || tile_n == 128 || tile_n == 256, I4TC_EINVAL,
-               "tile_n must be 0 (automatic), 64, 128 or 256");
+  I4TC_REQUIRE(tile_n == 0 || tile_n == 64 || tile_n == 128 || tile_n == 192 || tile_n == 256, I4TC_EINVAL,
+               "tile_n must be 0 (automatic), 64, 128, 192 (SM pairs only) or 256");
   I4TC_REQUIRE(swap >= -1 && swap <= 1, I4TC_EINVAL, "swap must be -1 (automatic), 0 or 1");
   g_force_bn = tile_n;
   g_force_swap = swap;

@@ -49,6 +49,8 @@ constexpr int kScaleWarp0 = 2, kScaleWarps = 2;
 template <int EW> struct Regs;
 template <> struct Regs<8> { static constexpr int WG0 = 56, CONV = 64, EPI = 192; static constexpr bool PIPE = false; };
 template <> struct Regs<16> { static constexpr int WG0 = 24, CONV = 40, EPI = 104; static constexpr bool PIPE = false; };
+//  12 epilogue warps, 640 threads x 96: 128*56 + 128*64 + 384*120 = 61440 (192-column tiles: 64 running sums per thread)
+template <> struct Regs<12> { static constexpr int WG0 = 56, CONV = 64, EPI = 120; static constexpr bool PIPE = false; };
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
 // CG = 1: one CTA computes a 128 x BN tile.  CG = 2: a pair of CTAs (a cluster of two SMs) computes a
@@ -58,16 +60,17 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 // four warps per scheduler hide what two cannot; 16 warps hold BN / 4 columns of running sums each.
 template <int BN, int CG = 1, int EW = 8>
 struct Cfg {
-  static_assert(EW == 8 || EW == 16, "8 or 16 epilogue warps");
+  static_assert(EW == 8 || EW == 12 || EW == 16, "8, 12 or 16 epilogue warps");
+  static_assert(BN % (EW / 4) == 0 && (BN / (EW / 4)) % 32 == 0, "every epilogue warp drains whole 32-column chunks");
   static_assert(BN / (EW / 4) >= 32, "an epilogue warp drains at least one 32-column chunk");
   static constexpr int EPI_WARPS = EW;
   static constexpr int THREADS = (kEpiWarp0 + EW) * 32;
   static constexpr int QR = BN / CG;                                   // Q rows staged by this CTA
   static constexpr int NP = (CG == 2) ? 4 : ((BN >= 128) ? 5 : 6);     // packed stages
-  static constexpr int NI = (CG == 2) ? 4 : (BN >= 256 ? 2 : 4);       // int8 stages
+  static constexpr int NI = (CG == 2) ? 4 : (BN >= 192 ? 2 : 4);       // int8 stages
   // TMEM accumulators: as many as fit in the 512 columns (at most 4), so that narrow tiles -- whose K loop is a
   // chain of short handshakes -- find a free accumulator and a converted stage without waiting
-  static constexpr int NT = (BN >= 256) ? 2 : 4;
+  static constexpr int NT = (BN >= 192) ? 2 : 4;
   // With a flush per group the epilogue waits on the barrier ring of the int8 stages.  Group j + NI can only be
   // multiplied after group j + NI - NT was drained, so with NI >= NT a barrier never completes a second phase
   // before the epilogue has seen the first.
@@ -77,7 +80,7 @@ struct Cfg {
   static constexpr int I8_P = kBM * kI8Row;                            // 16 KB
   static constexpr int I8_Q = QR * kI8Row;
   static constexpr int COLS_PER_WARP = BN / (EW / 4);                  // epilogue columns per warp
-  static constexpr int TMEM_COLS = NT * BN;                            // 256 or 512: a power of two >= 32
+  static constexpr int TMEM_COLS = (NT * BN > 256) ? 512 : 256;        // allocation: a power of two >= 32
   // shared memory layout (offsets from a 1024-byte aligned base)
   static constexpr int OFF_I8 = 0;
   static constexpr int OFF_PK = OFF_I8 + NI * (I8_P + I8_Q);
@@ -1098,9 +1101,11 @@ int launch_w4a4_gemm(const GemmParams& p, const CUtensorMap& tmP, const CUtensor
                      bool cta_pair, int epi_warps, cudaStream_t st) {
   const bool wide = epi_warps == 16 && bn >= 128;   // 64-column tiles have only 8 x 32 columns to hand out
   if (cta_pair) {
-    I4TC_REQUIRE(bn == 256 && (grid % 2) == 0 && p.expert_offsets == nullptr && !p.swap && p.splits == 1 &&
+    I4TC_REQUIRE((bn == 256 || bn == 192) && (grid % 2) == 0 && p.expert_offsets == nullptr && !p.swap && p.splits == 1 &&
                      (p.epi_mode == EPI_CHANNEL || p.epi_mode == EPI_GROUP),
-                 I4TC_EINVAL, "CTA-pair launch needs a dense, unswapped 256-wide problem and an even grid");
+                 I4TC_EINVAL, "CTA-pair launch needs a dense, unswapped 192- or 256-wide problem and an even grid");
+    // 192-column tiles: three epilogue warps per scheduler, 64 running sums per thread
+    if (bn == 192) return launch_bn<192, 2, 12>(p, tmP, tmQ, grid, st);
     return wide ? launch_bn<256, 2, 16>(p, tmP, tmQ, grid, st) : launch_bn<256, 2, 8>(p, tmP, tmQ, grid, st);
   }
   switch (bn) {

@@ -425,3 +425,32 @@ def test_split_k_workspace_is_per_stream_and_never_moves(tc, ops):
     other = torch.cuda.Stream()
     with torch.cuda.stream(other):
         assert ops.workspace_bytes() == 0               # another stream: its own (not yet needed) workspace
+
+
+@pytest.mark.parametrize("M,N,G", [(700, 1000, 5), (1024, 1536, 8), (513, 192, 3)])
+def test_192_wide_tiles_on_sm_pairs(tc, ops, M, N, G):
+    """192-column tiles (256 x 192 on a pair of SMs, twelve epilogue warps): per-group, zero-point and per-channel
+    outputs equal the oracle bit for bit, ragged edges included."""
+    rng = np.random.RandomState(M + N + G)
+    a, b = rand_codes(rng, (G, M, 128)), rand_codes(rng, (G, N, 128))
+    sa = (rng.rand(G, M).astype(np.float32) + 0.01) * 0.1
+    sb = (rng.rand(G, N).astype(np.float32) + 0.01) * 0.01
+    adj = rng.randint(-7, 9, size=(G, M)).astype(np.float32)
+    ap, bp = dev_packed(a), dev_packed(b)
+    ops.set_tuning(192, 0)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    tc.cutlass_int4_fused_grouped_gemm(ap, bp, dev_f32(sa), dev_f32(sb), out, M, N, 128, G)
+    ops.check_status()
+    assert torch.equal(out.cpu(), O.linear_grouped(a, b, sa, sb))
+    wcs = O.weight_group_sums(b)
+    out.fill_(float("nan"))
+    tc.cutlass_int4_fused_grouped_gemm_azp(ap, bp, dev_f32(sa), dev_f32(sb), out, dev_f32(adj), dev_f32(wcs), M, N, 128, G)
+    ops.check_status()
+    assert torch.equal(out.cpu(), O.to_bf16(O.linear_grouped_azp_f32(a, b, sa, sb, adj, wcs)))
+    K = G * 128
+    ar = a.transpose(1, 0, 2).reshape(M, K)
+    br = b.transpose(1, 0, 2).reshape(N, K)
+    out.fill_(float("nan"))
+    tc.cutlass_int4_scaled_mm(dev_packed(ar), dev_packed(br), dev_f32(sa[0]), dev_f32(sb[0]), out, M, N, K)
+    ops.check_status()
+    assert torch.equal(out.cpu(), O.linear_per_channel(ar, br, sa[0], sb[0]))
