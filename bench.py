@@ -505,7 +505,7 @@ def bench_sweep(dev, peaks) -> list:
     return out_rows
 
 
-def bench_moe(args, world, rank, dev, peaks, weak: bool = False) -> dict:
+def bench_moe(args, world, rank, dev, peaks, weak: bool = False, tokens: int = 4096) -> dict:
     """MoE grouped W4A4 layer (BASELINE configs[3]): 128 experts, top-8, 4096 tokens, hidden 2048,
     intermediate 768, group-128; experts and tokens split evenly across ranks, all-to-all dispatch and
     combine.  Timed from (token rows, expert ids, routing weights) to the combined bf16 output.
@@ -515,7 +515,7 @@ def bench_moe(args, world, rank, dev, peaks, weak: bool = False) -> dict:
 
     from fp8_inference_toolkit_b200 import moe, moe_ep, ops, synthetic
 
-    T, H, I, E, k = (4096 * world if weak else 4096), 2048, 768, 128, 8
+    T, H, I, E, k = (tokens * world if weak else tokens), 2048, 768, 128, 8
     t_loc, e_loc = T // world, E // world
     x, logits = synthetic.moe_inputs(T, H, E, k, seed=0)
     ids, w = moe.moe_route(logits.to(dev), k)
@@ -644,7 +644,9 @@ def bench_quant(dev, peaks, M: int = 16384, K: int = 12288, steps: int = 10) -> 
     from fp8_inference_toolkit_b200 import synthetic
 
     xs = [synthetic.activations(M, K, seed=i, outlier_frac=0.01, device=dev) for i in range(2)]
-    fns = {"row": lambda x: tc.dynamic_int4_quant(x), "group": lambda x: tc.dynamic_int4_quant_grouped(x, GROUP)}
+    fns = {"row": lambda x: tc.dynamic_int4_quant(x), "group": lambda x: tc.dynamic_int4_quant_grouped(x, GROUP),
+           "clipped": lambda x: tc.dynamic_int4_quant_clipped_grouped(x, GROUP, 0.95),
+           "asymmetric": lambda x: tc.dynamic_int4_quant_asymmetric_clipped_grouped(x, GROUP, 0.95, None)}
     res = {}
     for mode, fn in fns.items():
         for i in range(4):
@@ -657,7 +659,7 @@ def bench_quant(dev, peaks, M: int = 16384, K: int = 12288, steps: int = 10) -> 
             evs.append((e0, e1))
         torch.cuda.synchronize()
         us = statistics.mean(a.elapsed_time(b) for a, b in evs) * 1e3
-        byts = 2 * M * K + M * K // 2 + 4 * M * (1 if mode == "row" else K // GROUP)
+        byts = 2 * M * K + M * K // 2 + 4 * M * (1 if mode == "row" else K // GROUP) * (2 if mode == "asymmetric" else 1)
         res[mode] = {"us": us, "GBs": byts / us / 1e3, "frac": byts / us / 1e3 / peaks["hbm_gbs"], "bytes": byts}
     res["config"] = {"workload": f"BASELINE configs[2]: fused quantise+pack, bf16 [{M},{K}]", "bound": "hbm",
                      "peak_GBs": peaks["hbm_gbs"], "peak_source": f"copy bandwidth of MEASURED_PEAKS.json ({peaks['source']})"}
@@ -701,56 +703,31 @@ def bench_prefill(args, dev, steps: int = 2) -> dict:
 
 
 def run_quant(args) -> None:
-    """BASELINE configs[2]: fused activation quantise+pack, bf16 [M, K] with 1 % outlier channels x20,
-    per-token and per-group-128 scales.  One step = both variants over the same input; HBM-bound."""
-    import int4_native_tc as tc
-    from fp8_inference_toolkit_b200 import synthetic
-
+    """BASELINE configs[2] alone: fused activation quantise+pack of bf16 [M, K] (1 % outlier channels x20), per-token,
+    per-group-128, clipped and asymmetric variants; HBM-bound.  One JSON line."""
     torch.cuda.set_device(0)
-    M, K = args.m, args.k
     peaks = load_peaks()
-    xs = [synthetic.activations(M, K, seed=i, outlier_frac=0.01, device="cuda") for i in range(2)]
-    ev = {"row": [], "group": []}
-
-    def step(timed):
-        for i, x in enumerate(xs):
-            for mode in ("row", "group"):
-                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-                e0.record()
-                if mode == "row":
-                    tc.dynamic_int4_quant(x)
-                else:
-                    tc.dynamic_int4_quant_grouped(x, GROUP)
-                e1.record()
-                if timed:
-                    ev[mode].append((e0, e1))
-
-    for _ in range(max(args.warmup, 3)):
-        step(False)
-    torch.cuda.synchronize()
-    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        step(True)
-    t1.record()
-    torch.cuda.synchronize()
-    ms = t0.elapsed_time(t1) / args.steps
-    res = {}
-    for mode, gs in (("row", 1), ("group", K // GROUP)):
-        byts = 2 * M * K + M * K // 2 + 4 * M * gs
-        us = statistics.mean(a.elapsed_time(b) for a, b in ev[mode]) * 1e3
-        res[mode] = {"us": us, "GBs": byts / us / 1e3, "frac": byts / us / 1e3 / peaks["hbm_gbs"], "bytes": byts}
-    tot_bytes = 2 * (res["row"]["bytes"] + res["group"]["bytes"])
+    res = bench_quant(torch.device("cuda", 0), peaks, args.m, args.k, max(args.steps, 3))
+    tot = sum(res[m]["bytes"] for m in ("row", "group")) / ((res["row"]["us"] + res["group"]["us"]) * 1e-6) / 1e9
     emit({
-        "metric": "int4_quant_pack_gbs", "value": tot_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-        "dtype": "f32 on bf16 -> s4", "data": "synthetic",
-        "config": {"workload": f"BASELINE configs[2]: fused quantise+pack, bf16 [{M},{K}], per-token and per-group-128",
-                   "l2": "two input copies of %d MB alternate" % (2 * M * K // 2 ** 20)},
+        "metric": "int4_quant_pack_gbs", "value": tot, "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 3),
+        "warmup": 4, "ms_per_step": (res["row"]["us"] + res["group"]["us"]) * 1e-3, "higher_is_better": True,
+        "dtype": "f32 on bf16 -> s4", "data": "synthetic", "config": res["config"],
         "roofline": {"bound": "hbm", "achieved": res["group"]["GBs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": res["group"]["frac"], "traffic": None, "kernel": "quant_grouped_kernel",
-                     "per_kernel": res},
+                     "per_kernel": {k: v for k, v in res.items() if k != "config"}},
     })
+
+
+def run_moe(args) -> None:
+    """BASELINE configs[3] on one GPU with --tokens tokens (4096 by default; a small count gives a case for ncu)."""
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    peaks = load_peaks()
+    res = bench_moe(args, 1, 0, dev, peaks, tokens=args.tokens)
+    emit({"metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": 1, "steps": max(args.steps, 10),
+          "warmup": 5, "ms_per_step": res["ms_per_layer"], "higher_is_better": True, "dtype": "s4*s4->s32, f32 dequant",
+          "data": "synthetic", "config": res["config"], "roofline": res["roofline"]})
 
 
 def run_prefill(args) -> None:
@@ -796,9 +773,10 @@ def run_prefill(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="linear", choices=["linear", "quant", "prefill"],
-                    help="linear: the headline W4A4 linears (default); quant: quantise+pack only; "
-                         "prefill: Qwen3-8B-shaped prefill")
+    ap.add_argument("--workload", default="linear", choices=["linear", "quant", "prefill", "moe"],
+                    help="linear: the headline W4A4 linears (default; its line also carries the other workloads); "
+                         "quant: quantise+pack only; prefill: Qwen3-8B-shaped prefill; moe: the MoE layer on one GPU")
+    ap.add_argument("--tokens", type=int, default=4096, help="tokens of the MoE layer for --workload moe")
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--seq", type=int, default=512)
@@ -823,6 +801,8 @@ def main() -> None:
         run_quant(args)
     elif args.workload == "prefill":
         run_prefill(args)
+    elif args.workload == "moe":
+        run_moe(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
