@@ -325,12 +325,23 @@ def cutlass_int4_fused_grouped_gemm(a_packed, b_packed, scale_a, scale_b, out, M
                                 _dev(out), _stream(out)), "cutlass_int4_fused_grouped_gemm")
 
 
-# Same contract, different kernels in the reference (int4_gemm.cu:3751, 4073, 4007, 3932, 929).
+# Same contract, different kernels in the reference (int4_gemm.cu:3751, 4073, 4007, 3932).
 cutlass_int4_fused_grouped_gemm_v5 = cutlass_int4_fused_grouped_gemm
 cutlass_int4_fused_grouped_gemm_v7 = cutlass_int4_fused_grouped_gemm
 cutlass_int4_fused_grouped_gemm_v8 = cutlass_int4_fused_grouped_gemm
 cutlass_int4_fused_grouped_gemm_v9 = cutlass_int4_fused_grouped_gemm
-cutlass_int4_scaled_mm_grouped = cutlass_int4_fused_grouped_gemm
+
+
+def cutlass_int4_scaled_mm_grouped(a_packed, b_packed, scale_a, scale_b, out, M: int, N: int, group_size: int,
+                                   num_groups: int) -> None:
+    """The reference's per-group loop of scaled GEMMs (``int4_gemm.cu:929-992``), served here by the fused kernel:
+    a narrower contract -- ``group_size`` 128 and bf16 output only, and no rounding of each group's product to the
+    output type before the fp32 accumulation (the reference's loop accepts any multiple of 64 and fp16)."""
+    _require(group_size == 128, "cutlass_int4_scaled_mm_grouped: this build serves group_size=128 only "
+                                f"(got {group_size}; the reference accepts any multiple of 64)")
+    _require(out.dtype == torch.bfloat16, "cutlass_int4_scaled_mm_grouped: this build writes bfloat16 only "
+                                         f"(got {out.dtype}; the reference also accepts float16)")
+    cutlass_int4_fused_grouped_gemm(a_packed, b_packed, scale_a, scale_b, out, M, N, group_size, num_groups)
 
 
 def cutlass_int4_fused_grouped_gemm_azp(a_packed, b_packed, scale_a, scale_b, out, azp_adj, w_col_sum, M: int,
@@ -355,10 +366,21 @@ def cutlass_int4_fused_grouped_gemm_azp(a_packed, b_packed, scale_a, scale_b, ou
           "cutlass_int4_fused_grouped_gemm_azp")
 
 
-# Same contract, different kernels in the reference (int4_gemm.cu:3838, 4149, 994).
+# Same contract, different kernels in the reference (int4_gemm.cu:3838, 4149).
 cutlass_int4_fused_grouped_gemm_v5_azp = cutlass_int4_fused_grouped_gemm_azp
 cutlass_int4_fused_grouped_gemm_v7_azp = cutlass_int4_fused_grouped_gemm_azp
-cutlass_int4_scaled_mm_azp_grouped = cutlass_int4_fused_grouped_gemm_azp
+
+
+def cutlass_int4_scaled_mm_azp_grouped(a_packed, b_packed, scale_a, scale_b, out, azp_adj, w_col_sum, M: int, N: int,
+                                       group_size: int, num_groups: int) -> None:
+    """The reference's per-group loop with the zero-point term (``int4_gemm.cu:994-1000``), served by the fused
+    kernel under the same narrower contract as ``cutlass_int4_scaled_mm_grouped``."""
+    _require(group_size == 128, "cutlass_int4_scaled_mm_azp_grouped: this build serves group_size=128 only "
+                                f"(got {group_size}; the reference accepts any multiple of 64)")
+    _require(out.dtype == torch.bfloat16, "cutlass_int4_scaled_mm_azp_grouped: this build writes bfloat16 only "
+                                         f"(got {out.dtype}; the reference also accepts float16)")
+    cutlass_int4_fused_grouped_gemm_azp(a_packed, b_packed, scale_a, scale_b, out, azp_adj, w_col_sum, M, N, group_size,
+                                        num_groups)
 
 
 def int4_grouped_partials(a_packed, b_packed, M: int, N: int, num_groups: int) -> torch.Tensor:
