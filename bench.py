@@ -596,7 +596,7 @@ def bench_moe(args, world, rank, dev, peaks, weak: bool = False, tokens: int = 4
 def moe_roofline(moe, x, ids, w, mw, ms_layer, ops_layer, peaks) -> dict:
     """Single-GPU MoE layer stage by stage (CUDA events around each launch group, mean of 10 passes)."""
     T, k = ids.shape
-    names = ["sort", "gather_quant", "gemm_gate_up", "silu_quant", "gemm_down", "combine"]
+    names = ["sort", "quant_gather", "gemm_gate_up", "silu_quant", "gemm_down", "combine"]
     acc = {n: 0.0 for n in names}
     reps = 10
     for it in range(reps + 2):
@@ -604,7 +604,7 @@ def moe_roofline(moe, x, ids, w, mw, ms_layer, ops_layer, peaks) -> dict:
         ev[0].record()
         sp, inv, off = moe.moe_sort_tokens(ids, mw.num_experts)
         ev[1].record()
-        ap, asc = moe.moe_gather_quant(x, sp, k)
+        ap, asc = moe.moe_quant_gather(x, sp, k)
         ev[2].record()
         P = asc.shape[1]
         h = torch.empty((P, 2 * mw.inter), dtype=torch.bfloat16, device=x.device)

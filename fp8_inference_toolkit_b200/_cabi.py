@@ -58,6 +58,7 @@ SIGNATURES = {
     "i4tc_moe_ep_unpack": (_i, [_p, _l, _l, _l, _l, _l, _p, _p, _p, _p, _p, _p, _i, _p]),
     "i4tc_moe_silu_mul_quant_rows": (_i, [_p, _l, _p, _l, _p, _p, _i, _p]),
     "i4tc_moe_ep_pack_return": (_i, [_p, _p, _l, _l, _p, _p, _p, _l, _l, _l, _i, _p]),
+    "i4tc_moe_gather_packed": (_i, [_p, _p, _l, _l, _p, _l, _l, _p, _p, _p, _l, _p, _l, _l, _i, _p]),
     "i4tc_moe_gather_quant": (_i, [_p, _i, _l, _l, _l, _p, _l, _l, _p, _p, _i, _p]),
     "i4tc_moe_grouped_gemm": (_i, [_p, _p, _p, _p, _p, _p, _l, _l, _l, _l, _i, _p]),
     "i4tc_moe_silu_mul_quant": (_i, [_p, _l, _l, _p, _p, _i, _p]),

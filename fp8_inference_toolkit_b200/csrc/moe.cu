@@ -2,12 +2,14 @@
 // weighted combine of expert outputs.  The reference has no MoE path; these feed the grouped-tile
 // W4A4 GEMM, which walks the sorted rows expert by expert.
 //
-// Sort = three small launches over chunks of 1024 pairs:
+// Up to one chunk per SM the three steps below run as ONE cooperative launch (a grid-wide barrier between counting
+// and placing: every block is resident by construction of a cooperative launch); larger inputs use three launches:
 //   1. per-chunk histogram                    -> scratch counts [chunks, E]
 //   2. scan over chunks and experts           -> scratch bases  [chunks, E], expert_offsets [E+1]
 //   3. stable rank inside the chunk + scatter -> sorted_pairs, inv_pairs
 // The scratch ([chunks, E] int32) is caller-provided global memory.
 #include "common.cuh"
+#include <cooperative_groups.h>
 #include <mutex>
 
 namespace i4tc {
@@ -128,6 +130,85 @@ __global__ void __launch_bounds__(kSortChunk) moe_scatter_kernel(const int32_t* 
   } else if (in && inv_pairs) {
     inv_pairs[i] = -1;
   }
+}
+
+// The whole sort in one cooperative launch (chunks <= co-resident blocks): count, grid barrier, then every block forms
+// the expert offsets and its own bases from the [chunks, E] histogram and places its pairs.  Same outputs as the
+// three-launch form, including the -1 tail of sorted_pairs.
+__global__ void __launch_bounds__(kSortChunk) moe_sort_fused_kernel(const int32_t* __restrict__ ids, int P, int E,
+                                                                   int32_t* __restrict__ counts,
+                                                                   int32_t* __restrict__ expert_offsets,
+                                                                   int32_t* __restrict__ sorted_pairs,
+                                                                   int32_t* __restrict__ inv_pairs) {
+  __shared__ int s_cnt[32][kMaxExperts];
+  __shared__ int s_base[kMaxExperts];
+  __shared__ int s_warp[kMaxExperts / 32];
+  __shared__ int s_total;
+  const int chunks = gridDim.x;
+  const int i = blockIdx.x * kSortChunk + threadIdx.x;
+  const bool in = i < P;
+  const int e = in ? ids[i] : 0;
+  const bool valid = in && e >= 0 && e < E;
+  int rank, total;
+  chunk_rank(e, valid, E, s_cnt, rank, total);
+  if ((int)threadIdx.x < E) counts[(long long)blockIdx.x * E + threadIdx.x] = total;
+  __threadfence();
+  cooperative_groups::this_grid().sync();
+  const int t = threadIdx.x;
+  if (t < kMaxExperts) {
+    int tot = 0, before = 0;
+    if (t < E) {
+      for (int c0 = 0; c0 < chunks; c0 += 8) {
+        int v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (c0 + j < chunks) ? __ldcg(counts + (long long)(c0 + j) * E + t) : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          tot += v[j];
+          if (c0 + j < (int)blockIdx.x) before += v[j];
+        }
+      }
+    }
+    const int lane = t & 31, warp = t >> 5;
+    int incl = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += u;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    // the first kMaxExperts threads are whole warps, so the block barrier below is reached by everyone
+    s_base[t] = incl - tot + before;   // completed after the barrier with the totals of the earlier warps
+  }
+  __syncthreads();
+  if (t < kMaxExperts) {
+    const int warp = t >> 5;
+    int warp_base = 0;
+#pragma unroll
+    for (int w = 0; w < kMaxExperts / 32; ++w) warp_base += (w < warp) ? s_warp[w] : 0;
+    const int off = s_base[t] - 0 + warp_base;   // expert offset + rows of earlier chunks
+    s_base[t] = off;
+    if (blockIdx.x == 0 && t < E) {
+      expert_offsets[t] = off;   // block 0 has no earlier chunks: its bases are the offsets themselves
+    }
+    if (t == kMaxExperts - 1) {
+      int all = 0;
+#pragma unroll
+      for (int w = 0; w < kMaxExperts / 32; ++w) all += s_warp[w];
+      s_total = all;
+      if (blockIdx.x == 0) expert_offsets[E] = all;
+    }
+  }
+  __syncthreads();
+  if (valid) {
+    const int pos = s_base[e] + rank;
+    sorted_pairs[pos] = i;
+    if (inv_pairs) inv_pairs[i] = pos;
+  } else if (in && inv_pairs) {
+    inv_pairs[i] = -1;
+  }
+  // the tail that left-out pairs would have filled
+  for (int j = s_total + blockIdx.x * kSortChunk + threadIdx.x; j < P; j += chunks * kSortChunk) sorted_pairs[j] = -1;
 }
 
 // out[t, :] = bf16( sum_j w[t, j] * y[inv[t*k + j], :] ), fp32 accumulation in ascending j, one fused multiply-add
@@ -331,6 +412,53 @@ __global__ void __launch_bounds__(256) moe_ep_pack_return_kernel(const __nv_bflo
   }
 }
 
+// Rows that were quantised once per token, copied to where each (token, slot) pair needs them.  One warp per output
+// row r: source token = pairs[r] / top_k (nothing is copied for a negative or out-of-range pair index, or beyond
+// *rows_dev).  Source layout: group-major [G, T, 64] codes and [G, T] scales.  Destination: group-major [G, R, 64] / [G, R]
+// (row_map == nullptr), or rows of G x 64 code bytes followed by G scales (row_bytes = 68 G) at row row_map[r] of a
+// block buffer -- a local one, or with peer_bases the block `my_block` of the buffer of the rank that owns block
+// row_map[r] / block_rows (plain stores over NVLink).
+__global__ void __launch_bounds__(256) moe_gather_packed_kernel(const uint8_t* __restrict__ src_codes,
+                                                               const float* __restrict__ src_scale, long long T, int G,
+                                                               const int32_t* __restrict__ pairs, int top_k, long long R,
+                                                               uint8_t* __restrict__ dst_codes, float* __restrict__ dst_scale,
+                                                               const int32_t* __restrict__ row_map, long long row_bytes,
+                                                               const unsigned long long* __restrict__ peer_bases,
+                                                               int block_rows, int my_block) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long r = (long long)blockIdx.x * 8 + warp;
+  if (r >= R) return;
+  const int pair = pairs[r];
+  if (pair < 0) return;
+  const long long t = pair / top_k;
+  if (t >= T) return;
+  if (row_map == nullptr) {
+    for (int c = lane; c < G * 4; c += 32) {
+      const int g = c >> 2, q = c & 3;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src_codes + ((long long)g * T + t) * 64 + q * 16));
+      *reinterpret_cast<uint4*>(dst_codes + ((long long)g * R + r) * 64 + q * 16) = v;
+    }
+    for (int g = lane; g < G; g += 32) dst_scale[(long long)g * R + r] = __ldg(src_scale + (long long)g * T + t);
+    return;
+  }
+  const long long m = row_map[r];
+  if (m < 0) return;
+  uint8_t* row;
+  if (peer_bases != nullptr) {
+    const long long blk = m / block_rows;
+    row = reinterpret_cast<uint8_t*>(peer_bases[blk]) + ((long long)my_block * block_rows + (m - blk * block_rows)) * row_bytes;
+  } else {
+    row = dst_codes + m * row_bytes;
+  }
+  for (int c = lane; c < G * 4; c += 32) {
+    const int g = c >> 2, q = c & 3;
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(src_codes + ((long long)g * T + t) * 64 + q * 16));
+    *reinterpret_cast<uint4*>(row + (long long)c * 16) = v;
+  }
+  float* srow = reinterpret_cast<float*>(row + (long long)G * 64);
+  for (int g = lane; g < G; g += 32) srow[g] = __ldg(src_scale + (long long)g * T + t);
+}
+
 // Cross-GPU completion flags.  A rank that has finished writing into its peers' buffers (all earlier work of its
 // stream) stores a growing epoch number into its slot of every peer's flag array; a rank that is about to read its
 // own buffer waits until every slot has reached the epoch.  The wait is bounded: after two seconds it sets bit 1 of
@@ -368,6 +496,19 @@ __global__ void peer_wait_kernel(const unsigned int* __restrict__ flags, int wor
 int moe_sort_launch(const int32_t* ids, int64_t P, int64_t E, int32_t* sorted_pairs, int32_t* inv_pairs,
                     int32_t* expert_offsets, int32_t* scratch, cudaStream_t st) {
   const int chunks = (int)((P + kSortChunk - 1) / kSortChunk);
+  int dev = 0, sms = 0, coop = 0;
+  I4TC_CUDA(cudaGetDevice(&dev));
+  I4TC_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  I4TC_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+  if (coop && chunks <= sms) {
+    int Pi = (int)P, Ei = (int)E;
+    void* args[] = {(void*)&ids, (void*)&Pi, (void*)&Ei, (void*)&scratch, (void*)&expert_offsets, (void*)&sorted_pairs,
+                    (void*)&inv_pairs};
+    const cudaError_t e = cudaLaunchCooperativeKernel((const void*)moe_sort_fused_kernel, dim3(chunks), dim3(kSortChunk), args,
+                                                      0, st);
+    if (e == cudaSuccess) return I4TC_OK;
+    cudaGetLastError();   // not launchable as one cooperative grid here (a partitioned GPU, for instance): three launches
+  }
   moe_hist_kernel<<<chunks, kSortChunk, 0, st>>>(ids, (int)P, (int)E, scratch);
   moe_scan_kernel<<<1, kMaxExperts, 0, st>>>(scratch, chunks, (int)E, expert_offsets, sorted_pairs, (int)P);
   moe_scatter_kernel<<<chunks, kSortChunk, 0, st>>>(ids, (int)P, (int)E, scratch, sorted_pairs, inv_pairs);
@@ -454,6 +595,7 @@ extern "C" int i4tc_moe_sort_noalloc_prepare(int device) {
   I4TC_CUDA(cudaFuncGetAttributes(&attr, moe_hist_kernel));
   I4TC_CUDA(cudaFuncGetAttributes(&attr, moe_scan_kernel));
   I4TC_CUDA(cudaFuncGetAttributes(&attr, moe_scatter_kernel));
+  I4TC_CUDA(cudaFuncGetAttributes(&attr, moe_sort_fused_kernel));
   return I4TC_OK;
 }
 
@@ -482,6 +624,31 @@ extern "C" int i4tc_moe_sort_noalloc(const int32_t* expert_ids, int64_t num_pair
   // Nothing in the scratch has to start at zero: the histogram pass writes every entry that the
   // scan and scatter passes of this call read, so the previous call's contents are never seen.
   return moe_sort_launch(expert_ids, num_pairs, num_experts, sorted_pairs, inv_pairs, expert_offsets, scratch, st);
+}
+
+extern "C" int i4tc_moe_gather_packed(const uint8_t* tok_packed, const float* tok_scale, int64_t num_tokens,
+                                      int64_t num_groups, const int32_t* pairs, int64_t num_pairs, int64_t top_k,
+                                      uint8_t* packed, float* scale, const int32_t* row_map, int64_t row_bytes,
+                                      const uint64_t* peer_bases, int64_t cap, int64_t my_rank, int device,
+                                      void* stream) {
+  I4TC_REQUIRE(num_tokens >= 0 && num_pairs >= 0 && num_groups > 0 && top_k > 0 && top_k < (1 << 20), I4TC_EINVAL, "bad sizes");
+  if (num_pairs == 0 || num_tokens == 0) return I4TC_OK;
+  I4TC_REQUIRE(tok_packed && tok_scale && pairs, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(aligned_to(tok_packed, 16), I4TC_EALIGN, "packed rows must be 16-byte aligned");
+  if (row_map == nullptr) {
+    I4TC_REQUIRE(packed && scale && aligned_to(packed, 16), I4TC_EINVAL, "group-major destination missing or misaligned");
+  } else {
+    I4TC_REQUIRE(row_bytes == num_groups * 68, I4TC_EINVAL, "a buffer row is 64 bytes of codes and one fp32 scale per group");
+    I4TC_REQUIRE((packed && aligned_to(packed, 16)) || peer_bases, I4TC_EINVAL, "buffer destination missing or misaligned");
+    I4TC_REQUIRE(peer_bases == nullptr || (cap > 0 && my_rank >= 0), I4TC_EINVAL, "peer destinations need cap and the rank");
+  }
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  moe_gather_packed_kernel<<<(unsigned)((num_pairs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      tok_packed, tok_scale, num_tokens, (int)num_groups, pairs, (int)top_k, num_pairs, packed, scale, row_map, row_bytes,
+      reinterpret_cast<const unsigned long long*>(peer_bases), (int)(1 + cap), (int)my_rank);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
 }
 
 extern "C" int i4tc_moe_ep_plan(const int32_t* expert_offsets, const int32_t* sorted_pairs, int64_t num_pairs,

@@ -61,6 +61,27 @@ def moe_gather_quant(x: torch.Tensor, sorted_pairs: torch.Tensor, top_k: int):
     return packed, scale
 
 
+def moe_quant_gather(x: torch.Tensor, sorted_pairs: torch.Tensor, top_k: int):
+    """The result of ``moe_gather_quant`` by quantising every token once and copying its packed row to each of its
+    (token, slot) pairs: the quantiser works on whole rows, so the codes and scales are the same, with ``top_k`` times
+    less arithmetic.  Rows of pairs the sort left out (index -1) are left unwritten: no later stage reads them."""
+    from .ops import dynamic_int4_quant_grouped
+
+    _require(x.is_cuda and x.dim() == 2 and x.is_contiguous() and x.dtype == torch.bfloat16,
+             "x must be a contiguous 2D bfloat16 CUDA tensor")
+    T, K = x.shape
+    _require(K % 128 == 0, "hidden size must be a multiple of 128")
+    G = K // 128
+    tp, ts = dynamic_int4_quant_grouped(x, 128)
+    P = sorted_pairs.numel()
+    packed = torch.empty((G, P, 64), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((G, P), dtype=torch.float32, device=x.device)
+    check(lib.i4tc_moe_gather_packed(tp.data_ptr(), ts.data_ptr(), T, G, sorted_pairs.data_ptr(), P, top_k,
+                                     packed.data_ptr(), scale.data_ptr(), None, 0, None, 0, 0, _dev(x), _stream(x)),
+          "moe_quant_gather")
+    return packed, scale
+
+
 def moe_w4a4_grouped_gemm(a_packed, scale_a, b_packed, scale_b, expert_offsets, out, N: int, num_groups: int,
                           num_experts: int) -> None:
     """out[r,:] = linear_grouped(a[:, r, :], W_e) for rows r of expert e (bf16 [P,N], caller-allocated).
@@ -147,6 +168,6 @@ def moe_layer(x: torch.Tensor, expert_ids: torch.Tensor, expert_w: torch.Tensor,
     """Single-GPU MoE layer.  ``x`` bf16 [T,H]; ``expert_ids`` i32 [T,k]; ``expert_w`` f32 [T,k] -> bf16 [T,H]."""
     T, top_k = expert_ids.shape
     sorted_pairs, inv_pairs, offsets = moe_sort_tokens(expert_ids, w.num_experts)
-    ap, asc = moe_gather_quant(x, sorted_pairs, top_k)
+    ap, asc = moe_quant_gather(x, sorted_pairs, top_k)
     y = moe_experts_forward(ap, asc, offsets, w)
     return moe_combine(y, inv_pairs, expert_w.contiguous(), T, top_k)

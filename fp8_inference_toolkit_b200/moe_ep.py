@@ -313,6 +313,8 @@ class ExpertParallelMoE:
         self.y = torch.zeros(R, H, dtype=bf16, device=dev)
         self.ret_send = torch.zeros(R, H, dtype=bf16, device=dev)
         self.ret_recv = torch.zeros(R, H, dtype=bf16, device=dev)
+        self.tok_packed = torch.empty(G, tokens_per_rank, 64, dtype=u8, device=dev)
+        self.tok_scale = torch.empty(G, tokens_per_rank, dtype=f32, device=dev)
         self.sorted_pairs = torch.empty(self.P, dtype=i32, device=dev)
         self.inv_pairs = torch.empty(self.P, dtype=i32, device=dev)
         self.offsets = torch.empty(num_experts + 1, dtype=i32, device=dev)
@@ -368,9 +370,12 @@ class ExpertParallelMoE:
         check(lib.i4tc_moe_ep_plan(self.offsets.data_ptr(), self.sorted_pairs.data_ptr(), self.P, self.E, self.world,
                                    self.cap, self.row_bytes, send, self.slot.data_ptr(), self.ret_row.data_ptr(),
                                    self.overflow.data_ptr(), bases, self.rank, d, st), "moe_ep_plan")
-        check(lib.i4tc_moe_ep_dispatch_quant(x.data_ptr(), self.T, self.H, x.stride(0), self.sorted_pairs.data_ptr(),
-                                             self.P, self.k, self.slot.data_ptr(), send, self.row_bytes, bases, self.cap,
-                                             self.rank, d, st), "moe_ep_dispatch_quant")
+        # every token is quantised once; its 68 bytes per group are then copied to the block row of each of its pairs
+        check(lib.i4tc_quant_grouped(x.data_ptr(), 0, self.T, self.H, x.stride(0), 128, self.tok_packed.data_ptr(),
+                                     self.tok_scale.data_ptr(), 0, d, st), "quant_grouped")
+        check(lib.i4tc_moe_gather_packed(self.tok_packed.data_ptr(), self.tok_scale.data_ptr(), self.T, self.G,
+                                         self.sorted_pairs.data_ptr(), self.P, self.k, send, None, self.slot.data_ptr(),
+                                         self.row_bytes, bases, self.cap, self.rank, d, st), "moe_gather_packed")
 
     def _signal(self, addrs):
         from ._cabi import check

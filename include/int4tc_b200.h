@@ -244,6 +244,18 @@ int i4tc_moe_gather_quant(const void* x, int dtype, int64_t num_tokens, int64_t 
                           const int32_t* sorted_pairs, int64_t num_pairs, int64_t top_k,
                           uint8_t* packed, float* scale, int device, void* stream);
 
+/* The same result from rows that were quantised once per token (i4tc_quant_grouped over x, group size 128:
+ * tok_packed [G, T, 64], tok_scale [G, T]) -- the quantiser works on whole rows, so quantising a token once and
+ * copying its 68 bytes per group to every (token, slot) pair gives the codes and scales of quantising after the
+ * gather, with top_k times less arithmetic.  Destination: group-major packed [G, P, 64] / scale [G, P] (row_map NULL),
+ * or, for the expert-parallel exchange, rows of row_bytes = 68 G bytes at row row_map[i] of a block buffer (`packed`,
+ * or with peer_bases the destination ranks' buffers as in i4tc_moe_ep_dispatch_quant).  Pair indices that are negative
+ * or name no token copy nothing. */
+int i4tc_moe_gather_packed(const uint8_t* tok_packed, const float* tok_scale, int64_t num_tokens,
+                           int64_t num_groups, const int32_t* pairs, int64_t num_pairs, int64_t top_k,
+                           uint8_t* packed, float* scale, const int32_t* row_map, int64_t row_bytes,
+                           const uint64_t* peer_bases, int64_t cap, int64_t my_rank, int device, void* stream);
+
 /* Grouped-tile W4A4 GEMM over expert-sorted rows:
  *   for rows r in [expert_offsets[e], expert_offsets[e+1]):  out[r, :] = linear_grouped(a[:, r, :], W_e)
  * a: [G, P, 64], scale_a [G, P]; b: [E, G, N, 64], scale_b [E, G, N]; out bf16 [P, N].

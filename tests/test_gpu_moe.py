@@ -62,6 +62,8 @@ def test_ids_outside_the_expert_range_are_left_out(moe, ops):
     assert (inv.cpu().numpy()[np.setdiff1d(np.arange(T * k), keep)] == -1).all()
     p, s = moe.moe_gather_quant(x.cuda(), sp, k)
     assert (p[:, n:].cpu().numpy() == 0).all()
+    p2, s2 = moe.moe_quant_gather(x.cuda(), sp, k)      # quantise once per token, copy packed rows: the same rows
+    assert torch.equal(p2[:, :n], p[:, :n]) and torch.equal(s2[:, :n], s[:, :n])
     mw = moe.MoEWeights.quantize(gu.cuda(), dn.cuda())
     out = moe.moe_layer(x.cuda(), ids.cuda(), w.cuda(), mw)
     ops.check_status()
@@ -95,10 +97,11 @@ def test_gather_quant_and_silu_quant(moe):
     T, H, k = 50, 512, 4
     x, _ = synthetic.moe_inputs(T, H, 8, k, seed=3)
     pairs = torch.from_numpy(np.random.RandomState(0).permutation(T * k).astype(np.int32))
-    p, s = moe.moe_gather_quant(x.cuda(), pairs.cuda(), k)
     codes, so = O.quant_grouped(x[(pairs // k).long()], 128, "activation")
-    assert np.array_equal(p.cpu().numpy(), O.pack_int4(codes))
-    assert np.array_equal(s.cpu().numpy(), so)
+    for fn in (moe.moe_gather_quant, moe.moe_quant_gather):
+        p, s = fn(x.cuda(), pairs.cuda(), k)
+        assert np.array_equal(p.cpu().numpy(), O.pack_int4(codes))
+        assert np.array_equal(s.cpu().numpy(), so)
     g = torch.Generator().manual_seed(1)
     h = (torch.randn(37, 512, generator=g) * 2).to(torch.bfloat16)
     h[0, :8] = torch.tensor([-30.0, -9.0, -8.0, 8.0, 9.0, 30.0, 0.0, -0.0]).to(torch.bfloat16)   # both branches of the kernel
