@@ -28,6 +28,7 @@ SIGNATURES = {
     "i4tc_set_split_k": (_i, [_i]),
     "i4tc_set_cta_pairs": (_i, [_i]),
     "i4tc_set_epilogue_warps": (_i, [_i]),
+    "i4tc_set_small_m_path": (_i, [_i]),
     "i4tc_reserve_workspace": (_i, [_i, _p, _l]),
     "i4tc_workspace_bytes": (_l, [_i, _p]),
     "i4tc_release_workspaces": (_i, [_i]),

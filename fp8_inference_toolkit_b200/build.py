@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libint4tc_b200.so")
-SOURCES = ["runtime.cu", "quant.cu", "quant_ext.cu", "gemm_kernel.cu", "gemm_host.cu", "gemv.cu", "moe.cu"]
+SOURCES = ["runtime.cu", "quant.cu", "quant_ext.cu", "gemm_kernel.cu", "gemm_host.cu", "gemv.cu", "skinny.cu", "moe.cu"]
 HEADERS = ["common.cuh", "gemm.cuh", "ptx.cuh", os.path.join("..", "..", "include", "int4tc_b200.h")]
 
 

@@ -77,6 +77,12 @@ int split_workspace(int device, cudaStream_t stream, size_t bytes, float** out);
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+// Vectorised clipped-symmetric / asymmetric per-group quantiser (quant.cu); the caller has validated the sizes and
+// holds the device.  grouped_ext_fast_ok: the pointers and the row stride allow its 128-bit accesses.
+bool grouped_ext_fast_ok(const void* x, int64_t ldx, const uint8_t* packed);
+int launch_grouped_ext(bool asym, const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx, int gs, float clip,
+                       uint8_t* packed, float* scale, float* azp_adj, cudaStream_t st);
+
 // ---- device helpers ------------------------------------------------------------
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }

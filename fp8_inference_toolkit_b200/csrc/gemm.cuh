@@ -75,6 +75,13 @@ bool gemv_applicable(long long M, long long N, long long K, int epi_mode);
 int launch_w4a4_gemv(const uint8_t* x, const uint8_t* w, const float* sx, const float* sw, void* out, int out_dtype,
                      long long M, long long N, int G, bool rowmajor, int epi_mode, int sm_count, cudaStream_t st);
 
+// Register-fed tensor-core weight-streaming kernel for M <= 32 tokens (same operands and outputs as the kernel above;
+// `status` is the device status word that a bounded wait flags).
+bool skinny_applicable(long long M, long long N, long long K, int epi_mode, int sm_count);
+int launch_w4a4_skinny(const uint8_t* x, const uint8_t* w, const float* sx, const float* sw, void* out, int out_dtype,
+                       long long M, long long N, int G, bool rowmajor, int epi_mode, int sm_count, unsigned int* status,
+                       cudaStream_t st);
+
 // Builds (or fetches from a small per-device cache) a tensor map over packed int4 data.
 // rowmajor: 2-D view [rows, row_bytes]; otherwise 3-D view [slabs, rows, 64].
 int get_tensor_map(int device, const void* base, bool rowmajor, long long rows, long long row_bytes_or_slabs,

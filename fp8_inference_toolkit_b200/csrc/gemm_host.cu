@@ -10,6 +10,7 @@ namespace i4tc {
 // reads every hook once, at its start).
 static std::atomic<int> g_force_bn{0};      // 0 = choose automatically
 static std::atomic<int> g_force_swap{-1};   // -1 = choose automatically
+static std::atomic<int> g_small_m_path{0};  // 0 = automatic, 1 = CUDA-core kernel only, 2 = register-fed tensor-core kernel whenever it applies, 3 = tile kernel only
 static std::atomic<int> g_force_splits{0};  // 0 = choose automatically, 1 = never split, n = n K ranges
 static std::atomic<int> g_cta_pairs{-1};    // -1 = choose automatically, 0 = never, 1 = whenever the problem allows it
 static std::atomic<bool> g_pairs_launchable{true};   // cleared when an automatic cluster launch was refused
@@ -109,11 +110,21 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   I4TC_CUDA(guard.err);
   I4TC_REQUIRE(d.M < (1ll << 31) - 256 && d.N < (1ll << 31) - 256, I4TC_EINVAL, "M or N too large");
 
-  // a handful of tokens: stream the weights through the CUDA cores instead (unless a test pins the tile shape)
+  // a few dozen tokens: stream the weights (unless a test pins the tile shape).  Up to 8 tokens the CUDA-core kernel,
+  // up to 32 the register-fed tensor-core one.
   if (g_force_bn == 0 && g_force_swap < 0 && g_force_splits == 0 && d.azp_adj == nullptr && !d.i8_operands &&
-      gemv_applicable(d.M, d.N, (long long)d.G * 128, d.epi_mode) && (!d.rowmajor || d.K == (long long)d.G * 128))
-    return launch_w4a4_gemv(d.a, d.b, d.sa, d.sb, d.out, d.out_dtype, d.M, d.N, d.G, d.rowmajor, d.epi_mode,
-                            info->sm_count, static_cast<cudaStream_t>(stream));
+      (!d.rowmajor || d.K == (long long)d.G * 128)) {
+    const int path = g_small_m_path.load();
+    const long long K = (long long)d.G * 128;
+    const bool gemv_ok = path != 3 && path != 2 && gemv_applicable(d.M, d.N, K, d.epi_mode);
+    const bool skinny_ok = path != 3 && path != 1 && skinny_applicable(d.M, d.N, K, d.epi_mode, info->sm_count);
+    if (skinny_ok && (path == 2 || !gemv_ok))
+      return launch_w4a4_skinny(d.a, d.b, d.sa, d.sb, d.out, d.out_dtype, d.M, d.N, d.G, d.rowmajor, d.epi_mode,
+                                info->sm_count, info->status, static_cast<cudaStream_t>(stream));
+    if (gemv_ok)
+      return launch_w4a4_gemv(d.a, d.b, d.sa, d.sb, d.out, d.out_dtype, d.M, d.N, d.G, d.rowmajor, d.epi_mode,
+                              info->sm_count, static_cast<cudaStream_t>(stream));
+  }
 
   const bool group_mode = d.epi_mode == EPI_GROUP || d.epi_mode == EPI_GROUP_INT32;
   const bool pairs_allowed = (d.epi_mode == EPI_CHANNEL || d.epi_mode == EPI_GROUP) && g_pairs_launchable.load();
@@ -256,6 +267,12 @@ extern "C" int i4tc_set_split_k(int splits) {
 extern "C" int i4tc_set_cta_pairs(int mode) {
   I4TC_REQUIRE(mode >= -1 && mode <= 1, I4TC_EINVAL, "mode must be -1 (automatic), 0 or 1");
   g_cta_pairs = mode;
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_set_small_m_path(int path) {
+  I4TC_REQUIRE(path >= 0 && path <= 3, I4TC_EINVAL, "path must be 0 (automatic), 1, 2 or 3");
+  g_small_m_path = path;
   return I4TC_OK;
 }
 

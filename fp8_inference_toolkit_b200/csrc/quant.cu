@@ -438,6 +438,199 @@ __global__ void __launch_bounds__(256) quant_grouped_kernel(
 }
 
 // ------------------------------------------------------------------------------------------
+// Clipped symmetric and asymmetric per-group quantisers on the layout of the grouped kernel above (a lane owns 32
+// consecutive elements, a group is LPG adjacent lanes, 128-bit loads and stores, next segment loaded while this one is
+// quantised).  Arithmetic per group, IEEE fp32:
+//   t = max|x| * clip
+//   symmetric:  s = t / 7;  code = clamp(rint(x / s), -8, 7), 0 when s == 0;  scale = max(s, 1/(7*512))
+//   asymmetric: c = clamp(x, -t, t);  s = max((max c - min c) / 15, 1/(7*512));  azp = clamp(rint(-min c / s), 0, 15);
+//               u = clamp(rint(c / s + azp), 0, 15);  stored nibble = u - 8;  azp_adj = 8 - azp
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void minmax_of(const Vec8<T> (&v)[kQVecs], float& mn, float& mx) {
+  mn = INFINITY;
+  mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kQVecs; ++j) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      mn = fminf(mn, v[j].v[i]);
+      mx = fmaxf(mx, v[j].v[i]);
+    }
+  }
+}
+template <>
+__device__ __forceinline__ void minmax_of<__nv_bfloat16>(const Vec8<__nv_bfloat16> (&v)[kQVecs], float& mn, float& mx) {
+  // min and max of packed bf16 halves are exact
+  __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&v[0].w[0]), hi = lo;
+#pragma unroll
+  for (int j = 0; j < kQVecs; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&v[j].w[i]);
+      lo = __hmin2(lo, h);
+      hi = __hmax2(hi, h);
+    }
+  }
+  const uint32_t bl = *reinterpret_cast<const uint32_t*>(&lo), bh = *reinterpret_cast<const uint32_t*>(&hi);
+  mn = fminf(__uint_as_float(bl << 16), __uint_as_float(bl & 0xFFFF0000u));
+  mx = fmaxf(__uint_as_float(bh << 16), __uint_as_float(bh & 0xFFFF0000u));
+}
+
+// Parameters of one asymmetric group, the same in all its lanes.
+struct AsymGroup {
+  float thr, s, r, azp;   // clip range, step, ~1/step, zero point
+  float ylo, yhi;         // images of -thr / +thr under y = c * r + azp, intersected with [0, 15]
+  bool fast;
+};
+
+// Eight unsigned codes u (stored as u - 8).  Fast path: y = x * r + azp in one FMA.  The FMA is monotone in x, so
+// clamping y to [y(-thr), y(thr)] equals clamping x first; intersected with [0, 15] that is one clamp per element.
+// For |c / s| < 64 the FMA lies within 2e-5 of RN(RN(c / s) + azp), so outside 1e-4 of a rounding boundary both round to
+// the same integer; for |c / s| >= 64 both saturate on the same side.  Elements inside the window take the IEEE
+// division.
+template <typename T>
+__device__ __forceinline__ uint32_t pack8_asym(const Vec8<T>& x, const AsymGroup& q) {
+  constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+  constexpr float kThr = 0.5f - 1e-4f;
+  const float2 r2 = make_float2(q.r, q.r), az = make_float2(q.azp, q.azp), mg = make_float2(kMagic, kMagic);
+  const float2 nmg = make_float2(-kMagic, -kMagic);
+  float2 v[4], y[4];
+  float worst = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    y[i] = __ffma2_rn(make_float2(x.get(i), x.get(i + 4)), r2, az);
+    y[i].x = fminf(fmaxf(y[i].x, q.ylo), q.yhi);
+    y[i].y = fminf(fmaxf(y[i].y, q.ylo), q.yhi);
+    v[i] = __fadd2_rn(__fadd2_rn(y[i], mg), nmg);
+    const float2 e = __ffma2_rn(v[i], make_float2(-1.f, -1.f), y[i]);
+    worst = fmaxf(worst, fmaxf(fabsf(e.x), fabsf(e.y)));
+  }
+  if (!q.fast || !(worst <= kThr)) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (!q.fast || !(fabsf(y[i].x - v[i].x) <= kThr)) {
+        const float c = fminf(fmaxf(x.get(i), -q.thr), q.thr);
+        v[i].x = fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(c, q.s), q.azp)), 0.0f), 15.0f);
+      }
+      if (!q.fast || !(fabsf(y[i].y - v[i].y) <= kThr)) {
+        const float c = fminf(fmaxf(x.get(i + 4), -q.thr), q.thr);
+        v[i].y = fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(c, q.s), q.azp)), 0.0f), 15.0f);
+      }
+    }
+  }
+  float2 lh = __ffma2_rn(v[3], make_float2(4096.f, 4096.f),
+                         __ffma2_rn(v[2], make_float2(256.f, 256.f), __ffma2_rn(v[1], make_float2(16.f, 16.f), v[0])));
+  lh = __fadd2_rn(lh, mg);
+  const uint32_t wl = __float_as_uint(lh.x) & 0xFFFFu;
+  const uint32_t wh = __float_as_uint(lh.y) << 16;
+  return (wl | wh) ^ 0x88888888u;   // u - 8 as a two's-complement nibble is u ^ 8
+}
+
+template <typename T, int LPG, bool ASYM>
+__global__ void __launch_bounds__(256) quant_grouped_ext_kernel(const T* __restrict__ x, int64_t rows, int K,
+                                                                int64_t ldx, float clip, uint8_t* __restrict__ packed,
+                                                                float* __restrict__ scale,
+                                                                float* __restrict__ azp_adj, int segs_per_block) {
+  constexpr int GS = LPG * kQLane;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * kQRows + warp;
+  const bool row_ok = r < rows;
+  const int nseg = (K + kQSeg - 1) / kQSeg;
+  const int seg_begin = blockIdx.y * segs_per_block;
+  const int seg_end = min(nseg, seg_begin + segs_per_block);
+  const T* src = row_ok ? x + r * ldx : nullptr;
+  Vec8<T> cur[kQVecs], nxt[kQVecs];
+  load_segment<T, 0>(cur, src, seg_begin * kQSeg + lane * kQLane, K, row_ok);
+  for (int seg = seg_begin; seg < seg_end; ++seg) {
+    const int k = seg * kQSeg + lane * kQLane;
+    if (seg + 1 < seg_end) load_segment<T, 0>(nxt, src, k + kQSeg, K, row_ok);
+    const bool ok = row_ok && k < K;
+    const int g = k / GS;
+    float mn, mx;
+    minmax_of(cur, mn, mx);
+#pragma unroll
+    for (int o = 1; o < LPG; o <<= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    const float thr = __fmul_rn(fmaxf(-mn, mx), clip);
+    uint4 w;
+    if (ASYM) {
+      AsymGroup q;
+      q.thr = thr;
+      const float cmn = fminf(fmaxf(mn, -thr), thr), cmx = fminf(fmaxf(mx, -thr), thr);
+      q.s = fmaxf(__fdiv_rn(__fsub_rn(cmx, cmn), 15.0f), min_scale());
+      q.azp = fminf(fmaxf(rintf(__fdiv_rn(-cmn, q.s)), 0.0f), 15.0f);
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(q.r) : "f"(q.s));
+      q.fast = (q.r > 7.8886090522e-31f) && (q.r < 1.2676506002e30f);
+      q.ylo = fmaxf(fmaf(-thr, q.r, q.azp), 0.0f);
+      q.yhi = fminf(fmaf(thr, q.r, q.azp), 15.0f);
+      if (ok && (lane % LPG) == 0) {
+        scale[(int64_t)g * rows + r] = q.s;
+        azp_adj[(int64_t)g * rows + r] = 8.0f - q.azp;
+      }
+      w.x = pack8_asym<T>(cur[0], q);
+      w.y = pack8_asym<T>(cur[1], q);
+      w.z = pack8_asym<T>(cur[2], q);
+      w.w = pack8_asym<T>(cur[3], q);
+    } else {
+      const float s = __fdiv_rn(thr, 7.0f);
+      const bool zero = !(s > 0.0f);
+      const Recip q = make_recip<false>(zero ? 1.0f : s);
+      if (ok && (lane % LPG) == 0) scale[(int64_t)g * rows + r] = fmaxf(s, min_scale());
+      w.x = pack8<T, true>(cur[0], q, zero);
+      w.y = pack8<T, true>(cur[1], q, zero);
+      w.z = pack8<T, true>(cur[2], q, zero);
+      w.w = pack8<T, true>(cur[3], q, zero);
+    }
+    if (ok) *reinterpret_cast<uint4*>(packed + ((int64_t)g * rows + r) * (GS / 2) + (lane % LPG) * 16) = w;
+#pragma unroll
+    for (int j = 0; j < kQVecs; ++j) cur[j] = nxt[j];
+  }
+}
+
+template <typename T, bool ASYM>
+static int launch_grouped_ext_t(const T* x, int64_t rows, int64_t K, int64_t ldx, int gs, float clip, uint8_t* packed,
+                                float* scale, float* azp_adj, cudaStream_t st) {
+  const int64_t row_blocks = (rows + kQRows - 1) / kQRows;
+  const int nseg = (int)((K + kQSeg - 1) / kQSeg);
+  int spb = nseg;
+  if (row_blocks < 2048) spb = (int)((int64_t)nseg * row_blocks / 2048);
+  if (spb < 1) spb = 1;
+  dim3 grid((unsigned)row_blocks, (unsigned)((nseg + spb - 1) / spb));
+  I4TC_REQUIRE(grid.y <= 65535, I4TC_EINVAL, "K=%lld too large for the grouped quantiser", (long long)K);
+  switch (gs) {
+    case 64: quant_grouped_ext_kernel<T, 2, ASYM><<<grid, 256, 0, st>>>(x, rows, (int)K, ldx, clip, packed, scale, azp_adj, spb); break;
+    case 128: quant_grouped_ext_kernel<T, 4, ASYM><<<grid, 256, 0, st>>>(x, rows, (int)K, ldx, clip, packed, scale, azp_adj, spb); break;
+    case 256: quant_grouped_ext_kernel<T, 8, ASYM><<<grid, 256, 0, st>>>(x, rows, (int)K, ldx, clip, packed, scale, azp_adj, spb); break;
+    default: return fail(I4TC_EUNSUPPORTED, "group_size=%d not supported (64, 128 or 256)", gs);
+  }
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+// Whether the vectorised kernel can take this call: 16-byte aligned rows and outputs (it moves 128 bits per lane).
+bool grouped_ext_fast_ok(const void* x, int64_t ldx, const uint8_t* packed) {
+  return aligned_to(x, 16) && (ldx * 2) % 16 == 0 && aligned_to(packed, 16);
+}
+
+int launch_grouped_ext(bool asym, const void* x, int dtype, int64_t rows, int64_t K, int64_t ldx, int gs, float clip,
+                       uint8_t* packed, float* scale, float* azp_adj, cudaStream_t st) {
+  if (dtype == I4TC_BF16) {
+    const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(x);
+    return asym ? launch_grouped_ext_t<__nv_bfloat16, true>(p, rows, K, ldx, gs, clip, packed, scale, azp_adj, st)
+                : launch_grouped_ext_t<__nv_bfloat16, false>(p, rows, K, ldx, gs, clip, packed, scale, azp_adj, st);
+  }
+  if (dtype == I4TC_FP16) {
+    const __half* p = static_cast<const __half*>(x);
+    return asym ? launch_grouped_ext_t<__half, true>(p, rows, K, ldx, gs, clip, packed, scale, azp_adj, st)
+                : launch_grouped_ext_t<__half, false>(p, rows, K, ldx, gs, clip, packed, scale, azp_adj, st);
+  }
+  return fail(I4TC_EUNSUPPORTED, "input must be bf16 or fp16 (dtype %d)", dtype);
+}
+
+// ------------------------------------------------------------------------------------------
 // Row-wise kernel.  One 256-thread block per row; the row is cached in registers
 // (NCH chunks of 2048 elements, 8 per thread per chunk), so HBM is read once.
 // ------------------------------------------------------------------------------------------

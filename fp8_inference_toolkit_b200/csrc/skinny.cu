@@ -1,0 +1,312 @@
+// W4A4 linear for a few dozen tokens (M <= 32): weight streaming through register-fed tensor-core instructions.
+//
+// At these sizes the op moves half a byte per 2 M operations, far below the machine balance, so the only thing that
+// counts is how many weight bytes are in flight.  The tile kernel (TMA -> converter warps -> tcgen05 -> TMEM drain) is a
+// chain of per-group handshakes with a handful of stages per SM; here a thread block asks for ALL of its weight bytes
+// at once (cp.async.bulk, one mbarrier per warp and K group), several blocks share an SM, and nothing waits on
+// another role: a warp expands the nibbles of its K groups in registers, multiplies them with
+// mma.sync.m16n8k32 (int8, int32 accumulators in registers) against the tokens' codes read straight from
+// global memory / L2, and applies the group's scales in registers.
+//
+// A block covers ROWS = 16 or 32 weight rows and the whole K; its 8 warps split the K groups into contiguous ranges
+// and the ranges are added in ascending order through shared memory (int32 for per-channel scales: exact; fp32 for
+// per-group scales: a fixed order, so the result is deterministic).  No workspace and no second launch.
+//
+// Nibble arithmetic as in the other kernels: a nibble moved to the top of its byte is 16 x the code, so every int32
+// sum is exactly 256 x the true one and the factor leaves as 2^-8 on a scale.  The k order inside an MMA is
+// free as long as both operands agree: fragment register j of a lane holds the even (a0/a1/b0) or odd (a2/a3/b1)
+// codes of 32-bit word 4 t + j of the 64-byte group row, for weights and tokens alike.
+#include "gemm.cuh"
+#include "ptx.cuh"
+
+namespace i4tc {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kWarps = 8;
+constexpr int kMaxGroupsPerWarp = 16;
+constexpr uint64_t kSkinnyWaitNs = 2000000000ull;   // 2 s
+
+struct SkinnyParams {
+  const uint8_t* x;   // activations, packed
+  const uint8_t* w;   // weights, packed
+  const float* sx;    // per-group: [G, M]; per-channel: [M]
+  const float* sw;    // per-group: [G, N]; per-channel: [N]
+  void* out;          // [M, N]
+  int M, N, G;
+  int gper;           // K groups per warp
+  long long x_row, x_grp;   // byte strides of the activations: token, K group
+  long long w_row, w_grp;   // byte strides of the weights: row, K group
+  int rowmajor;
+  int out_fp16;
+  unsigned int* status;     // bit 0 is set when a bounded wait expires
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :: "r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void expand4(const uint4& w, uint32_t (&lo)[4], uint32_t (&hi)[4]) {
+  lo[0] = (w.x << 4) & 0xF0F0F0F0u; hi[0] = w.x & 0xF0F0F0F0u;
+  lo[1] = (w.y << 4) & 0xF0F0F0F0u; hi[1] = w.y & 0xF0F0F0F0u;
+  lo[2] = (w.z << 4) & 0xF0F0F0F0u; hi[2] = w.z & 0xF0F0F0F0u;
+  lo[3] = (w.w << 4) & 0xF0F0F0F0u; hi[3] = w.w & 0xF0F0F0F0u;
+}
+
+// Bounded wait for phase 0 of a barrier; on expiry bit 0 of the status word is set and false returned.
+__device__ __forceinline__ bool wait_landed(uint32_t bar, unsigned int* status) {
+  if (mbar_test_wait(bar, 0)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, 0)) return true;
+    if ((++spins & 63u) == 0 && globaltimer_ns() - t0 > kSkinnyWaitNs) {
+      atomicOr(status, 1u);
+      return false;
+    }
+  }
+}
+
+// MTILES: 16-row tiles per block (ROWS = 16 MTILES).  NT: 8-token tiles (M <= 8 NT).
+template <int MTILES, int NT, bool PER_GROUP>
+__global__ void __launch_bounds__(kWarps * 32) w4a4_skinny_kernel(const SkinnyParams p) {
+  constexpr int ROWS = 16 * MTILES;
+  constexpr int CHUNK = ROWS * 64;   // bytes of one K group of the block's rows
+  extern __shared__ __align__(128) uint8_t smem[];
+  // layout: weights [warp][group of the warp][ROWS][64] (later reused for the warps' partial sums) | barriers
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * ROWS;
+  const int g0 = min(p.G, warp * p.gper), g1 = min(p.G, g0 + p.gper), gw = g1 - g0;
+  const size_t w_bytes = (size_t)kWarps * p.gper * CHUNK;
+  const size_t red_bytes = (size_t)kWarps * (8 * NT) * ROWS * 4;
+  uint8_t* wsm = smem + (size_t)warp * p.gper * CHUNK;
+  const uint32_t bars = smem_u32(smem + (w_bytes > red_bytes ? w_bytes : red_bytes)) + (uint32_t)warp * kMaxGroupsPerWarp * 8u;
+
+  // ---- ask for every weight byte of this warp's K range ----
+  if (lane < gw) mbar_init(bars + lane * 8u, 1);
+  fence_mbar_init();
+  __syncwarp();
+  if (!p.rowmajor) {
+    // group-major weights: the block's rows of one group are contiguous
+    if (lane < gw) {
+      mbar_arrive_expect_tx(bars + lane * 8u, CHUNK);
+      bulk_load(smem_u32(wsm) + lane * CHUNK, p.w + (long long)(g0 + lane) * p.w_grp + (long long)n0 * 64, CHUNK,
+                bars + lane * 8u);
+    }
+  } else {
+    if (lane < gw) mbar_arrive_expect_tx(bars + lane * 8u, CHUNK);
+    __syncwarp();
+    for (int i = lane; i < gw * ROWS; i += 32) {
+      const int gi = i / ROWS, r = i - gi * ROWS;
+      bulk_load(smem_u32(wsm) + gi * CHUNK + r * 64, p.w + (long long)(n0 + r) * p.w_row + (long long)(g0 + gi) * 64, 64,
+                bars + gi * 8u);
+    }
+  }
+
+  // ---- token codes and scales of the first group (registers) ----
+  uint4 xb[NT];
+  float sxs[NT][2], sws[MTILES][2];
+  auto fetch = [&](int grp) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int tok = 8 * nt + g;
+      xb[nt] = make_uint4(0u, 0u, 0u, 0u);
+      if (tok < p.M) xb[nt] = __ldg(reinterpret_cast<const uint4*>(p.x + (long long)tok * p.x_row + (long long)grp * p.x_grp) + t);
+      if (PER_GROUP) {
+        const int t0 = 8 * nt + 2 * t;
+        sxs[nt][0] = t0 < p.M ? __ldg(p.sx + (long long)grp * p.M + t0) * (1.0f / 256.0f) : 0.f;
+        sxs[nt][1] = t0 + 1 < p.M ? __ldg(p.sx + (long long)grp * p.M + t0 + 1) * (1.0f / 256.0f) : 0.f;
+      }
+    }
+    if (PER_GROUP) {
+#pragma unroll
+      for (int mt = 0; mt < MTILES; ++mt) {
+        sws[mt][0] = __ldg(p.sw + (long long)grp * p.N + n0 + 16 * mt + g);
+        sws[mt][1] = __ldg(p.sw + (long long)grp * p.N + n0 + 16 * mt + g + 8);
+      }
+    }
+  };
+  if (gw > 0) fetch(g0);
+
+  float f[MTILES][NT][4];
+  int c[MTILES][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < MTILES; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { f[mt][nt][i] = 0.f; c[mt][nt][i] = 0; }
+
+  bool alive = true;
+  for (int gi = 0; gi < gw && alive; ++gi) {
+    uint32_t blo[NT][4], bhi[NT][4];
+    float sx_c[NT][2], sw_c[MTILES][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      expand4(xb[nt], blo[nt], bhi[nt]);
+      sx_c[nt][0] = sxs[nt][0]; sx_c[nt][1] = sxs[nt][1];
+    }
+#pragma unroll
+    for (int mt = 0; mt < MTILES; ++mt) { sw_c[mt][0] = sws[mt][0]; sw_c[mt][1] = sws[mt][1]; }
+    if (gi + 1 < gw) fetch(g0 + gi + 1);
+    alive = wait_landed(bars + gi * 8u, p.status);
+    alive = __all_sync(0xffffffffu, alive);
+    if (!alive) break;
+    const uint32_t base = smem_u32(wsm) + gi * CHUNK + g * 64 + t * 16;
+#pragma unroll
+    for (int mt = 0; mt < MTILES; ++mt) {
+      const uint4 ra = lds128(base + mt * 1024);
+      const uint4 rb = lds128(base + mt * 1024 + 512);
+      uint32_t alo[4], ahi[4], a8lo[4], a8hi[4];
+      expand4(ra, alo, ahi);
+      expand4(rb, a8lo, a8hi);
+      if (PER_GROUP) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) c[mt][nt][i] = 0;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_s8(c[mt][nt], alo[j], a8lo[j], ahi[j], a8hi[j], blo[nt][j], bhi[nt][j]);
+      if (PER_GROUP) {
+        // reference order: (acc * scale_x[g, m]) * scale_w[g, n]; 2^-8 rides on the token scale (exact)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          f[mt][nt][0] = fmaf(__int2float_rn(c[mt][nt][0]) * sx_c[nt][0], sw_c[mt][0], f[mt][nt][0]);
+          f[mt][nt][1] = fmaf(__int2float_rn(c[mt][nt][1]) * sx_c[nt][1], sw_c[mt][0], f[mt][nt][1]);
+          f[mt][nt][2] = fmaf(__int2float_rn(c[mt][nt][2]) * sx_c[nt][0], sw_c[mt][1], f[mt][nt][2]);
+          f[mt][nt][3] = fmaf(__int2float_rn(c[mt][nt][3]) * sx_c[nt][1], sw_c[mt][1], f[mt][nt][3]);
+        }
+      }
+    }
+  }
+
+  // ---- add the warps' ranges in ascending order ----
+  __syncthreads();   // every warp is done with the weight bytes: the region becomes [warp][token][row] partial sums
+  constexpr int TOK = 8 * NT;
+  {
+    uint32_t* red = reinterpret_cast<uint32_t*>(smem) + (size_t)warp * TOK * ROWS;
+#pragma unroll
+    for (int mt = 0; mt < MTILES; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int row = 16 * mt + g + (i >> 1) * 8, tok = 8 * nt + 2 * t + (i & 1);
+          red[tok * ROWS + row] = PER_GROUP ? __float_as_uint(f[mt][nt][i]) : (uint32_t)c[mt][nt][i];
+        }
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < TOK * ROWS; o += kWarps * 32) {
+    const int tok = o / ROWS, row = o - tok * ROWS;
+    if (tok >= p.M) continue;
+    const uint32_t* red = reinterpret_cast<const uint32_t*>(smem) + o;
+    float v;
+    if (PER_GROUP) {
+      v = __uint_as_float(red[0]);
+#pragma unroll
+      for (int w2 = 1; w2 < kWarps; ++w2) v += __uint_as_float(red[(size_t)w2 * TOK * ROWS]);
+    } else {
+      int s = (int)red[0];
+#pragma unroll
+      for (int w2 = 1; w2 < kWarps; ++w2) s += (int)red[(size_t)w2 * TOK * ROWS];
+      // reference order: (acc * scale_b[n]) * scale_a[m]
+      v = (__int2float_rn(s) * (__ldg(p.sw + n0 + row) * (1.0f / 256.0f))) * __ldg(p.sx + tok);
+    }
+    const long long idx = (long long)tok * p.N + n0 + row;
+    if (p.out_fp16) static_cast<__half*>(p.out)[idx] = __float2half_rn(v);
+    else static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(v);
+  }
+}
+
+size_t skinny_smem(int rows, int nt, int gper) {
+  const size_t w_bytes = (size_t)kWarps * gper * rows * 64;
+  const size_t red_bytes = (size_t)kWarps * (8 * nt) * rows * 4;
+  return (w_bytes > red_bytes ? w_bytes : red_bytes) + (size_t)kWarps * kMaxGroupsPerWarp * 8;
+}
+
+template <int MTILES, int NT, bool PER_GROUP>
+int launch_one(const SkinnyParams& p, size_t smem, cudaStream_t st) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  I4TC_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    I4TC_CUDA(cudaFuncSetAttribute(w4a4_skinny_kernel<MTILES, NT, PER_GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   220 * 1024));
+    configured[dev] = true;
+  }
+  w4a4_skinny_kernel<MTILES, NT, PER_GROUP><<<p.N / (16 * MTILES), kWarps * 32, smem, st>>>(p);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+template <int MTILES, bool PER_GROUP>
+int launch_nt(const SkinnyParams& p, int nt, size_t smem, cudaStream_t st) {
+  switch (nt) {
+    case 1: return launch_one<MTILES, 1, PER_GROUP>(p, smem, st);
+    case 2: return launch_one<MTILES, 2, PER_GROUP>(p, smem, st);
+    case 3: return launch_one<MTILES, 3, PER_GROUP>(p, smem, st);
+    default: return launch_one<MTILES, 4, PER_GROUP>(p, smem, st);
+  }
+}
+
+// Rows per block: 32 when that still gives every SM two blocks, else 16; 0 when the shape does not fit.
+int skinny_rows(long long M, long long N, long long K, int sm_count) {
+  const int G = (int)(K / 128), gper = (G + kWarps - 1) / kWarps, nt = (int)((M + 7) / 8);
+  if (gper > kMaxGroupsPerWarp) return 0;
+  for (int rows : {32, 16}) {
+    if (N % rows != 0) continue;
+    if (rows == 32 && N / 32 < 2ll * sm_count) continue;
+    if (skinny_smem(rows, nt, gper) <= 220 * 1024) return rows;
+  }
+  return 0;
+}
+
+}  // namespace
+
+bool skinny_applicable(long long M, long long N, long long K, int epi_mode, int sm_count) {
+  if (M < 1 || M > 32 || N < 16 || K < 128 || K % 128 != 0 || K > 65536) return false;
+  if (epi_mode != EPI_GROUP && epi_mode != EPI_CHANNEL) return false;
+  return skinny_rows(M, N, K, sm_count) != 0;
+}
+
+int launch_w4a4_skinny(const uint8_t* x, const uint8_t* w, const float* sx, const float* sw, void* out, int out_dtype,
+                       long long M, long long N, int G, bool rowmajor, int epi_mode, int sm_count, unsigned int* status,
+                       cudaStream_t st) {
+  SkinnyParams p;
+  p.x = x; p.w = w; p.sx = sx; p.sw = sw; p.out = out;
+  p.M = (int)M; p.N = (int)N; p.G = G;
+  p.gper = (G + kWarps - 1) / kWarps;
+  if (rowmajor) {
+    p.x_row = p.w_row = (long long)G * 64; p.x_grp = p.w_grp = 64;
+  } else {
+    p.x_row = p.w_row = 64; p.x_grp = M * 64; p.w_grp = N * 64;
+  }
+  p.rowmajor = rowmajor ? 1 : 0;
+  p.out_fp16 = out_dtype == I4TC_FP16;
+  p.status = status;
+  I4TC_REQUIRE(aligned_to(x, 16) && aligned_to(w, 16), I4TC_EALIGN, "packed operands must be 16-byte aligned");
+  const int rows = skinny_rows(M, N, (long long)G * 128, sm_count);
+  I4TC_REQUIRE(rows != 0, I4TC_EINVAL, "shape not supported by the small-batch kernel");
+  const int nt = (int)((M + 7) / 8);
+  const size_t smem = skinny_smem(rows, nt, p.gper);
+  const bool pg = epi_mode == EPI_GROUP;
+  if (rows == 32) return pg ? launch_nt<2, true>(p, nt, smem, st) : launch_nt<2, false>(p, nt, smem, st);
+  return pg ? launch_nt<1, true>(p, nt, smem, st) : launch_nt<1, false>(p, nt, smem, st);
+}
+
+}  // namespace i4tc

@@ -411,6 +411,12 @@ def set_cta_pairs(mode: int = -1) -> None:
     check(lib.i4tc_set_cta_pairs(mode), "set_cta_pairs")
 
 
+def set_small_m_path(path: int = 0) -> None:
+    """Test / tuning hook: 0 = automatic, 1 = CUDA-core kernel only, 2 = register-fed tensor-core kernel wherever it
+    applies (1..32 tokens), 3 = always the tile kernel."""
+    check(lib.i4tc_set_small_m_path(path), "set_small_m_path")
+
+
 def set_epilogue_warps(warps: int = 0) -> None:
     """Force 8 or 16 epilogue warps per thread block of the tensor-core GEMM (tests); 0 restores automatic."""
     check(lib.i4tc_set_epilogue_warps(warps), "set_epilogue_warps")

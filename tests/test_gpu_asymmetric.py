@@ -86,6 +86,43 @@ def test_asymmetric_strided_rows(tc):
     np.testing.assert_array_equal(scale.cpu().numpy(), s)
 
 
+def _adversarial(M, K, seed, dtype):
+    """Rows that stress the rounding decisions: lattice values (exact ties), a large offset with a tiny range, huge and
+    tiny magnitudes, one-sided rows."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    x[0] = torch.randint(-30, 31, (K,), generator=g).float() * 0.25          # quarter lattice: ties everywhere
+    x[1] = 100.0 + torch.randint(0, 4, (K,), generator=g).float() * 0.5      # offset >> range
+    x[2] = torch.randint(0, 16, (K,), generator=g).float()                   # already codes 0..15
+    x[3] = torch.rand(K, generator=g) * 1e-6                                 # below the scale floor
+    x[4] = torch.randn(K, generator=g) * 1e4                                 # large
+    x[5] = -torch.rand(K, generator=g) * 7.0                                 # one-sided negative
+    x[6] = torch.randint(-7, 8, (K,), generator=g).float() * 0.5 + 0.5       # half-integers
+    x[7, ::2] = 0.0
+    return x.to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("gs,clip", [(128, 1.0), (128, 0.7), (64, 0.1), (256, 0.95)])
+def test_quantisers_adversarial_both_kernels(tc, dtype, gs, clip):
+    """The 128-bit kernel (aligned rows) and the general one (rows that start 8 bytes off) give the oracle's codes on
+    rows built to sit on rounding boundaries."""
+    M, K = 24, 2048
+    x = _adversarial(M, K, seed=gs + int(clip * 100), dtype=dtype)
+    codes, s, a = O.quant_asymmetric_grouped(x, gs, clip)
+    ccodes, cs = O.quant_clipped_grouped(x, gs, clip)
+    wide = torch.zeros(M, K + 8, dtype=dtype, device="cuda")
+    wide[:, 4:K + 4] = x.cuda()
+    for xin in (x.cuda(), wide[:, 4:K + 4]):
+        packed, scale, adj = tc.dynamic_int4_quant_asymmetric_clipped_grouped(xin, gs, clip, None)
+        np.testing.assert_array_equal(scale.cpu().numpy(), s)
+        np.testing.assert_array_equal(adj.cpu().numpy(), a)
+        np.testing.assert_array_equal(_codes_of(packed), codes)
+        packed, scale = tc.dynamic_int4_quant_clipped_grouped(xin, gs, clip)
+        np.testing.assert_array_equal(scale.cpu().numpy(), cs)
+        np.testing.assert_array_equal(_codes_of(packed), ccodes)
+
+
 def test_asymmetric_argument_checks(tc):
     x = torch.zeros(4, 256, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError, match="clip_ratio"):

@@ -188,6 +188,42 @@ def test_small_m_weight_streaming(tc, ops, M, N, G):
     assert (outs[0] - outs[1]).abs().max() <= 2e-2 * outs[1].abs().max() + 1e-6
 
 
+@pytest.mark.parametrize("M", [1, 4, 8, 9, 16, 17, 24, 31, 32])
+@pytest.mark.parametrize("N,G", [(16, 1), (48, 3), (4096, 32), (512, 96), (6144, 7)])
+def test_small_m_register_fed_kernel(tc, ops, M, N, G):
+    """The register-fed tensor-core kernel (forced for 1..32 tokens): per-channel results bit-identical to the oracle in
+    both output types, per-group results within the tolerance and a couple of bf16 steps from the tile kernel's."""
+    rng = np.random.RandomState(M * 11 + N + G)
+    K = G * 128
+    a, b = rand_codes(rng, (G, M, 128)), rand_codes(rng, (G, N, 128))
+    if M > 2:
+        a[:, 1, :] = -8      # extreme codes on a whole token: the largest group sums
+        b[:, 3, :] = -8
+    sa = (rng.rand(G, M).astype(np.float32) + 0.01) * 0.1
+    sb = (rng.rand(G, N).astype(np.float32) + 0.01) * 0.01
+    ref_g = O.linear_grouped(a, b, sa, sb)
+    ar, br = a.transpose(1, 0, 2).reshape(M, K), b.transpose(1, 0, 2).reshape(N, K)
+    ref_c = torch.from_numpy(O.dequant_per_channel(O.int_gemm(ar, br), sa[0], sb[0]))
+    ap, bp, arp, brp = dev_packed(a), dev_packed(b), dev_packed(ar), dev_packed(br)
+    outs = {}
+    try:
+        for path in (2, 3):
+            ops.set_small_m_path(path)
+            og = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            tc.cutlass_int4_fused_grouped_gemm(ap, bp, dev_f32(sa), dev_f32(sb), og, M, N, 128, G)
+            ops.check_status()
+            assert_close_bf16(og, ref_g, f"grouped M={M} N={N} G={G} path={path}")
+            outs[path] = og.float().cpu()
+            for dtype in (torch.bfloat16, torch.float16):
+                oc = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+                tc.cutlass_int4_scaled_mm(arp, brp, dev_f32(sa[0]), dev_f32(sb[0]), oc, M, N, K)
+                ops.check_status()
+                assert torch.equal(oc.cpu(), ref_c.to(dtype)), (M, N, G, path, dtype)
+    finally:
+        ops.set_small_m_path(0)
+    assert (outs[2] - outs[3]).abs().max() <= 2e-2 * outs[3].abs().max() + 1e-6
+
+
 def test_config0_end_to_end(tc, ops):
     """x [16,4096] with outlier channels, W [4096,4096]: quantise on the GPU, per-channel linear,
     compare codes, scales and bf16 output with the oracle bit for bit."""
