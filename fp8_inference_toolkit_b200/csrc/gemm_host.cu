@@ -110,15 +110,15 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
   I4TC_CUDA(guard.err);
   I4TC_REQUIRE(d.M < (1ll << 31) - 256 && d.N < (1ll << 31) - 256, I4TC_EINVAL, "M or N too large");
 
-  // a few dozen tokens: stream the weights (unless a test pins the tile shape).  Up to 8 tokens the CUDA-core kernel,
-  // up to 32 the register-fed tensor-core one.
+  // a few dozen tokens: stream the weights (unless a test pins the tile shape)
   if (g_force_bn == 0 && g_force_swap < 0 && g_force_splits == 0 && d.azp_adj == nullptr && !d.i8_operands &&
       (!d.rowmajor || d.K == (long long)d.G * 128)) {
     const int path = g_small_m_path.load();
     const long long K = (long long)d.G * 128;
     const bool gemv_ok = path != 3 && path != 2 && gemv_applicable(d.M, d.N, K, d.epi_mode);
     const bool skinny_ok = path != 3 && path != 1 && skinny_applicable(d.M, d.N, K, d.epi_mode, info->sm_count);
-    if (skinny_ok && (path == 2 || !gemv_ok))
+    // one or two tokens: dp4a on the CUDA cores does not waste tensor-core columns; from three on the tensor cores win
+    if (skinny_ok && (path == 2 || !gemv_ok || d.M > 2))
       return launch_w4a4_skinny(d.a, d.b, d.sa, d.sb, d.out, d.out_dtype, d.M, d.N, d.G, d.rowmajor, d.epi_mode,
                                 info->sm_count, info->status, static_cast<cudaStream_t>(stream));
     if (gemv_ok)
