@@ -200,7 +200,8 @@ def workload_config(M: int, n_gpus: int, per_channel: bool = False) -> dict:
     return {
         "workload": f"BASELINE configs[1]: dense W4A4 {scales} linears at Qwen3-8B shapes "
                     f"(K,N) in (4096,6144),(4096,4096),(4096,24576),(12288,4096), M={M} tokens; "
-                    f"step = quantise+pack of the activations then the fused GEMM, for each shape",
+                    f"step = quantise+pack of the activations then the fused GEMM, for each shape"
+                    + ("; the quantise of the next linear runs on a second stream under the GEMM" if n_gpus > 1 else ""),
         "M": M, "group_size": 0 if per_channel else GROUP, "n_split": n_gpus,
         "l2": "inputs larger than L2 (weights + activations + outputs of one step exceed 126 MB)",
     }
@@ -247,10 +248,41 @@ def run_ours(args) -> None:
     outs = [torch.empty(M, l.out_features, dtype=torch.bfloat16, device=dev) for l in layers]
     ops_per_step = sum(2 * M * N * K for _, K, N in SHAPES)  # whole job, all ranks
 
+    # With the output columns split over several GPUs every rank still quantises whole activations, so that part of
+    # the step does not shrink with N.  It is HBM-bound while the GEMM is tensor/ALU-bound, and the four linears of a
+    # step have independent inputs: from two GPUs on, the quantise of linear i + 1 runs on a second stream under the
+    # GEMM of linear i (it fills the SMs that the GEMM's last wave leaves idle).
+    overlap = world > 1
+    quant_stream = torch.cuda.Stream(dev) if overlap else None
+
+    def quantise(i):
+        return tc.dynamic_int4_quant(xs_dev[i]) if per_channel else tc.dynamic_int4_quant_grouped(xs_dev[i], GROUP)
+
+    held = []   # quantised activations of the running step (allocated on the second stream, read on the main one)
+
     def step(events=None):
+        cur = torch.cuda.current_stream(dev)
+        pending = None
+        if overlap:
+            # the second stream starts a step after the main one has finished the previous step; only then are the
+            # previous step's buffers released, so the allocator can hand them out again on that stream at once
+            quant_stream.wait_stream(cur)
+            held.clear()
+            with torch.cuda.stream(quant_stream):
+                pending = quantise(0) + (torch.cuda.Event(),)
+                pending[2].record(quant_stream)
         for i, (name, K, N) in enumerate(SHAPES):
             lin = layers[i]
-            xp, xsc = tc.dynamic_int4_quant(xs_dev[i]) if per_channel else tc.dynamic_int4_quant_grouped(xs_dev[i], GROUP)
+            if overlap:
+                xp, xsc, ready = pending
+                held.append((xp, xsc))
+                cur.wait_event(ready)
+                if i + 1 < len(SHAPES):
+                    with torch.cuda.stream(quant_stream):
+                        pending = quantise(i + 1) + (torch.cuda.Event(),)
+                        pending[2].record(quant_stream)
+            else:
+                xp, xsc = quantise(i)
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -538,6 +570,37 @@ def bench_moe(args, world, rank, dev, peaks, weak: bool = False, tokens: int = 4
         out = layer()
     ops.check_status()
     torch.cuda.synchronize()
+    # The layer is a chain of short launches, so it is replayed as a CUDA graph where every launch is one of this
+    # library's kernels (one GPU, or the peer transport); with NCCL in the chain it runs eagerly.
+    launch = "eager"
+    graph = None
+    if world == 1 or ep.transport == "peer":
+        try:
+            if world > 1:
+                graph, gout = ep.capture(x_l, ids_l, w_l)
+            else:
+                side = torch.cuda.Stream(dev)
+                with torch.cuda.stream(side):
+                    layer()
+                    side.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=side):
+                        gout = layer()
+        except Exception as exc:   # a launch that cannot be captured here: stay eager (every rank takes the same path)
+            graph = None
+            launch = "eager (capture failed: %s)" % repr(exc)[:120]
+        torch.cuda.synchronize()
+    if graph is not None:
+        eager_layer = layer
+
+        def layer():  # noqa: F811
+            graph.replay()
+            return gout
+        launch = "CUDA graph replay"
+        for _ in range(3):
+            out = layer()
+        ops.check_status()
+        torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     steps = max(args.steps, 10)
@@ -563,7 +626,8 @@ def bench_moe(args, world, rank, dev, peaks, weak: bool = False, tokens: int = 4
         "config": {"workload": "BASELINE configs[3]: 128 experts, top-8 of softmax(N(0,1) logits), %d tokens, "
                                "hidden 2048, intermediate 768, group-128; %d experts and %d tokens per rank"
                                % (T, e_loc, t_loc),
-                   "timed": "sort + dispatch + gather-quantise + gate/up GEMM + SwiGLU-quantise + down GEMM + combine"},
+                   "timed": "sort + dispatch + gather-quantise + gate/up GEMM + SwiGLU-quantise + down GEMM + combine",
+                   "launch": launch},
     }
     if world > 1:
         res["transport"] = ep.transport + (" (rows stored straight into the destination rank's buffer over NVLink, device-side "

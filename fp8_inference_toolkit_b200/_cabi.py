@@ -55,6 +55,8 @@ SIGNATURES = {
     "i4tc_moe_ep_dispatch_quant": (_i, [_p, _l, _l, _l, _p, _l, _l, _p, _p, _l, _p, _l, _l, _i, _p]),
     "i4tc_peer_signal": (_i, [_p, _l, C.c_uint32, _i, _p]),
     "i4tc_peer_wait": (_i, [_p, _l, C.c_uint32, _i, _p]),
+    "i4tc_peer_signal_counter": (_i, [_p, _l, _p, _i, _i, _p]),
+    "i4tc_peer_wait_counter": (_i, [_p, _l, _p, _i, _p]),
     "i4tc_moe_ep_meta_ints": (_l, [_l, _l]),
     "i4tc_moe_ep_unpack": (_i, [_p, _l, _l, _l, _l, _l, _p, _p, _p, _p, _p, _p, _i, _p]),
     "i4tc_moe_silu_mul_quant_rows": (_i, [_p, _l, _p, _l, _p, _p, _i, _p]),

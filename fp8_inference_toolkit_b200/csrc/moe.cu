@@ -463,17 +463,31 @@ __global__ void __launch_bounds__(256) moe_gather_packed_kernel(const uint8_t* _
 // stream) stores a growing epoch number into its slot of every peer's flag array; a rank that is about to read its
 // own buffer waits until every slot has reached the epoch.  The wait is bounded: after two seconds it sets bit 1 of
 // the status word and lets the stream go on.
-__global__ void peer_signal_kernel(const unsigned long long* __restrict__ flag_addrs, int world, unsigned int epoch) {
+// `counter` (optional): the epoch lives in device memory, so that a captured graph of a layer advances it on every
+// replay.  The dispatch signal of a layer bumps it; everything else in the layer reads it.
+__global__ void peer_signal_kernel(const unsigned long long* __restrict__ flag_addrs, int world, unsigned int epoch,
+                                   unsigned int* counter, int bump) {
+  __shared__ unsigned int s_epoch;
+  if (threadIdx.x == 0) {
+    unsigned int e = epoch;
+    if (counter != nullptr) {
+      e = *counter + (bump ? 1u : 0u);
+      if (bump) *counter = e;
+    }
+    s_epoch = e;
+  }
   __threadfence_system();
+  __syncthreads();
   if ((int)threadIdx.x < world) {
     volatile unsigned int* f = reinterpret_cast<volatile unsigned int*>(flag_addrs[threadIdx.x]);
-    *f = epoch;
+    *f = s_epoch;
   }
   __threadfence_system();
 }
 
 __global__ void peer_wait_kernel(const unsigned int* __restrict__ flags, int world, unsigned int epoch,
-                                 unsigned int* status) {
+                                 const unsigned int* counter, unsigned int* status) {
+  if (counter != nullptr) epoch = *counter;
   if ((int)threadIdx.x < world) {
     const volatile unsigned int* f = flags + threadIdx.x;
     unsigned long long t0;
@@ -728,7 +742,30 @@ extern "C" int i4tc_peer_signal(const uint64_t* flag_addrs, int64_t world, uint3
   DeviceGuard guard(device);
   I4TC_CUDA(guard.err);
   peer_signal_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const unsigned long long*>(flag_addrs), (int)world, epoch);
+      reinterpret_cast<const unsigned long long*>(flag_addrs), (int)world, epoch, nullptr, 0);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_peer_signal_counter(const uint64_t* flag_addrs, int64_t world, uint32_t* counter, int bump,
+                                        int device, void* stream) {
+  I4TC_REQUIRE(flag_addrs && counter && world > 0 && world <= 256, I4TC_EINVAL, "bad arguments");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  peer_signal_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const unsigned long long*>(flag_addrs), (int)world, 0u, counter, bump);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_peer_wait_counter(const uint32_t* flags, int64_t world, const uint32_t* counter, int device,
+                                      void* stream) {
+  I4TC_REQUIRE(flags && counter && world > 0 && world <= 256, I4TC_EINVAL, "bad arguments");
+  const DeviceInfo* info;
+  if (int rc = device_info(device, &info)) return rc;
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  peer_wait_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(flags, (int)world, 0u, counter, info->status);
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
 }
@@ -739,7 +776,7 @@ extern "C" int i4tc_peer_wait(const uint32_t* flags, int64_t world, uint32_t epo
   if (int rc = device_info(device, &info)) return rc;
   DeviceGuard guard(device);
   I4TC_CUDA(guard.err);
-  peer_wait_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(flags, (int)world, epoch, info->status);
+  peer_wait_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(flags, (int)world, epoch, nullptr, info->status);
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
 }

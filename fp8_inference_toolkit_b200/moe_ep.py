@@ -290,7 +290,7 @@ class ExpertParallelMoE:
         self.send = torch.zeros(W * (1 + cap) * self.row_bytes, dtype=u8, device=dev)
         self.recv = torch.zeros_like(self.send)
         self.transport = "nccl"
-        self.epoch = 0
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)   # exchanges done so far (peer transport)
         if transport in ("auto", "peer") and world is None and self.world > 1:
             try:
                 self._setup_peer()
@@ -377,15 +377,16 @@ class ExpertParallelMoE:
                                          self.sorted_pairs.data_ptr(), self.P, self.k, send, None, self.slot.data_ptr(),
                                          self.row_bytes, bases, self.cap, self.rank, d, st), "moe_gather_packed")
 
-    def _signal(self, addrs):
+    def _signal(self, addrs, bump: bool):
         from ._cabi import check
-        check(self._lib.i4tc_peer_signal(addrs.data_ptr(), self.world, self.epoch, self.dev.index,
-                                         torch.cuda.current_stream(self.dev).cuda_stream), "peer_signal")
+        check(self._lib.i4tc_peer_signal_counter(addrs.data_ptr(), self.world, self.epoch_dev.data_ptr(), int(bump),
+                                                 self.dev.index, torch.cuda.current_stream(self.dev).cuda_stream),
+              "peer_signal_counter")
 
     def _wait(self, flags):
         from ._cabi import check
-        check(self._lib.i4tc_peer_wait(flags.data_ptr(), self.world, self.epoch, self.dev.index,
-                                       torch.cuda.current_stream(self.dev).cuda_stream), "peer_wait")
+        check(self._lib.i4tc_peer_wait_counter(flags.data_ptr(), self.world, self.epoch_dev.data_ptr(), self.dev.index,
+                                               torch.cuda.current_stream(self.dev).cuda_stream), "peer_wait_counter")
 
     def _unpack(self):
         from ._cabi import check
@@ -419,12 +420,11 @@ class ExpertParallelMoE:
 
     def _stages(self, x, expert_ids, expert_w):
         if self.transport == "peer":
-            self.epoch += 1
-            yield "sort_plan_quantise_store", lambda: (self._prepare(x, expert_ids), self._signal(self.flag_addrs_dispatch))
+            yield "sort_plan_quantise_store", lambda: (self._prepare(x, expert_ids), self._signal(self.flag_addrs_dispatch, True))
             yield "wait_rows", lambda: self._wait(self.flags_dispatch)
             yield "unpack", self._unpack
             yield "experts", self._experts
-            yield "return_store", lambda: (self._pack_return(), self._signal(self.flag_addrs_return))
+            yield "return_store", lambda: (self._pack_return(), self._signal(self.flag_addrs_return, False))
             yield "wait_returns", lambda: self._wait(self.flags_return)
             yield "combine", lambda: self._moe.moe_combine(self.ret_local, self.inv_pairs, expert_w.contiguous(), self.T, self.k)
             return
@@ -443,6 +443,23 @@ class ExpertParallelMoE:
         if self.check_each_call and self.overflowed():
             out = moe_layer_ep(x, expert_ids, expert_w, self.weights, self.E, group=self.group)
         return out
+
+    def capture(self, x: torch.Tensor, expert_ids: torch.Tensor, expert_w: torch.Tensor):
+        """One call of the layer on these (static) tensors as a CUDA graph: ``graph, out = layer.capture(...)``, then
+        ``graph.replay()`` redoes the layer on whatever the tensors hold and leaves the result in ``out``.  Peer
+        transport only (every launch of the layer is then one of this library's kernels and the exchange epoch lives
+        on the device).  Collective: every rank captures, and later replays, the same number of times."""
+        assert self.transport == "peer", "graph capture needs the peer transport"
+        side = torch.cuda.Stream(self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):   # first-use allocations (workspaces, device info) happen outside the capture
+                self(x, expert_ids, expert_w)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            out = self(x, expert_ids, expert_w)
+        return graph, out
 
     def overflowed(self) -> bool:
         """True if any rank exceeded its capacity in a call since the last check (collective: every rank must call it)."""

@@ -323,6 +323,13 @@ int i4tc_moe_ep_dispatch_quant(const void* x, int64_t num_tokens, int64_t K, int
  * exchange; waiting and signalling kernels of different ranks run on different GPUs. */
 int i4tc_peer_signal(const uint64_t* flag_addrs, int64_t world, uint32_t epoch, int device, void* stream);
 int i4tc_peer_wait(const uint32_t* flags, int64_t world, uint32_t epoch, int device, void* stream);
+/* The same pair with the epoch held in device memory (`counter`, one uint32 per layer object), for layers that are
+ * replayed as a CUDA graph: a signal with bump != 0 first adds one to the counter, every other call uses its current
+ * value.  One exchange layer = signal(bump = 1), wait, ..., signal(bump = 0) on a second flag array, wait.
+ * No reference counterpart. */
+int i4tc_peer_signal_counter(const uint64_t* flag_addrs, int64_t world, uint32_t* counter, int bump, int device,
+                             void* stream);
+int i4tc_peer_wait_counter(const uint32_t* flags, int64_t world, const uint32_t* counter, int device, void* stream);
 int64_t i4tc_moe_ep_meta_ints(int64_t world, int64_t e_loc);
 /* a_packed [G, world * cap, 64], a_scale [G, world * cap]: received rows in expert-sorted order (rows past *rows_dev
  * are not written); expert_offsets_loc [e_loc + 1]; pos_of [world * cap]: sorted position of received row (s, j). */

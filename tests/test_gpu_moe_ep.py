@@ -133,6 +133,18 @@ def _worker(rank, world, port):
             out = layer(x[ts].contiguous(), ids[ts].contiguous(), w[ts].contiguous())
             ops.check_status()
             assert torch.equal(out, ref[ts]), transport
+        if transport == "peer":
+            # the same layer replayed as a CUDA graph (the exchange epoch advances on the device)
+            xs, idss, wss = x[ts].contiguous(), ids[ts].contiguous(), w[ts].contiguous()
+            graph, gout = layer.capture(xs, idss, wss)
+            for _ in range(3):
+                gout.zero_()
+                graph.replay()
+                torch.cuda.synchronize()
+                ops.check_status()
+                assert torch.equal(gout, ref[ts]), "graph replay"
+            out = layer(xs, idss, wss)      # and eager calls still line up with the replays of the other rank
+            assert torch.equal(out, ref[ts])
         assert not layer.overflowed()
         layer.close()
     tiny = moe_ep.ExpertParallelMoE(mine, E, t_loc, k, H, cap=64, check_each_call=True, transport="nccl")   # overflows: redone exactly
