@@ -2,13 +2,13 @@
 //
 // At these sizes the op moves half a byte per 2 M operations, far below the machine balance, so the only thing that
 // counts is how many weight bytes are in flight.  The tile kernel (TMA -> converter warps -> tcgen05 -> TMEM drain) is a
-// chain of per-group handshakes with a handful of stages per SM; here a thread block asks for ALL of its weight bytes
-// at once (cp.async.bulk, one mbarrier per warp and K group), several blocks share an SM, and nothing waits on
-// another role: a warp expands the nibbles of its K groups in registers, multiplies them with
-// mma.sync.m16n8k32 (int8, int32 accumulators in registers) against the tokens' codes read straight from
-// global memory / L2, and applies the group's scales in registers.
+// chain of per-group handshakes with a handful of stages per SM; here a thread block asks for ALL of its bytes
+// at once (cp.async.bulk, one mbarrier per warp and K group: the weight rows and, where they fit, the tokens' codes
+// and the scales), several blocks share an SM, and nothing waits on another role: a warp expands the nibbles of its
+// K groups in registers, multiplies them with mma.sync.m16n8k32 (int8, int32 accumulators in registers) and applies
+// the group's scales in registers.
 //
-// A block covers ROWS = 16 or 32 weight rows and the whole K; its 8 warps split the K groups into contiguous ranges
+// A block covers ROWS = 16 or 32 weight rows and the whole K; its 8 or 16 warps split the K groups into contiguous ranges
 // and the ranges are added in ascending order through shared memory (int32 for per-channel scales: exact; fp32 for
 // per-group scales: a fixed order, so the result is deterministic).  No workspace and no second launch.
 //
@@ -25,7 +25,8 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kWarps = 8;
+// Warps per block: 16 halve the serial chain of a warp; 32-row tiles take 8 so that the registers of two blocks fit an SM.
+__host__ __device__ constexpr int skinny_warps(int mtiles) { return mtiles == 2 ? 8 : 16; }
 constexpr int kMaxGroupsPerWarp = 16;
 constexpr uint64_t kSkinnyWaitNs = 2000000000ull;   // 2 s
 
@@ -37,6 +38,7 @@ struct SkinnyParams {
   void* out;          // [M, N]
   int M, N, G;
   int gper;           // K groups per warp
+  int warps;          // warps per block
   long long x_row, x_grp;   // byte strides of the activations: token, K group
   long long w_row, w_grp;   // byte strides of the weights: row, K group
   int rowmajor;
@@ -55,6 +57,12 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
 }
 
 __device__ __forceinline__ void expand4(const uint4& w, uint32_t (&lo)[4], uint32_t (&hi)[4]) {
@@ -78,44 +86,87 @@ __device__ __forceinline__ bool wait_landed(uint32_t bar, unsigned int* status) 
   }
 }
 
+// Bytes of shared memory per warp and K group: the block's weight rows, then (STAGE) the tokens' codes and the rows'
+// scales of that group.
+__host__ __device__ constexpr int skinny_item(int rows, int tok, bool stage) {
+  return rows * 64 + (stage ? tok * 64 + rows * 4 : 0);
+}
+
 // MTILES: 16-row tiles per block (ROWS = 16 MTILES).  NT: 8-token tiles (M <= 8 NT).
-template <int MTILES, int NT, bool PER_GROUP>
-__global__ void __launch_bounds__(kWarps * 32) w4a4_skinny_kernel(const SkinnyParams p) {
+// STAGE: the tokens' codes and both scale vectors of a warp's K groups are brought into shared memory up front as
+// well (bulk copies on the weights' barriers, plain loads for the token scales), so that the loop over the groups
+// touches no global memory; otherwise they are fetched into registers one group ahead (shapes whose tokens would
+// leave room for only one block per SM).
+template <int MTILES, int NT, bool PER_GROUP, bool STAGE>
+__global__ void __launch_bounds__(skinny_warps(MTILES) * 32) w4a4_skinny_kernel(const SkinnyParams p) {
   constexpr int ROWS = 16 * MTILES;
+  constexpr int TOK = 8 * NT;
   constexpr int CHUNK = ROWS * 64;   // bytes of one K group of the block's rows
+  constexpr int ITEM = skinny_item(ROWS, TOK, STAGE);
   extern __shared__ __align__(128) uint8_t smem[];
-  // layout: weights [warp][group of the warp][ROWS][64] (later reused for the warps' partial sums) | barriers
+  // layout: items [warp][group of the warp][ITEM] | token scales [warp][group][TOK] (STAGE) | barriers; the start is
+  // later reused for the warps' partial sums
+  constexpr int nwarps = skinny_warps(MTILES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * ROWS;
   const int g0 = min(p.G, warp * p.gper), g1 = min(p.G, g0 + p.gper), gw = g1 - g0;
-  const size_t w_bytes = (size_t)kWarps * p.gper * CHUNK;
-  const size_t red_bytes = (size_t)kWarps * (8 * NT) * ROWS * 4;
-  uint8_t* wsm = smem + (size_t)warp * p.gper * CHUNK;
-  const uint32_t bars = smem_u32(smem + (w_bytes > red_bytes ? w_bytes : red_bytes)) + (uint32_t)warp * kMaxGroupsPerWarp * 8u;
+  const size_t item_bytes = (size_t)nwarps * p.gper * ITEM;
+  const size_t sx_bytes = (STAGE && PER_GROUP) ? (size_t)nwarps * p.gper * TOK * 4 : 0;
+  const size_t red_bytes = (size_t)nwarps * TOK * ROWS * 4;
+  const size_t data_bytes = item_bytes + sx_bytes > red_bytes ? item_bytes + sx_bytes : red_bytes;
+  uint8_t* wsm = smem + (size_t)warp * p.gper * ITEM;
+  float* sx_s = reinterpret_cast<float*>(smem + item_bytes) + (size_t)warp * p.gper * TOK;
+  const uint32_t bars = smem_u32(smem + data_bytes) + (uint32_t)warp * kMaxGroupsPerWarp * 8u;
 
-  // ---- ask for every weight byte of this warp's K range ----
+  // ---- ask for every byte of this warp's K range ----
   if (lane < gw) mbar_init(bars + lane * 8u, 1);
   fence_mbar_init();
   __syncwarp();
-  if (!p.rowmajor) {
-    // group-major weights: the block's rows of one group are contiguous
-    if (lane < gw) {
-      mbar_arrive_expect_tx(bars + lane * 8u, CHUNK);
-      bulk_load(smem_u32(wsm) + lane * CHUNK, p.w + (long long)(g0 + lane) * p.w_grp + (long long)n0 * 64, CHUNK,
-                bars + lane * 8u);
+  const uint32_t tx = CHUNK + (STAGE ? (uint32_t)p.M * 64u + (PER_GROUP ? ROWS * 4u : 0u) : 0u);
+  if (lane < gw) {
+    const uint32_t bar = bars + lane * 8u, dst = smem_u32(wsm) + lane * ITEM;
+    const int grp = g0 + lane;
+    mbar_arrive_expect_tx(bar, tx);
+    // group-major operands: the block's rows (and all tokens) of one group are contiguous
+    if (!p.rowmajor) bulk_load(dst, p.w + (long long)grp * p.w_grp + (long long)n0 * 64, CHUNK, bar);
+    if (STAGE) {
+      if (!p.rowmajor) bulk_load(dst + CHUNK, p.x + (long long)grp * p.x_grp, (uint32_t)p.M * 64u, bar);
+      if (PER_GROUP) bulk_load(dst + CHUNK + TOK * 64, p.sw + (long long)grp * p.N + n0, ROWS * 4, bar);
     }
-  } else {
-    if (lane < gw) mbar_arrive_expect_tx(bars + lane * 8u, CHUNK);
+  }
+  if (p.rowmajor) {
     __syncwarp();
     for (int i = lane; i < gw * ROWS; i += 32) {
       const int gi = i / ROWS, r = i - gi * ROWS;
-      bulk_load(smem_u32(wsm) + gi * CHUNK + r * 64, p.w + (long long)(n0 + r) * p.w_row + (long long)(g0 + gi) * 64, 64,
+      bulk_load(smem_u32(wsm) + gi * ITEM + r * 64, p.w + (long long)(n0 + r) * p.w_row + (long long)(g0 + gi) * 64, 64,
                 bars + gi * 8u);
     }
+    if (STAGE) {
+      for (int i = lane; i < gw * p.M; i += 32) {
+        const int gi = i / p.M, m = i - gi * p.M;
+        bulk_load(smem_u32(wsm) + gi * ITEM + CHUNK + m * 64, p.x + (long long)m * p.x_row + (long long)(g0 + gi) * 64, 64,
+                  bars + gi * 8u);
+      }
+    }
+  }
+  if (STAGE) {
+    // padding tokens: zero codes; token scales with the 2^-8 folded in
+    const int pad = TOK - p.M;
+    for (int i = lane; i < gw * pad * 4; i += 32) {
+      const int gi = i / (pad * 4), r = i - gi * (pad * 4);
+      *reinterpret_cast<uint4*>(wsm + (size_t)gi * ITEM + CHUNK + (size_t)p.M * 64 + (size_t)r * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (PER_GROUP) {
+      for (int i = lane; i < gw * TOK; i += 32) {
+        const int gi = i / TOK, m = i - gi * TOK;
+        sx_s[i] = m < p.M ? __ldg(p.sx + (long long)(g0 + gi) * p.M + m) * (1.0f / 256.0f) : 0.f;
+      }
+    }
+    __syncwarp();
   }
 
-  // ---- token codes and scales of the first group (registers) ----
+  // ---- without staging: token codes and scales of the first group (registers) ----
   uint4 xb[NT];
   float sxs[NT][2], sws[MTILES][2];
   auto fetch = [&](int grp) {
@@ -138,7 +189,7 @@ __global__ void __launch_bounds__(kWarps * 32) w4a4_skinny_kernel(const SkinnyPa
       }
     }
   };
-  if (gw > 0) fetch(g0);
+  if (!STAGE && gw > 0) fetch(g0);
 
   float f[MTILES][NT][4];
   int c[MTILES][NT][4];
@@ -153,18 +204,39 @@ __global__ void __launch_bounds__(kWarps * 32) w4a4_skinny_kernel(const SkinnyPa
   for (int gi = 0; gi < gw && alive; ++gi) {
     uint32_t blo[NT][4], bhi[NT][4];
     float sx_c[NT][2], sw_c[MTILES][2];
+    if (!STAGE) {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      expand4(xb[nt], blo[nt], bhi[nt]);
-      sx_c[nt][0] = sxs[nt][0]; sx_c[nt][1] = sxs[nt][1];
+      for (int nt = 0; nt < NT; ++nt) {
+        expand4(xb[nt], blo[nt], bhi[nt]);
+        sx_c[nt][0] = sxs[nt][0]; sx_c[nt][1] = sxs[nt][1];
+      }
+#pragma unroll
+      for (int mt = 0; mt < MTILES; ++mt) { sw_c[mt][0] = sws[mt][0]; sw_c[mt][1] = sws[mt][1]; }
+      if (gi + 1 < gw) fetch(g0 + gi + 1);
     }
-#pragma unroll
-    for (int mt = 0; mt < MTILES; ++mt) { sw_c[mt][0] = sws[mt][0]; sw_c[mt][1] = sws[mt][1]; }
-    if (gi + 1 < gw) fetch(g0 + gi + 1);
     alive = wait_landed(bars + gi * 8u, p.status);
     alive = __all_sync(0xffffffffu, alive);
     if (!alive) break;
-    const uint32_t base = smem_u32(wsm) + gi * CHUNK + g * 64 + t * 16;
+    const uint32_t item = smem_u32(wsm) + gi * ITEM;
+    if (STAGE) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4 xv = lds128(item + CHUNK + (8 * nt + g) * 64 + t * 16);
+        expand4(xv, blo[nt], bhi[nt]);
+        if (PER_GROUP) {
+          const float2 s2 = *reinterpret_cast<const float2*>(sx_s + gi * TOK + 8 * nt + 2 * t);
+          sx_c[nt][0] = s2.x; sx_c[nt][1] = s2.y;
+        }
+      }
+      if (PER_GROUP) {
+#pragma unroll
+        for (int mt = 0; mt < MTILES; ++mt) {
+          sw_c[mt][0] = lds_f32(item + CHUNK + TOK * 64 + (16 * mt + g) * 4);
+          sw_c[mt][1] = lds_f32(item + CHUNK + TOK * 64 + (16 * mt + g + 8) * 4);
+        }
+      }
+    }
+    const uint32_t base = item + g * 64 + t * 16;
 #pragma unroll
     for (int mt = 0; mt < MTILES; ++mt) {
       const uint4 ra = lds128(base + mt * 1024);
@@ -196,8 +268,7 @@ __global__ void __launch_bounds__(kWarps * 32) w4a4_skinny_kernel(const SkinnyPa
   }
 
   // ---- add the warps' ranges in ascending order ----
-  __syncthreads();   // every warp is done with the weight bytes: the region becomes [warp][token][row] partial sums
-  constexpr int TOK = 8 * NT;
+  __syncthreads();   // every warp is done with its staged bytes: the region becomes [warp][token][row] partial sums
   {
     uint32_t* red = reinterpret_cast<uint32_t*>(smem) + (size_t)warp * TOK * ROWS;
 #pragma unroll
@@ -211,7 +282,7 @@ __global__ void __launch_bounds__(kWarps * 32) w4a4_skinny_kernel(const SkinnyPa
         }
   }
   __syncthreads();
-  for (int o = threadIdx.x; o < TOK * ROWS; o += kWarps * 32) {
+  for (int o = threadIdx.x; o < TOK * ROWS; o += nwarps * 32) {
     const int tok = o / ROWS, row = o - tok * ROWS;
     if (tok >= p.M) continue;
     const uint32_t* red = reinterpret_cast<const uint32_t*>(smem) + o;
@@ -219,11 +290,11 @@ __global__ void __launch_bounds__(kWarps * 32) w4a4_skinny_kernel(const SkinnyPa
     if (PER_GROUP) {
       v = __uint_as_float(red[0]);
 #pragma unroll
-      for (int w2 = 1; w2 < kWarps; ++w2) v += __uint_as_float(red[(size_t)w2 * TOK * ROWS]);
+      for (int w2 = 1; w2 < nwarps; ++w2) v += __uint_as_float(red[(size_t)w2 * TOK * ROWS]);
     } else {
       int s = (int)red[0];
 #pragma unroll
-      for (int w2 = 1; w2 < kWarps; ++w2) s += (int)red[(size_t)w2 * TOK * ROWS];
+      for (int w2 = 1; w2 < nwarps; ++w2) s += (int)red[(size_t)w2 * TOK * ROWS];
       // reference order: (acc * scale_b[n]) * scale_a[m]
       v = (__int2float_rn(s) * (__ldg(p.sw + n0 + row) * (1.0f / 256.0f))) * __ldg(p.sx + tok);
     }
@@ -233,47 +304,75 @@ __global__ void __launch_bounds__(kWarps * 32) w4a4_skinny_kernel(const SkinnyPa
   }
 }
 
-size_t skinny_smem(int rows, int nt, int gper) {
-  const size_t w_bytes = (size_t)kWarps * gper * rows * 64;
-  const size_t red_bytes = (size_t)kWarps * (8 * nt) * rows * 4;
-  return (w_bytes > red_bytes ? w_bytes : red_bytes) + (size_t)kWarps * kMaxGroupsPerWarp * 8;
+size_t skinny_smem(int warps, int rows, int nt, int gper, bool per_group, bool stage) {
+  const size_t item_bytes = (size_t)warps * gper * skinny_item(rows, 8 * nt, stage);
+  const size_t sx_bytes = (stage && per_group) ? (size_t)warps * gper * 8 * nt * 4 : 0;
+  const size_t red_bytes = (size_t)warps * (8 * nt) * rows * 4;
+  return (item_bytes + sx_bytes > red_bytes ? item_bytes + sx_bytes : red_bytes) + (size_t)warps * kMaxGroupsPerWarp * 8;
 }
 
-template <int MTILES, int NT, bool PER_GROUP>
+template <int MTILES, int NT, bool PER_GROUP, bool STAGE>
 int launch_one(const SkinnyParams& p, size_t smem, cudaStream_t st) {
   static bool configured[64] = {false};
   int dev = 0;
   I4TC_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    I4TC_CUDA(cudaFuncSetAttribute(w4a4_skinny_kernel<MTILES, NT, PER_GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   220 * 1024));
+    I4TC_CUDA(cudaFuncSetAttribute(w4a4_skinny_kernel<MTILES, NT, PER_GROUP, STAGE>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     configured[dev] = true;
   }
-  w4a4_skinny_kernel<MTILES, NT, PER_GROUP><<<p.N / (16 * MTILES), kWarps * 32, smem, st>>>(p);
+  w4a4_skinny_kernel<MTILES, NT, PER_GROUP, STAGE><<<p.N / (16 * MTILES), skinny_warps(MTILES) * 32, smem, st>>>(p);
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
 }
 
-template <int MTILES, bool PER_GROUP>
+template <int MTILES, bool PER_GROUP, bool STAGE>
 int launch_nt(const SkinnyParams& p, int nt, size_t smem, cudaStream_t st) {
   switch (nt) {
-    case 1: return launch_one<MTILES, 1, PER_GROUP>(p, smem, st);
-    case 2: return launch_one<MTILES, 2, PER_GROUP>(p, smem, st);
-    case 3: return launch_one<MTILES, 3, PER_GROUP>(p, smem, st);
-    default: return launch_one<MTILES, 4, PER_GROUP>(p, smem, st);
+    case 1: return launch_one<MTILES, 1, PER_GROUP, STAGE>(p, smem, st);
+    case 2: return launch_one<MTILES, 2, PER_GROUP, STAGE>(p, smem, st);
+    default: break;
   }
+  if constexpr (MTILES == 1) {   // 32-row tiles exist for up to 16 tokens only
+    if (nt == 3) return launch_one<MTILES, 3, PER_GROUP, STAGE>(p, smem, st);
+    if (nt == 4) return launch_one<MTILES, 4, PER_GROUP, STAGE>(p, smem, st);
+  }
+  return fail(I4TC_EINVAL, "unsupported token count");
 }
 
-// Rows per block: 32 when that still gives every SM two blocks, else 16; 0 when the shape does not fit.
-int skinny_rows(long long M, long long N, long long K, int sm_count) {
-  const int G = (int)(K / 128), gper = (G + kWarps - 1) / kWarps, nt = (int)((M + 7) / 8);
-  if (gper > kMaxGroupsPerWarp) return 0;
+struct SkinnyPlan {
+  int rows = 0;        // 0: the shape does not fit
+  int warps = 16;
+  int gper = 0;
+  bool stage = false;
+  size_t smem = 0;
+};
+
+// Rows per block: 32 when that still gives every SM two blocks (and there are at most 16 tokens), else 16.  The tokens are staged in shared memory when
+// at least two blocks still fit an SM.
+SkinnyPlan skinny_plan(long long M, long long N, long long K, bool per_group, int sm_count) {
+  SkinnyPlan pl;
+  const int G = (int)(K / 128), nt = (int)((M + 7) / 8);
   for (int rows : {32, 16}) {
     if (N % rows != 0) continue;
-    if (rows == 32 && N / 32 < 2ll * sm_count) continue;
-    if (skinny_smem(rows, nt, gper) <= 220 * 1024) return rows;
+    if (rows == 32 && (N / 32 < 2ll * sm_count || nt > 2)) continue;   // (two row tiles x four token tiles would spill)
+    const int warps = skinny_warps(rows / 16);
+    const int gper = (G + warps - 1) / warps;
+    if (gper > kMaxGroupsPerWarp) continue;
+    const size_t staged = skinny_smem(warps, rows, nt, gper, per_group, true);
+    const size_t plain = skinny_smem(warps, rows, nt, gper, per_group, false);
+    pl.warps = warps;
+    pl.gper = gper;
+    if (staged <= 110 * 1024) {
+      pl.rows = rows; pl.stage = true; pl.smem = staged;
+      return pl;
+    }
+    if (plain <= 220 * 1024) {
+      pl.rows = rows; pl.stage = false; pl.smem = plain;
+      return pl;
+    }
   }
-  return 0;
+  return pl;
 }
 
 }  // namespace
@@ -281,7 +380,7 @@ int skinny_rows(long long M, long long N, long long K, int sm_count) {
 bool skinny_applicable(long long M, long long N, long long K, int epi_mode, int sm_count) {
   if (M < 1 || M > 32 || N < 16 || K < 128 || K % 128 != 0 || K > 65536) return false;
   if (epi_mode != EPI_GROUP && epi_mode != EPI_CHANNEL) return false;
-  return skinny_rows(M, N, K, sm_count) != 0;
+  return skinny_plan(M, N, K, epi_mode == EPI_GROUP, sm_count).rows != 0;
 }
 
 int launch_w4a4_skinny(const uint8_t* x, const uint8_t* w, const float* sx, const float* sw, void* out, int out_dtype,
@@ -290,7 +389,6 @@ int launch_w4a4_skinny(const uint8_t* x, const uint8_t* w, const float* sx, cons
   SkinnyParams p;
   p.x = x; p.w = w; p.sx = sx; p.sw = sw; p.out = out;
   p.M = (int)M; p.N = (int)N; p.G = G;
-  p.gper = (G + kWarps - 1) / kWarps;
   if (rowmajor) {
     p.x_row = p.w_row = (long long)G * 64; p.x_grp = p.w_grp = 64;
   } else {
@@ -300,13 +398,28 @@ int launch_w4a4_skinny(const uint8_t* x, const uint8_t* w, const float* sx, cons
   p.out_fp16 = out_dtype == I4TC_FP16;
   p.status = status;
   I4TC_REQUIRE(aligned_to(x, 16) && aligned_to(w, 16), I4TC_EALIGN, "packed operands must be 16-byte aligned");
-  const int rows = skinny_rows(M, N, (long long)G * 128, sm_count);
-  I4TC_REQUIRE(rows != 0, I4TC_EINVAL, "shape not supported by the small-batch kernel");
-  const int nt = (int)((M + 7) / 8);
-  const size_t smem = skinny_smem(rows, nt, p.gper);
   const bool pg = epi_mode == EPI_GROUP;
-  if (rows == 32) return pg ? launch_nt<2, true>(p, nt, smem, st) : launch_nt<2, false>(p, nt, smem, st);
-  return pg ? launch_nt<1, true>(p, nt, smem, st) : launch_nt<1, false>(p, nt, smem, st);
+  SkinnyPlan pl = skinny_plan(M, N, (long long)G * 128, pg, sm_count);
+  I4TC_REQUIRE(pl.rows != 0, I4TC_EINVAL, "shape not supported by the small-batch kernel");
+  const int nt = (int)((M + 7) / 8);
+  p.gper = pl.gper;
+  p.warps = pl.warps;
+  if (pl.stage && pg && !aligned_to(sw, 16)) {   // the bulk copy of the row scales needs 16-byte alignment
+    pl.stage = false;
+    pl.smem = skinny_smem(pl.warps, pl.rows, nt, pl.gper, pg, false);
+  }
+#define I4TC_SKINNY_CASE(MT_, PG_, ST_) \
+  if (pl.rows == 16 * MT_ && pg == PG_ && pl.stage == ST_) return launch_nt<MT_, PG_, ST_>(p, nt, pl.smem, st);
+  I4TC_SKINNY_CASE(1, true, true)
+  I4TC_SKINNY_CASE(1, true, false)
+  I4TC_SKINNY_CASE(1, false, true)
+  I4TC_SKINNY_CASE(1, false, false)
+  I4TC_SKINNY_CASE(2, true, true)
+  I4TC_SKINNY_CASE(2, true, false)
+  I4TC_SKINNY_CASE(2, false, true)
+  I4TC_SKINNY_CASE(2, false, false)
+#undef I4TC_SKINNY_CASE
+  return fail(I4TC_EINVAL, "unsupported configuration");
 }
 
 }  // namespace i4tc
