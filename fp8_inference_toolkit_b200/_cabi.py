@@ -64,6 +64,8 @@ SIGNATURES = {
     "i4tc_moe_gather_packed": (_i, [_p, _p, _l, _l, _p, _l, _l, _p, _p, _p, _l, _p, _l, _l, _i, _p]),
     "i4tc_moe_gather_quant": (_i, [_p, _i, _l, _l, _l, _p, _l, _l, _p, _p, _i, _p]),
     "i4tc_moe_grouped_gemm": (_i, [_p, _p, _p, _p, _p, _p, _l, _l, _l, _l, _i, _p]),
+    "i4tc_moe_grouped_gemm_rows": (_i, [_p, _p, _p, _p, _p, _p, _l, _l, _l, _l, _i, _p]),
+    "i4tc_moe_ep_return_rows": (_i, [_p, _l, _l, _p, _p, _l, _l, _l, _p, _i, _p]),
     "i4tc_moe_silu_mul_quant": (_i, [_p, _l, _l, _p, _p, _i, _p]),
     "i4tc_rmsnorm_quant_grouped": (_i, [_p, _l, _l, _l, _p, _f, _l, _p, _p, _i, _p]),
     "i4tc_moe_combine": (_i, [_p, _p, _p, _l, _l, _l, _p, _i, _p]),

@@ -33,6 +33,9 @@ struct GemmParams {
   const float* sq;   // Q-side scales, element (g, q) at sq[g * sq_gstride + q]
   long long sp_gstride;
   long long sq_gstride;
+  // Optional (per-group epilogue, unswapped, 16-bit output): address of every output row, 16-byte aligned, instead of
+  // out + row * ldc -- rows may lie in another GPU's memory (plain stores over NVLink).
+  const unsigned long long* out_rows;
   // Zero-point term of asymmetrically quantised activations (EPI_GROUP only; nullptr = none): group g adds
   // zp[g, p] * zq[g, q] to its integer sum before the scales (activation side: azp_adj, weight side: w_col_sum);
   // same strides as sp / sq.

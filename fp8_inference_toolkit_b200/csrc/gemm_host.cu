@@ -355,15 +355,37 @@ extern "C" int i4tc_gemm_grouped_int32(const uint8_t* a, const uint8_t* b, int32
   return run_dense(d, device, stream);
 }
 
+static int moe_grouped_gemm_impl(const uint8_t* a, const float* scale_a, const uint8_t* b, const float* scale_b,
+                                 const int32_t* expert_offsets, void* out, const uint64_t* out_rows, int64_t num_pairs,
+                                 int64_t N, int64_t num_groups, int64_t num_experts, int device, void* stream);
+
 extern "C" int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, const uint8_t* b,
                                      const float* scale_b, const int32_t* expert_offsets, void* out,
                                      int64_t num_pairs, int64_t N, int64_t num_groups, int64_t num_experts,
                                      int device, void* stream) {
+  I4TC_REQUIRE(out != nullptr || num_pairs == 0 || N == 0, I4TC_EINVAL, "null pointer");
+  return moe_grouped_gemm_impl(a, scale_a, b, scale_b, expert_offsets, out, nullptr, num_pairs, N, num_groups, num_experts,
+                               device, stream);
+}
+
+extern "C" int i4tc_moe_grouped_gemm_rows(const uint8_t* a, const float* scale_a, const uint8_t* b,
+                                          const float* scale_b, const int32_t* expert_offsets,
+                                          const uint64_t* out_rows, int64_t num_pairs, int64_t N, int64_t num_groups,
+                                          int64_t num_experts, int device, void* stream) {
+  I4TC_REQUIRE(out_rows != nullptr || num_pairs == 0 || N == 0, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(N % 8 == 0, I4TC_EINVAL, "N must be a multiple of 8 when rows are addressed through a table");
+  return moe_grouped_gemm_impl(a, scale_a, b, scale_b, expert_offsets, nullptr, out_rows, num_pairs, N, num_groups,
+                               num_experts, device, stream);
+}
+
+static int moe_grouped_gemm_impl(const uint8_t* a, const float* scale_a, const uint8_t* b, const float* scale_b,
+                                 const int32_t* expert_offsets, void* out, const uint64_t* out_rows, int64_t num_pairs,
+                                 int64_t N, int64_t num_groups, int64_t num_experts, int device, void* stream) {
   I4TC_REQUIRE(num_pairs >= 0 && N >= 0, I4TC_EINVAL, "negative size");
   I4TC_REQUIRE(num_groups > 0 && num_groups <= 512, I4TC_EINVAL, "num_groups must be in [1, 512]");
   I4TC_REQUIRE(num_experts > 0 && num_experts <= 65536, I4TC_EINVAL, "num_experts out of range");
   if (num_pairs == 0 || N == 0) return I4TC_OK;
-  I4TC_REQUIRE(a && b && scale_a && scale_b && expert_offsets && out, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(a && b && scale_a && scale_b && expert_offsets && (out || out_rows), I4TC_EINVAL, "null pointer");
   I4TC_REQUIRE(num_pairs < (1ll << 31) - 256 && N * num_experts < (1ll << 31), I4TC_EINVAL, "sizes too large");
   const DeviceInfo* info;
   if (int rc = device_info(device, &info)) return rc;
@@ -390,6 +412,7 @@ extern "C" int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, con
   p.sq_gstride = N;
   p.sq_estride = num_groups * N;
   p.out = out;
+  p.out_rows = reinterpret_cast<const unsigned long long*>(out_rows);
   p.ldc = N;
   p.num_q_tiles = (int)((N + bn - 1) / bn);
   p.expert_offsets = expert_offsets;

@@ -465,30 +465,38 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
     // ---- write the tile: thread owns rows 8a + lr, column pairs c * 32 + kk * 8 + 2 lq ----
     OutT* out = static_cast<OutT*>(p.out);
     float* ws = (p.split_ws != nullptr) ? p.split_ws + (long long)ti.split * p.ws_stride : nullptr;
+    // row addresses from a table (rows of another GPU's buffer, for instance) instead of out + row * ldc
+    const unsigned long long* orows = SWAP ? nullptr : p.out_rows;
     const bool vec_ok = !SWAP && ws == nullptr && ((p.ldc & 7) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) && (ti.q0 + col_base + CW <= ti.q_lim);
+                        (orows != nullptr || (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                        (ti.q0 + col_base + CW <= ti.q_lim);
     if (vec_ok) {
       // per row and 32-column chunk the quad holds four column pairs per lane; after the quad transpose
       // each lane writes 8 consecutive columns with one 16-byte store (64 contiguous bytes per quad)
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
         const int prow = ti.p0 + quad * 32 + 8 * a + lr;
+        OutT* rowp = nullptr;
+        if (prow < ti.p_lim)
+          rowp = (orows != nullptr) ? reinterpret_cast<OutT*>(orows[prow]) : out + (long long)prow * p.ldc;
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
           uint32_t x[4];
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) x[kk] = pack_pair<OutT>(f[(a * NCH + c) * 4 + kk]);
           const uint4 y = quad_transpose(x, lq);
-          if (prow < ti.p_lim)
-            *reinterpret_cast<uint4*>(out + (long long)prow * p.ldc + ti.q0 + col_base + c * 32 + lq * 8) = y;
+          if (prow < ti.p_lim) *reinterpret_cast<uint4*>(rowp + ti.q0 + col_base + c * 32 + lq * 8) = y;
         }
       }
     } else {
-      const bool pair_ok = ((p.ldc & 1) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
+      const bool pair_ok = ((p.ldc & 1) == 0) && (orows != nullptr || (reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
         const int prow = ti.p0 + quad * 32 + 8 * a + lr;
         if (prow >= ti.p_lim) continue;
+        // (with a row table: the row's own base and row index 0)
+        OutT* obase = (orows != nullptr) ? reinterpret_cast<OutT*>(orows[prow]) : out;
+        const int orow = (orows != nullptr) ? 0 : prow;
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
 #pragma unroll
@@ -506,7 +514,7 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
                 if (q + 1 < ti.q_lim) ws[(long long)(q + 1) * p.ldc + prow] = v.y;
               }
             } else {
-              store_pair<OutT, SWAP>(out, p.ldc, prow, q, ti.q_lim, v, pair_ok);
+              store_pair<OutT, SWAP>(obase, p.ldc, orow, q, ti.q_lim, v, pair_ok);
             }
           }
         }

@@ -383,10 +383,18 @@ __global__ void __launch_bounds__(256) moe_ep_pack_return_kernel(const __nv_bflo
                                                                 const int32_t* __restrict__ pos_of, long long rows,
                                                                 int H, __nv_bfloat16* __restrict__ ret_send,
                                                                 const unsigned long long* __restrict__ peer_bases,
-                                                                const int32_t* __restrict__ start, int cap) {
+                                                                const int32_t* __restrict__ start, int cap, int world,
+                                                                int rot) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * 8 + warp;
+  long long row = (long long)blockIdx.x * 8 + warp;
   if (row >= rows) return;
+  if (peer_bases != nullptr) {
+    // Neighbouring warps write to different ranks, and rank r starts its round with rank r + 1: otherwise every rank
+    // would send its block for rank 0 first, then the one for rank 1, ... and one receiver at a time would take all
+    // the senders' traffic while the other links sit idle.
+    const int s = (int)((row + rot) % world);
+    row = (long long)s * cap + row / world;
+  }
   const int pos = pos_of[row];
   if (pos < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(y + (long long)pos * H);
@@ -412,6 +420,20 @@ __global__ void __launch_bounds__(256) moe_ep_pack_return_kernel(const __nv_bflo
   }
 }
 
+// Where the expert output of every expert-sorted row has to go when it is written straight into the sources' return
+// buffers: out_rows[pos_of[s][j]] = address of row start[s] + j of source s's buffer (H 16-bit values per row).
+__global__ void moe_ep_return_rows_kernel(const int32_t* __restrict__ pos_of, long long rows, int H,
+                                          const unsigned long long* __restrict__ peer_bases,
+                                          const int32_t* __restrict__ start, int cap,
+                                          unsigned long long* __restrict__ out_rows) {
+  const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const int pos = pos_of[row];
+  if (pos < 0) return;
+  const int s = (int)(row / cap), j = (int)(row - (long long)s * cap);
+  out_rows[pos] = peer_bases[s] + ((unsigned long long)(start[s] + j)) * (unsigned long long)H * 2ull;
+}
+
 // Rows that were quantised once per token, copied to where each (token, slot) pair needs them.  One warp per output
 // row r: source token = pairs[r] / top_k (nothing is copied for a negative or out-of-range pair index, or beyond
 // *rows_dev).  Source layout: group-major [G, T, 64] codes and [G, T] scales.  Destination: group-major [G, R, 64] / [G, R]
@@ -426,7 +448,16 @@ __global__ void __launch_bounds__(256) moe_gather_packed_kernel(const uint8_t* _
                                                                const unsigned long long* __restrict__ peer_bases,
                                                                int block_rows, int my_block) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long r = (long long)blockIdx.x * 8 + warp;
+  long long r = (long long)blockIdx.x * 8 + warp;
+  if (peer_bases != nullptr) {
+    // rows are sorted by destination rank: walk eight evenly spaced stretches of them at once (warp w of a block takes
+    // stretch w, first stretch rotated by the rank), so that a rank writes to all its peers at the same time instead
+    // of every rank flooding rank 0 first
+    const long long per = (R + 7) / 8;
+    const long long i = r / 8;
+    r = (long long)((warp + my_block) & 7) * per + i;
+    if (i >= per) return;
+  }
   if (r >= R) return;
   const int pair = pairs[r];
   if (pair < 0) return;
@@ -658,7 +689,9 @@ extern "C" int i4tc_moe_gather_packed(const uint8_t* tok_packed, const float* to
   }
   DeviceGuard guard(device);
   I4TC_CUDA(guard.err);
-  moe_gather_packed_kernel<<<(unsigned)((num_pairs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  // (with peer destinations a block's eight warps take one row of each of eight stretches of ceil(num_pairs / 8) rows)
+  const long long launch_rows = peer_bases ? ((num_pairs + 7) / 8) * 8 : num_pairs;
+  moe_gather_packed_kernel<<<(unsigned)((launch_rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       tok_packed, tok_scale, num_tokens, (int)num_groups, pairs, (int)top_k, num_pairs, packed, scale, row_map, row_bytes,
       reinterpret_cast<const unsigned long long*>(peer_bases), (int)(1 + cap), (int)my_rank);
   I4TC_CUDA(cudaGetLastError());
@@ -732,7 +765,25 @@ extern "C" int i4tc_moe_ep_pack_return(const void* y, const int32_t* pos_of, int
   const int32_t* start = peer_bases ? meta + world + world * e_loc + world * (e_loc + 1) : nullptr;
   moe_ep_pack_return_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(y), pos_of, rows, (int)H, static_cast<__nv_bfloat16*>(ret_send),
-      reinterpret_cast<const unsigned long long*>(peer_bases), start, (int)(cap > 0 ? cap : 1));
+      reinterpret_cast<const unsigned long long*>(peer_bases), start, (int)(cap > 0 ? cap : 1),
+      (int)(world > 0 ? world : 1), peer_bases ? device + 1 : 0);
+  I4TC_CUDA(cudaGetLastError());
+  return I4TC_OK;
+}
+
+extern "C" int i4tc_moe_ep_return_rows(const int32_t* pos_of, int64_t rows, int64_t H, const uint64_t* peer_bases,
+                                       const int32_t* meta, int64_t world, int64_t e_loc, int64_t cap,
+                                       uint64_t* out_rows, int device, void* stream) {
+  I4TC_REQUIRE(rows >= 0 && H > 0 && H % 8 == 0, I4TC_EINVAL, "H must be a positive multiple of 8");
+  if (rows == 0) return I4TC_OK;
+  I4TC_REQUIRE(pos_of && peer_bases && meta && out_rows, I4TC_EINVAL, "null pointer");
+  I4TC_REQUIRE(world > 0 && e_loc > 0 && cap > 0 && rows == world * cap, I4TC_EINVAL, "rows must be world * cap");
+  DeviceGuard guard(device);
+  I4TC_CUDA(guard.err);
+  const int32_t* start = meta + world + world * e_loc + world * (e_loc + 1);
+  moe_ep_return_rows_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      pos_of, rows, (int)H, reinterpret_cast<const unsigned long long*>(peer_bases), start, (int)cap,
+      reinterpret_cast<unsigned long long*>(out_rows));
   I4TC_CUDA(cudaGetLastError());
   return I4TC_OK;
 }

@@ -104,6 +104,28 @@ def moe_w4a4_grouped_gemm(a_packed, scale_a, b_packed, scale_b, expert_offsets, 
                                     num_groups, num_experts, _dev(out), _stream(out)), "moe_w4a4_grouped_gemm")
 
 
+def moe_w4a4_grouped_gemm_rows(a_packed, scale_a, b_packed, scale_b, expert_offsets, out_rows, N: int, num_groups: int,
+                               num_experts: int) -> None:
+    """The grouped GEMM with output row r written to address ``out_rows[r]`` (int64 [P] on the device, 16-byte aligned
+    addresses of N bf16 values each; they may lie in another GPU's memory)."""
+    P = out_rows.numel()
+    _require(out_rows.dtype == torch.int64 and out_rows.is_cuda and out_rows.is_contiguous(), "out_rows must be int64 [P]")
+    _require(N % 8 == 0, "N must be a multiple of 8")
+    _require(a_packed.dtype == torch.uint8 and a_packed.is_contiguous() and a_packed.numel() == num_groups * P * 64,
+             "a_packed must be [G,P,64] uint8")
+    _require(b_packed.dtype == torch.uint8 and b_packed.is_contiguous()
+             and b_packed.numel() == num_experts * num_groups * N * 64, "b_packed must be [E,G,N,64] uint8")
+    _require(scale_a.dtype == torch.float32 and scale_a.numel() == num_groups * P, "scale_a must be f32 [G,P]")
+    _require(scale_b.dtype == torch.float32 and scale_b.numel() == num_experts * num_groups * N,
+             "scale_b must be f32 [E,G,N]")
+    _require(expert_offsets.dtype == torch.int32 and expert_offsets.numel() == num_experts + 1,
+             "expert_offsets must be int32 [E+1]")
+    check(lib.i4tc_moe_grouped_gemm_rows(a_packed.data_ptr(), scale_a.data_ptr(), b_packed.data_ptr(),
+                                         scale_b.data_ptr(), expert_offsets.data_ptr(), out_rows.data_ptr(), P, N,
+                                         num_groups, num_experts, _dev(out_rows), _stream(out_rows)),
+          "moe_w4a4_grouped_gemm_rows")
+
+
 def moe_silu_mul_quant(h: torch.Tensor):
     """bf16 [P,2I] laid out [gate | up] -> SwiGLU -> grouped-quantised [I/128,P,64] / [I/128,P]."""
     _require(h.is_cuda and h.dtype == torch.bfloat16 and h.is_contiguous(), "h must be contiguous bf16 CUDA")

@@ -311,6 +311,7 @@ class ExpertParallelMoE:
         self.hp = torch.zeros(I // 128, R, 64, dtype=u8, device=dev)
         self.hs = torch.zeros(I // 128, R, dtype=f32, device=dev)
         self.y = torch.zeros(R, H, dtype=bf16, device=dev)
+        self.out_rows = torch.zeros(R, dtype=torch.int64, device=dev)
         self.ret_send = torch.zeros(R, H, dtype=bf16, device=dev)
         self.ret_recv = torch.zeros(R, H, dtype=bf16, device=dev)
         self.tok_packed = torch.empty(G, tokens_per_rank, 64, dtype=u8, device=dev)
@@ -404,16 +405,22 @@ class ExpertParallelMoE:
                                 self.G, self.e_loc)
         check(lib.i4tc_moe_silu_mul_quant_rows(self.h.data_ptr(), self.r_max, self.rows_dev.data_ptr(), w.inter,
                                                self.hp.data_ptr(), self.hs.data_ptr(), d, st), "moe_silu_mul_quant_rows")
-        m.moe_w4a4_grouped_gemm(self.hp, self.hs, w.down_packed, w.down_scale, self.off_loc, self.y, self.H,
-                                w.inter // 128, self.e_loc)
+        if self.transport == "peer":
+            # the down projection writes every row straight into the return buffer of the rank it came from
+            check(lib.i4tc_moe_ep_return_rows(self.pos_of.data_ptr(), self.r_max, self.H, self.ret_bases.data_ptr(),
+                                              self.meta.data_ptr(), self.world, self.e_loc, self.cap,
+                                              self.out_rows.data_ptr(), d, st), "moe_ep_return_rows")
+            m.moe_w4a4_grouped_gemm_rows(self.hp, self.hs, w.down_packed, w.down_scale, self.off_loc, self.out_rows,
+                                         self.H, w.inter // 128, self.e_loc)
+        else:
+            m.moe_w4a4_grouped_gemm(self.hp, self.hs, w.down_packed, w.down_scale, self.off_loc, self.y, self.H,
+                                    w.inter // 128, self.e_loc)
 
     def _pack_return(self):
         from ._cabi import check
         lib, d, st = self._lib, self.dev.index, torch.cuda.current_stream(self.dev).cuda_stream
         if self.transport == "peer":
-            check(lib.i4tc_moe_ep_pack_return(self.y.data_ptr(), self.pos_of.data_ptr(), self.r_max, self.H, None,
-                                              self.ret_bases.data_ptr(), self.meta.data_ptr(), self.world, self.e_loc,
-                                              self.cap, d, st), "moe_ep_pack_return")
+            return   # the down projection already stored the rows where they belong
         else:
             check(lib.i4tc_moe_ep_pack_return(self.y.data_ptr(), self.pos_of.data_ptr(), self.r_max, self.H,
                                               self.ret_send.data_ptr(), None, None, 0, 0, 0, d, st), "moe_ep_pack_return")
@@ -424,7 +431,7 @@ class ExpertParallelMoE:
             yield "wait_rows", lambda: self._wait(self.flags_dispatch)
             yield "unpack", self._unpack
             yield "experts", self._experts
-            yield "return_store", lambda: (self._pack_return(), self._signal(self.flag_addrs_return, False))
+            yield "return_signal", lambda: self._signal(self.flag_addrs_return, False)
             yield "wait_returns", lambda: self._wait(self.flags_return)
             yield "combine", lambda: self._moe.moe_combine(self.ret_local, self.inv_pairs, expert_w.contiguous(), self.T, self.k)
             return

@@ -271,6 +271,14 @@ int i4tc_moe_grouped_gemm(const uint8_t* a, const float* scale_a, const uint8_t*
                           const float* scale_b, const int32_t* expert_offsets, void* out,
                           int64_t num_pairs, int64_t N, int64_t num_groups,
                           int64_t num_experts, int device, void* stream);
+/* The same GEMM with every output row written to its own address (out_rows [num_pairs], device array of 16-byte aligned
+ * addresses, N bf16 values each) instead of out + row * N: the expert-parallel layer lets the down projection write
+ * straight into the return buffers of the ranks the rows came from (i4tc_moe_ep_return_rows builds the table; rows in
+ * another GPU's memory are reached with plain stores over NVLink).  N must be a multiple of 8.  No reference counterpart. */
+int i4tc_moe_grouped_gemm_rows(const uint8_t* a, const float* scale_a, const uint8_t* b,
+                               const float* scale_b, const int32_t* expert_offsets, const uint64_t* out_rows,
+                               int64_t num_pairs, int64_t N, int64_t num_groups, int64_t num_experts,
+                               int device, void* stream);
 
 /* RMSNorm fused in front of the grouped quantiser: for every row of x (bf16 [rows, K], row stride ldx)
  *   y = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * norm_weight[k]),  then y is quantised like i4tc_quant_grouped
@@ -344,6 +352,12 @@ int i4tc_moe_silu_mul_quant_rows(const void* h, int64_t max_rows, const int32_t*
 int i4tc_moe_ep_pack_return(const void* y, const int32_t* pos_of, int64_t rows, int64_t H, void* ret_send,
                             const uint64_t* peer_bases, const int32_t* meta, int64_t world, int64_t e_loc,
                             int64_t cap, int device, void* stream);
+/* out_rows [world * cap] (device): for every expert-sorted row of this rank the address of its place in the return
+ * buffer of the rank it came from (peer_bases, meta, geometry as for i4tc_moe_ep_pack_return), for
+ * i4tc_moe_grouped_gemm_rows; entries of positions that hold no row are left alone.  No reference counterpart. */
+int i4tc_moe_ep_return_rows(const int32_t* pos_of, int64_t rows, int64_t H, const uint64_t* peer_bases,
+                            const int32_t* meta, int64_t world, int64_t e_loc, int64_t cap, uint64_t* out_rows,
+                            int device, void* stream);
 
 /* out[t, :] = bf16( sum_j w[t, j] * y[inv_pairs[t*top_k + j], :] ), j ascending, fp32 sum.
  * y bf16 [P, H]; inv_pairs[pair] = sorted position of that pair. */

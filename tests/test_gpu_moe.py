@@ -153,6 +153,36 @@ def test_grouped_gemm_per_expert(moe, ops, tile_n):
     assert torch.equal(out.cpu(), ref)
 
 
+@pytest.mark.parametrize("tile_n", [0, 128])
+def test_grouped_gemm_rows_through_address_table(moe, ops, tile_n):
+    """Every output row goes to its own address (a permutation of the rows of a wider buffer here): the same bits as
+    the plain grouped GEMM, nothing written anywhere else."""
+    rng = np.random.RandomState(11)
+    E, G, N = 5, 2, 384
+    counts = [3, 200, 0, 129, 70]
+    off = np.zeros(E + 1, np.int32)
+    off[1:] = np.cumsum(counts)
+    P = int(off[-1])
+    a = torch.from_numpy(O.pack_int4(rng.randint(-8, 8, size=(G, P, 128)).astype(np.int8))).cuda()
+    b = torch.from_numpy(O.pack_int4(rng.randint(-8, 8, size=(E, G, N, 128)).astype(np.int8))).cuda()
+    sa = torch.from_numpy((rng.rand(G, P).astype(np.float32) + 0.01) * 0.1).cuda()
+    sb = torch.from_numpy((rng.rand(E, G, N).astype(np.float32) + 0.01) * 0.01).cuda()
+    offd = torch.from_numpy(off).cuda()
+    ops.set_tuning(tile_n, -1)
+    plain = torch.empty(P, N, dtype=torch.bfloat16, device="cuda")
+    moe.moe_w4a4_grouped_gemm(a, sa, b, sb, offd, plain, N, G, E)
+    ld = N + 64                                     # rows of a wider buffer, in a shuffled order
+    wide = torch.full((P + 3, ld), float("nan"), dtype=torch.bfloat16, device="cuda")
+    perm = torch.from_numpy(rng.permutation(P + 3)[:P].astype(np.int64)).cuda()
+    rows = wide.data_ptr() + perm * (ld * 2)
+    moe.moe_w4a4_grouped_gemm_rows(a, sa, b, sb, offd, rows.contiguous(), N, G, E)
+    ops.check_status()
+    assert torch.equal(wide[perm, :N], plain)
+    untouched = torch.ones(P + 3, dtype=torch.bool, device="cuda")
+    untouched[perm] = False
+    assert torch.isnan(wide[untouched].float()).all() and torch.isnan(wide[:, N:].float()).all()
+
+
 def _layer_case(moe, T, H, I, E, k, seed):
     from fp8_inference_toolkit_b200 import synthetic
 
