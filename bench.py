@@ -446,6 +446,7 @@ def run_ours(args) -> None:
             big = [r for r in sweep if r["M"] >= 1024]
             line["roofline"]["sweep_min_frac_int8_peak_m1024_up"] = min(r["frac_int8_peak"] for r in big)
             line["roofline"]["sweep_min_frac_hbm_m1"] = min(r["frac_hbm"] for r in sweep if r["M"] == 1)
+            line["roofline"]["sweep_min_frac_hbm_m16"] = min(r["frac_hbm"] for r in sweep if r["M"] == 16)
         # the other north-star workloads, smallest objects last so that they survive a truncated log
         if moe_weak is not None:
             line["moe_weak"] = moe_weak

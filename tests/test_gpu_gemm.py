@@ -157,8 +157,9 @@ def test_cta_pairs_grouped(tc, ops, M, N, G):
 @pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 13, 16])
 @pytest.mark.parametrize("N,G", [(100, 3), (4096, 32), (257, 96)])
 def test_small_m_weight_streaming(tc, ops, M, N, G):
-    """A handful of tokens take the CUDA-core weight-streaming kernel (automatic choice): per-channel results are
-    bit-identical to the oracle, per-group results within the tolerance, and both agree with the tensor-core path."""
+    """A handful of tokens take a weight-streaming kernel (automatic choice: CUDA cores for one or two tokens, the
+    register-fed tensor-core kernel from three on): per-channel results are bit-identical to the oracle, per-group
+    results within the tolerance, and both agree with the tile kernel."""
     rng = np.random.RandomState(M * 7 + N + G)
     K = G * 128
     a, b = rand_codes(rng, (G, M, 128)), rand_codes(rng, (G, N, 128))
@@ -222,6 +223,31 @@ def test_small_m_register_fed_kernel(tc, ops, M, N, G):
     finally:
         ops.set_small_m_path(0)
     assert (outs[2] - outs[3]).abs().max() <= 2e-2 * outs[3].abs().max() + 1e-6
+
+
+def test_small_m_kernel_with_scales_that_are_only_4_byte_aligned(tc, ops):
+    """The register-fed kernel brings the weight scales in with 16-byte bulk copies when it can; scales that start on
+    an odd float fall back to plain loads, with the same result."""
+    rng = np.random.RandomState(3)
+    M, N, G = 12, 256, 8
+    a, b = rand_codes(rng, (G, M, 128)), rand_codes(rng, (G, N, 128))
+    sa = (rng.rand(G, M).astype(np.float32) + 0.01) * 0.1
+    sb = (rng.rand(G, N).astype(np.float32) + 0.01) * 0.01
+    ref = O.linear_grouped(a, b, sa, sb)
+    buf = torch.zeros(G * N + 1, dtype=torch.float32, device="cuda")
+    sb_odd = buf[1:].view(G, N)
+    sb_odd.copy_(torch.from_numpy(sb))
+    assert sb_odd.data_ptr() % 16 == 4
+    outs = []
+    for scale_b in (dev_f32(sb), sb_odd):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        tc.cutlass_int4_fused_grouped_gemm(dev_packed(a), dev_packed(b), dev_f32(sa), scale_b, out, M, N, 128, G)
+        ops.check_status()
+        assert_close_bf16(out, ref, "odd scale alignment")
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    with pytest.raises(RuntimeError):
+        ops.set_small_m_path(7)
 
 
 def test_config0_end_to_end(tc, ops):
