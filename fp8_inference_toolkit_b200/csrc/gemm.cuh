@@ -80,7 +80,7 @@ int launch_w4a4_gemv(const uint8_t* x, const uint8_t* w, const float* sx, const 
 
 // Register-fed tensor-core weight-streaming kernel for M <= 32 tokens (same operands and outputs as the kernel above;
 // `status` is the device status word that a bounded wait flags).
-bool skinny_applicable(long long M, long long N, long long K, int epi_mode, int sm_count);
+bool skinny_applicable(long long M, long long N, long long K, int epi_mode, bool rowmajor, int sm_count);
 int launch_w4a4_skinny(const uint8_t* x, const uint8_t* w, const float* sx, const float* sw, void* out, int out_dtype,
                        long long M, long long N, int G, bool rowmajor, int epi_mode, int sm_count, unsigned int* status,
                        cudaStream_t st);

@@ -116,7 +116,7 @@ static int run_dense(const DenseArgs& d, int device, void* stream) {
     const int path = g_small_m_path.load();
     const long long K = (long long)d.G * 128;
     const bool gemv_ok = path != 3 && path != 2 && gemv_applicable(d.M, d.N, K, d.epi_mode);
-    const bool skinny_ok = path != 3 && path != 1 && skinny_applicable(d.M, d.N, K, d.epi_mode, info->sm_count);
+    const bool skinny_ok = path != 3 && path != 1 && skinny_applicable(d.M, d.N, K, d.epi_mode, d.rowmajor, info->sm_count);
     // one or two tokens: dp4a on the CUDA cores does not waste tensor-core columns; from three on the tensor cores win
     if (skinny_ok && (path == 2 || !gemv_ok || d.M > 2))
       return launch_w4a4_skinny(d.a, d.b, d.sa, d.sb, d.out, d.out_dtype, d.M, d.N, d.G, d.rowmajor, d.epi_mode,

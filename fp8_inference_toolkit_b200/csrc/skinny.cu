@@ -42,6 +42,7 @@ struct SkinnyParams {
   long long x_row, x_grp;   // byte strides of the activations: token, K group
   long long w_row, w_grp;   // byte strides of the weights: row, K group
   int rowmajor;
+  int rstride;        // row-major operands: bytes between rows in shared memory (a warp's K range plus padding)
   int out_fp16;
   unsigned int* status;     // bit 0 is set when a bounded wait expires
 };
@@ -111,11 +112,19 @@ __global__ void __launch_bounds__(skinny_warps(MTILES) * 32) w4a4_skinny_kernel(
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * ROWS;
   const int g0 = min(p.G, warp * p.gper), g1 = min(p.G, g0 + p.gper), gw = g1 - g0;
-  const size_t item_bytes = (size_t)nwarps * p.gper * ITEM;
+  // Group-major operands: one item per K group ([ROWS][64] codes, then the staged tokens and scales).  Row-major operands
+  // ([rows, K/2]): a warp's K range of one row is contiguous, so each row arrives as one copy of gw * 64 bytes and rows
+  // lie `rstride` bytes apart (= 64 mod 128, so that eight rows x four 16-byte chunks hit distinct banks).
+  const bool rm = p.rowmajor != 0;
+  const int rs = rm ? p.rstride : 64;                  // bytes between rows of one K group
+  const int gstep = rm ? 64 : ITEM;                    // bytes between K groups
+  const int tok_off = rm ? ROWS * p.rstride : CHUNK;   // where the staged tokens' codes start
+  const size_t region = rm ? (size_t)(ROWS + (STAGE ? TOK : 0)) * p.rstride : (size_t)p.gper * ITEM;
+  const size_t item_bytes = (size_t)nwarps * region;
   const size_t sx_bytes = (STAGE && PER_GROUP) ? (size_t)nwarps * p.gper * TOK * 4 : 0;
   const size_t red_bytes = (size_t)nwarps * TOK * ROWS * 4;
   const size_t data_bytes = item_bytes + sx_bytes > red_bytes ? item_bytes + sx_bytes : red_bytes;
-  uint8_t* wsm = smem + (size_t)warp * p.gper * ITEM;
+  uint8_t* wsm = smem + (size_t)warp * region;
   float* sx_s = reinterpret_cast<float*>(smem + item_bytes) + (size_t)warp * p.gper * TOK;
   const uint32_t bars = smem_u32(smem + data_bytes) + (uint32_t)warp * kMaxGroupsPerWarp * 8u;
 
@@ -123,39 +132,43 @@ __global__ void __launch_bounds__(skinny_warps(MTILES) * 32) w4a4_skinny_kernel(
   if (lane < gw) mbar_init(bars + lane * 8u, 1);
   fence_mbar_init();
   __syncwarp();
-  const uint32_t tx = CHUNK + (STAGE ? (uint32_t)p.M * 64u + (PER_GROUP ? ROWS * 4u : 0u) : 0u);
-  if (lane < gw) {
-    const uint32_t bar = bars + lane * 8u, dst = smem_u32(wsm) + lane * ITEM;
-    const int grp = g0 + lane;
-    mbar_arrive_expect_tx(bar, tx);
-    // group-major operands: the block's rows (and all tokens) of one group are contiguous
-    if (!p.rowmajor) bulk_load(dst, p.w + (long long)grp * p.w_grp + (long long)n0 * 64, CHUNK, bar);
-    if (STAGE) {
-      if (!p.rowmajor) bulk_load(dst + CHUNK, p.x + (long long)grp * p.x_grp, (uint32_t)p.M * 64u, bar);
-      if (PER_GROUP) bulk_load(dst + CHUNK + TOK * 64, p.sw + (long long)grp * p.N + n0, ROWS * 4, bar);
-    }
-  }
-  if (p.rowmajor) {
-    __syncwarp();
-    for (int i = lane; i < gw * ROWS; i += 32) {
-      const int gi = i / ROWS, r = i - gi * ROWS;
-      bulk_load(smem_u32(wsm) + gi * ITEM + r * 64, p.w + (long long)(n0 + r) * p.w_row + (long long)(g0 + gi) * 64, 64,
-                bars + gi * 8u);
-    }
-    if (STAGE) {
-      for (int i = lane; i < gw * p.M; i += 32) {
-        const int gi = i / p.M, m = i - gi * p.M;
-        bulk_load(smem_u32(wsm) + gi * ITEM + CHUNK + m * 64, p.x + (long long)m * p.x_row + (long long)(g0 + gi) * 64, 64,
-                  bars + gi * 8u);
+  if (!rm) {
+    const uint32_t tx = CHUNK + (STAGE ? (uint32_t)p.M * 64u + (PER_GROUP ? ROWS * 4u : 0u) : 0u);
+    if (lane < gw) {
+      const uint32_t bar = bars + lane * 8u, dst = smem_u32(wsm) + lane * ITEM;
+      const int grp = g0 + lane;
+      mbar_arrive_expect_tx(bar, tx);
+      // the block's rows (and all tokens) of one group are contiguous
+      bulk_load(dst, p.w + (long long)grp * p.w_grp + (long long)n0 * 64, CHUNK, bar);
+      if (STAGE) {
+        bulk_load(dst + CHUNK, p.x + (long long)grp * p.x_grp, (uint32_t)p.M * 64u, bar);
+        if (PER_GROUP) bulk_load(dst + CHUNK + TOK * 64, p.sw + (long long)grp * p.N + n0, ROWS * 4, bar);
       }
+    }
+  } else if (gw > 0) {
+    // everything of this warp on its first barrier: one copy per weight row (and per staged token)
+    if (lane == 0) mbar_arrive_expect_tx(bars, (uint32_t)(ROWS + (STAGE ? p.M : 0)) * (uint32_t)gw * 64u);
+    __syncwarp();
+    for (int r = lane; r < ROWS; r += 32)
+      bulk_load(smem_u32(wsm) + r * rs, p.w + (long long)(n0 + r) * p.w_row + (long long)g0 * 64, (uint32_t)gw * 64u, bars);
+    if (STAGE) {
+      for (int m = lane; m < p.M; m += 32)
+        bulk_load(smem_u32(wsm) + tok_off + m * rs, p.x + (long long)m * p.x_row + (long long)g0 * 64, (uint32_t)gw * 64u, bars);
     }
   }
   if (STAGE) {
     // padding tokens: zero codes; token scales with the 2^-8 folded in
     const int pad = TOK - p.M;
-    for (int i = lane; i < gw * pad * 4; i += 32) {
-      const int gi = i / (pad * 4), r = i - gi * (pad * 4);
-      *reinterpret_cast<uint4*>(wsm + (size_t)gi * ITEM + CHUNK + (size_t)p.M * 64 + (size_t)r * 16) = make_uint4(0u, 0u, 0u, 0u);
+    if (!rm) {
+      for (int i = lane; i < gw * pad * 4; i += 32) {
+        const int gi = i / (pad * 4), r = i - gi * (pad * 4);
+        *reinterpret_cast<uint4*>(wsm + (size_t)gi * ITEM + CHUNK + (size_t)p.M * 64 + (size_t)r * 16) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    } else {
+      for (int i = lane; i < pad * gw * 4; i += 32) {
+        const int r = i / (gw * 4), c = i - r * (gw * 4);
+        *reinterpret_cast<uint4*>(wsm + tok_off + (size_t)(p.M + r) * rs + (size_t)c * 16) = make_uint4(0u, 0u, 0u, 0u);
+      }
     }
     if (PER_GROUP) {
       for (int i = lane; i < gw * TOK; i += 32) {
@@ -214,14 +227,14 @@ __global__ void __launch_bounds__(skinny_warps(MTILES) * 32) w4a4_skinny_kernel(
       for (int mt = 0; mt < MTILES; ++mt) { sw_c[mt][0] = sws[mt][0]; sw_c[mt][1] = sws[mt][1]; }
       if (gi + 1 < gw) fetch(g0 + gi + 1);
     }
-    alive = wait_landed(bars + gi * 8u, p.status);
+    alive = wait_landed(bars + (rm ? 0 : gi) * 8u, p.status);
     alive = __all_sync(0xffffffffu, alive);
     if (!alive) break;
-    const uint32_t item = smem_u32(wsm) + gi * ITEM;
+    const uint32_t item = smem_u32(wsm) + gi * gstep;
     if (STAGE) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const uint4 xv = lds128(item + CHUNK + (8 * nt + g) * 64 + t * 16);
+        const uint4 xv = lds128(item + tok_off + (8 * nt + g) * rs + t * 16);
         expand4(xv, blo[nt], bhi[nt]);
         if (PER_GROUP) {
           const float2 s2 = *reinterpret_cast<const float2*>(sx_s + gi * TOK + 8 * nt + 2 * t);
@@ -236,11 +249,11 @@ __global__ void __launch_bounds__(skinny_warps(MTILES) * 32) w4a4_skinny_kernel(
         }
       }
     }
-    const uint32_t base = item + g * 64 + t * 16;
+    const uint32_t base = item + g * rs + t * 16;
 #pragma unroll
     for (int mt = 0; mt < MTILES; ++mt) {
-      const uint4 ra = lds128(base + mt * 1024);
-      const uint4 rb = lds128(base + mt * 1024 + 512);
+      const uint4 ra = lds128(base + mt * 16 * rs);
+      const uint4 rb = lds128(base + mt * 16 * rs + 8 * rs);
       uint32_t alo[4], ahi[4], a8lo[4], a8hi[4];
       expand4(ra, alo, ahi);
       expand4(rb, a8lo, a8hi);
@@ -304,8 +317,12 @@ __global__ void __launch_bounds__(skinny_warps(MTILES) * 32) w4a4_skinny_kernel(
   }
 }
 
-size_t skinny_smem(int warps, int rows, int nt, int gper, bool per_group, bool stage) {
-  const size_t item_bytes = (size_t)warps * gper * skinny_item(rows, 8 * nt, stage);
+int skinny_rstride(int gper) { return gper * 64 + ((gper % 2 == 0) ? 64 : 0); }
+
+size_t skinny_smem(int warps, int rows, int nt, int gper, bool per_group, bool stage, bool rowmajor) {
+  const size_t region = rowmajor ? (size_t)(rows + (stage ? 8 * nt : 0)) * skinny_rstride(gper)
+                                 : (size_t)gper * skinny_item(rows, 8 * nt, stage);
+  const size_t item_bytes = (size_t)warps * region;
   const size_t sx_bytes = (stage && per_group) ? (size_t)warps * gper * 8 * nt * 4 : 0;
   const size_t red_bytes = (size_t)warps * (8 * nt) * rows * 4;
   return (item_bytes + sx_bytes > red_bytes ? item_bytes + sx_bytes : red_bytes) + (size_t)warps * kMaxGroupsPerWarp * 8;
@@ -350,7 +367,7 @@ struct SkinnyPlan {
 
 // Rows per block: 32 when that still gives every SM two blocks (and there are at most 16 tokens), else 16.  The tokens are staged in shared memory when
 // at least two blocks still fit an SM.
-SkinnyPlan skinny_plan(long long M, long long N, long long K, bool per_group, int sm_count) {
+SkinnyPlan skinny_plan(long long M, long long N, long long K, bool per_group, bool rowmajor, int sm_count) {
   SkinnyPlan pl;
   const int G = (int)(K / 128), nt = (int)((M + 7) / 8);
   for (int rows : {32, 16}) {
@@ -359,8 +376,9 @@ SkinnyPlan skinny_plan(long long M, long long N, long long K, bool per_group, in
     const int warps = skinny_warps(rows / 16);
     const int gper = (G + warps - 1) / warps;
     if (gper > kMaxGroupsPerWarp) continue;
-    const size_t staged = skinny_smem(warps, rows, nt, gper, per_group, true);
-    const size_t plain = skinny_smem(warps, rows, nt, gper, per_group, false);
+    // (row-major operands with per-group scales: no call site; the scales would need a layout of their own)
+    const size_t staged = (rowmajor && per_group) ? (size_t)-1 : skinny_smem(warps, rows, nt, gper, per_group, true, rowmajor);
+    const size_t plain = skinny_smem(warps, rows, nt, gper, per_group, false, rowmajor);
     pl.warps = warps;
     pl.gper = gper;
     if (staged <= 110 * 1024) {
@@ -377,10 +395,12 @@ SkinnyPlan skinny_plan(long long M, long long N, long long K, bool per_group, in
 
 }  // namespace
 
-bool skinny_applicable(long long M, long long N, long long K, int epi_mode, int sm_count) {
+bool skinny_applicable(long long M, long long N, long long K, int epi_mode, bool rowmajor, int sm_count) {
   if (M < 1 || M > 32 || N < 16 || K < 128 || K % 128 != 0 || K > 65536) return false;
   if (epi_mode != EPI_GROUP && epi_mode != EPI_CHANNEL) return false;
-  return skinny_plan(M, N, K, epi_mode == EPI_GROUP, sm_count).rows != 0;
+  // per-channel scales: the tile kernel has no per-group drain and is the faster one beyond 16 tokens (measured)
+  if (epi_mode == EPI_CHANNEL && M > 16) return false;
+  return skinny_plan(M, N, K, epi_mode == EPI_GROUP, rowmajor, sm_count).rows != 0;
 }
 
 int launch_w4a4_skinny(const uint8_t* x, const uint8_t* w, const float* sx, const float* sw, void* out, int out_dtype,
@@ -399,14 +419,15 @@ int launch_w4a4_skinny(const uint8_t* x, const uint8_t* w, const float* sx, cons
   p.status = status;
   I4TC_REQUIRE(aligned_to(x, 16) && aligned_to(w, 16), I4TC_EALIGN, "packed operands must be 16-byte aligned");
   const bool pg = epi_mode == EPI_GROUP;
-  SkinnyPlan pl = skinny_plan(M, N, (long long)G * 128, pg, sm_count);
+  SkinnyPlan pl = skinny_plan(M, N, (long long)G * 128, pg, rowmajor, sm_count);
   I4TC_REQUIRE(pl.rows != 0, I4TC_EINVAL, "shape not supported by the small-batch kernel");
   const int nt = (int)((M + 7) / 8);
   p.gper = pl.gper;
+  p.rstride = skinny_rstride(pl.gper);
   p.warps = pl.warps;
   if (pl.stage && pg && !aligned_to(sw, 16)) {   // the bulk copy of the row scales needs 16-byte alignment
     pl.stage = false;
-    pl.smem = skinny_smem(pl.warps, pl.rows, nt, pl.gper, pg, false);
+    pl.smem = skinny_smem(pl.warps, pl.rows, nt, pl.gper, pg, false, rowmajor);
   }
 #define I4TC_SKINNY_CASE(MT_, PG_, ST_) \
   if (pl.rows == 16 * MT_ && pg == PG_ && pl.stage == ST_) return launch_nt<MT_, PG_, ST_>(p, nt, pl.smem, st);

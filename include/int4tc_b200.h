@@ -90,7 +90,8 @@ int i4tc_set_cta_pairs(int mode);
 int i4tc_set_epilogue_warps(int warps);
 
 /* Test / tuning hook: which kernel serves a linear with few tokens (0 = automatic: the CUDA-core weight-streaming
- * kernel for one or two tokens, the register-fed tensor-core one up to 32, the tile kernel beyond; 1 = the CUDA-core kernel
+ * kernel for one or two tokens, the register-fed tensor-core one up to 32 (16 with per-channel scales), the tile kernel
+ * beyond; 1 = the CUDA-core kernel
  * where it applies, else the tile kernel; 2 = the register-fed kernel wherever it applies (1..32 tokens); 3 = always
  * the tile kernel).  Process-wide.  Per-channel results do not depend on it; per-group results differ only in the
  * order in which fp32 partial sums over K ranges are added.  No reference counterpart. */
