@@ -166,6 +166,7 @@ __device__ __forceinline__ uint32_t pack8(const Vec8<T>& x, const Recip& q, bool
   const float2 r2 = make_float2(q.r, q.r), eight = make_float2(8.f, 8.f), mg = make_float2(kMagic, kMagic);
   const float2 nmg = make_float2(-kMagic, -kMagic);
   float2 v[4];  // v[i] = (n_i + 8, n_{i+4} + 8)
+  float2 e[CLAMP ? 4 : 1];   // CLAMP: e[i] = y8 - v[i] (exact), kept for the rare path
   float worst = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -175,20 +176,25 @@ __device__ __forceinline__ uint32_t pack8(const Vec8<T>& x, const Recip& q, bool
       y8.y = fminf(fmaxf(y8.y, 0.0f), 15.0f);
     }
     v[i] = __fadd2_rn(__fadd2_rn(y8, mg), nmg);
-    const float2 e = __ffma2_rn(v[i], make_float2(-1.f, -1.f), y8);
-    worst = fmaxf(worst, fmaxf(fabsf(e.x), fabsf(e.y)));
+    const float2 d = __ffma2_rn(v[i], make_float2(-1.f, -1.f), y8);
+    if (CLAMP) e[i] = d;
+    worst = fmaxf(worst, fmaxf(fabsf(d.x), fabsf(d.y)));
   }
   if (!(worst <= kThr)) {
+    // rare: some element sits on a rounding boundary
     const float s = exact_divisor<!CLAMP>(q);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      float y0 = fmaf(x.get(i), q.r, 8.0f), y1 = fmaf(x.get(i + 4), q.r, 8.0f);
       if (CLAMP) {
-        y0 = fminf(fmaxf(y0, 0.0f), 15.0f);
-        y1 = fminf(fmaxf(y1, 0.0f), 15.0f);
+        // y8 = v + e exactly (v is y8 rounded to an integer, e the exact remainder): nothing is recomputed
+        if (!(fabsf(e[i].x) <= kThr)) v[i].x = exact_tie_code8(x.get(i), v[i].x + e[i].x, s);
+        if (!(fabsf(e[i].y) <= kThr)) v[i].y = exact_tie_code8(x.get(i + 4), v[i].y + e[i].y, s);
+      } else {
+        // (the absmax kernels run at four blocks per SM with 64 registers: recomputing is cheaper than keeping e)
+        const float y0 = fmaf(x.get(i), q.r, 8.0f), y1 = fmaf(x.get(i + 4), q.r, 8.0f);
+        if (!(fabsf(y0 - v[i].x) <= kThr)) v[i].x = exact_tie_code8(x.get(i), y0, s);
+        if (!(fabsf(y1 - v[i].y) <= kThr)) v[i].y = exact_tie_code8(x.get(i + 4), y1, s);
       }
-      if (!(fabsf(y0 - v[i].x) <= kThr)) v[i].x = exact_tie_code8(x.get(i), y0, s);
-      if (!(fabsf(y1 - v[i].y) <= kThr)) v[i].y = exact_tie_code8(x.get(i + 4), y1, s);
     }
   }
   // (lo, hi) = v0 + 16 v1 + 256 v2 + 4096 v3 for elements 0..3 and 4..7: exact, below 2^16
