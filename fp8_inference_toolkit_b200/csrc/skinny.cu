@@ -1,10 +1,10 @@
-// W4A4 linear for a few dozen tokens (M <= 32): weight streaming through register-fed tensor-core instructions.
+// W4A4 linear for 3 to 32 tokens: weight streaming through register-fed tensor-core instructions.
 //
 // At these sizes the op moves half a byte per 2 M operations, far below the machine balance, so the only thing that
 // counts is how many weight bytes are in flight.  The tile kernel (TMA -> converter warps -> tcgen05 -> TMEM drain) is a
 // chain of per-group handshakes with a handful of stages per SM; here a thread block asks for ALL of its bytes
-// at once (cp.async.bulk, one mbarrier per warp and K group: the weight rows and, where they fit, the tokens' codes
-// and the scales), several blocks share an SM, and nothing waits on another role: a warp expands the nibbles of its
+// at once (cp.async.bulk, one mbarrier per warp and K group -- per warp for row-major operands, where a row's K range is
+// one copy: the weight rows and, where they fit, the tokens' codes and the scales), several blocks share an SM, and nothing waits on another role: a warp expands the nibbles of its
 // K groups in registers, multiplies them with mma.sync.m16n8k32 (int8, int32 accumulators in registers) and applies
 // the group's scales in registers.
 //
