@@ -217,6 +217,20 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((kBM * CG) >> 4) << 24);
 }
 
+// Row order of a converted Q tile.  After tcgen05.ld.16x256b a lane (lr, lq) holds, of every 32-column chunk, the column
+// pairs 8 kk + 2 lq + {0, 1}, kk = 0..3.  The converters therefore store Q row n of a 32-row block at row
+// qperm(n) = 8 * ((n >> 1) & 3) + 2 * (n >> 3) + (n & 1): accumulator column 8 kk + 2 lq + e is then output column
+// 8 lq + 2 kk + e, a lane's four pairs are eight CONSECUTIVE output columns, and a chunk row leaves as one 16-byte store
+// per lane with no exchange between lanes (a 4 x 4 transpose in the quad costs 4 shuffles and 16 selects per chunk row).
+// The map is its own inverse.  Tiles that reach shared memory without the converters (int8 operands) keep the
+// natural order (QP = false below).
+__host__ __device__ constexpr int qperm(int n) {
+  return (n & ~31) | (((n >> 1) & 3) << 3) | (((n >> 3) & 3) << 1) | (n & 1);
+}
+// first of the two output columns (inside a 32-column chunk) of a lane's pair kk
+template <bool QP>
+__device__ __forceinline__ constexpr int pair_col(int kk, int lq) { return QP ? lq * 8 + kk * 2 : kk * 8 + lq * 2; }
+
 // Expand the packed P tile (ROWS_P x 64 B, dense) and Q tile (ROWS_Q x 64 B) of one stage into swizzled int8 tiles
 // (rows x 128 B).  16-byte packed chunk j of a row becomes int8 chunks 2j (even codes) and 2j+1 (odd codes).
 // The two tiles are walked as one list of chunks, up to six loads in flight per thread, so that a narrow stage
@@ -240,7 +254,7 @@ __device__ __forceinline__ void convert_stage(uint32_t pkP, uint32_t i8P, uint32
       const int c = i0 + i;
       if (c < T) {
         const int q = tid + (c < TP ? c : c - TP) * NT;
-        const int row = q >> 2, j = q & 3;
+        const int row = (c < TP) ? (q >> 2) : qperm(q >> 2), j = q & 3;   // Q rows in the order the epilogue wants
         uint4 lo, hi;
         lo.x = (w[i].x << 4) & 0xF0F0F0F0u; hi.x = w[i].x & 0xF0F0F0F0u;
         lo.y = (w[i].y << 4) & 0xF0F0F0F0u; hi.y = w[i].y & 0xF0F0F0F0u;
@@ -270,22 +284,23 @@ __device__ __forceinline__ void store_chunk_i(const GemmParams& p, int32_t* out,
   if (!p.swap) {
     int32_t* dst = out + (long long)prow * p.ldc + qcol0;
     const bool vec = (qcol0 + 32 <= ti.q_lim) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+    // accumulator column i of the chunk is output column qperm(i); output columns n .. n + 3 are r[qperm(n .. n + 3)]
     if (vec) {
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        int4 o = make_int4(((int32_t)r[i]) >> 8, ((int32_t)r[i + 1]) >> 8, ((int32_t)r[i + 2]) >> 8,
-                           ((int32_t)r[i + 3]) >> 8);
-        *reinterpret_cast<int4*>(dst + i) = o;
+      for (int n = 0; n < 32; n += 4) {
+        int4 o = make_int4(((int32_t)r[qperm(n)]) >> 8, ((int32_t)r[qperm(n + 1)]) >> 8, ((int32_t)r[qperm(n + 2)]) >> 8,
+                           ((int32_t)r[qperm(n + 3)]) >> 8);
+        *reinterpret_cast<int4*>(dst + n) = o;
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (qcol0 + i < ti.q_lim) dst[i] = ((int32_t)r[i]) >> 8;
+      for (int n = 0; n < 32; ++n)
+        if (qcol0 + n < ti.q_lim) dst[n] = ((int32_t)r[qperm(n)]) >> 8;
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (qcol0 + i < ti.q_lim) out[(long long)(qcol0 + i) * p.ldc + prow] = ((int32_t)r[i]) >> 8;
+    for (int n = 0; n < 32; ++n)
+      if (qcol0 + n < ti.q_lim) out[(long long)(qcol0 + n) * p.ldc + prow] = ((int32_t)r[qperm(n)]) >> 8;
   }
 }
 
@@ -441,9 +456,9 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
         const uint32_t (&r)[16] = rb[PIPE ? (u & 1) : 0];
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          const float2 sq = *reinterpret_cast<const float2*>(st_q + c * 32 + kk * 8 + lq * 2);
+          const float2 sq = *reinterpret_cast<const float2*>(st_q + c * 32 + pair_col<true>(kk, lq));
           float2 zq = make_float2(0.f, 0.f);
-          if (AZP) zq = *reinterpret_cast<const float2*>(st_q + (kBM + BN) + c * 32 + kk * 8 + lq * 2);
+          if (AZP) zq = *reinterpret_cast<const float2*>(st_q + (kBM + BN) + c * 32 + pair_col<true>(kk, lq));
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int a = sl * 2 + h;
@@ -481,10 +496,9 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
           rowp = (orows != nullptr) ? reinterpret_cast<OutT*>(orows[prow]) : out + (long long)prow * p.ldc;
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
-          uint32_t x[4];
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) x[kk] = pack_pair<OutT>(f[(a * NCH + c) * 4 + kk]);
-          const uint4 y = quad_transpose(x, lq);
+          // a lane's four pairs of a chunk are eight consecutive output columns (see qperm)
+          const uint4 y = make_uint4(pack_pair<OutT>(f[(a * NCH + c) * 4 + 0]), pack_pair<OutT>(f[(a * NCH + c) * 4 + 1]),
+                                     pack_pair<OutT>(f[(a * NCH + c) * 4 + 2]), pack_pair<OutT>(f[(a * NCH + c) * 4 + 3]));
           if (prow < ti.p_lim) *reinterpret_cast<uint4*>(rowp + ti.q0 + col_base + c * 32 + lq * 8) = y;
         }
       }
@@ -502,7 +516,7 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const float2 v = f[(a * NCH + c) * 4 + kk];
-            const int q = ti.q0 + col_base + c * 32 + kk * 8 + lq * 2;
+            const int q = ti.q0 + col_base + c * 32 + pair_col<true>(kk, lq);
             if (ws != nullptr) {
               // split-K: fp32 partial sums of this K range, element (m, n) at ws[split][m * ldc + n]
               if (!SWAP) {
@@ -525,7 +539,7 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
 
 // One flush per tile with per-channel scales: out = cast((acc * scale_b[n]) * scale_a[m]), the
 // reference's order.  Same slab register layout and quad-transposed stores as the per-group epilogue.
-template <int BN, typename OutT, bool SWAP, int CG, int EW>
+template <int BN, typename OutT, bool SWAP, int CG, int EW, bool QP>
 __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* smem, uint32_t tmem_base,
                                                  uint32_t bar_tm_full, uint32_t bar_tm_empty,
                                                  volatile int* abort_flag) {
@@ -594,7 +608,7 @@ __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* s
           if (prow >= ti.p_lim) continue;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            const int q = ti.q0 + col_base + c * 32 + kk * 8 + lq * 2;
+            const int q = ti.q0 + col_base + c * 32 + pair_col<QP>(kk, lq);
             const float d0 = __int2float_rn((int32_t)r[4 * kk + 2 * h]) * kInv256;
             const float d1 = __int2float_rn((int32_t)r[4 * kk + 2 * h + 1]) * kInv256;
             if (!SWAP) {
@@ -611,7 +625,7 @@ __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* s
       float2 v[2][4];
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
-        const float2 sq = *reinterpret_cast<const float2*>(sq_s + c * 32 + kk * 8 + lq * 2);
+        const float2 sq = *reinterpret_cast<const float2*>(sq_s + c * 32 + pair_col<QP>(kk, lq));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const float sp = spv[sl * 2 + h];
@@ -628,13 +642,14 @@ __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* s
           uint32_t x[4];
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) x[kk] = pack_pair<OutT>(v[h][kk]);
-          const uint4 y = quad_transpose(x, lq);
+          // converted tiles: the four pairs are eight consecutive columns already (see qperm)
+          const uint4 y = QP ? make_uint4(x[0], x[1], x[2], x[3]) : quad_transpose(x, lq);
           if (prow < ti.p_lim)
             *reinterpret_cast<uint4*>(out + (long long)prow * p.ldc + ti.q0 + col_base + c * 32 + lq * 8) = y;
         } else if (prow < ti.p_lim) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            store_pair<OutT, SWAP>(out, p.ldc, prow, ti.q0 + col_base + c * 32 + kk * 8 + lq * 2, ti.q_lim,
+            store_pair<OutT, SWAP>(out, p.ldc, prow, ti.q0 + col_base + c * 32 + pair_col<QP>(kk, lq), ti.q_lim,
                                    v[h][kk], pair_ok);
         }
       }
@@ -993,11 +1008,21 @@ w4a4_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ C
       }
     } else if (p.epi_mode == EPI_CHANNEL) {
       if (p.out_dtype == I4TC_FP16) {
-        if (p.swap) epilogue_channel<BN, __half, true, CG, EW>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
-        else epilogue_channel<BN, __half, false, CG, EW>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        if (p.i8_operands) {
+          if (p.swap) epilogue_channel<BN, __half, true, CG, EW, false>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+          else epilogue_channel<BN, __half, false, CG, EW, false>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        } else {
+          if (p.swap) epilogue_channel<BN, __half, true, CG, EW, true>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+          else epilogue_channel<BN, __half, false, CG, EW, true>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        }
       } else {
-        if (p.swap) epilogue_channel<BN, __nv_bfloat16, true, CG, EW>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
-        else epilogue_channel<BN, __nv_bfloat16, false, CG, EW>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        if (p.i8_operands) {
+          if (p.swap) epilogue_channel<BN, __nv_bfloat16, true, CG, EW, false>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+          else epilogue_channel<BN, __nv_bfloat16, false, CG, EW, false>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        } else {
+          if (p.swap) epilogue_channel<BN, __nv_bfloat16, true, CG, EW, true>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+          else epilogue_channel<BN, __nv_bfloat16, false, CG, EW, true>(p, smem, tmem_base, bar_tm_full, arr_tm_empty, abort_flag);
+        }
       }
     } else {
       epilogue_int32<BN, EW>(p, tmem_base, bar_tm_full, bar_i8_empty, bar_tm_empty, abort_flag);   // CG = 1 only
