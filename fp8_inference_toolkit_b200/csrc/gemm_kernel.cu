@@ -504,6 +504,8 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
       }
     } else {
       const bool pair_ok = ((p.ldc & 1) == 0) && (orows != nullptr || (reinterpret_cast<uintptr_t>(p.out) & 3) == 0);
+      // split-K partial sums, unswapped: a lane's four pairs of a chunk are eight consecutive floats of a row
+      const bool ws_vec = !SWAP && ws != nullptr && ((p.ldc & 3) == 0) && (ti.q0 + col_base + CW <= ti.q_lim);
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
         const int prow = ti.p0 + quad * 32 + 8 * a + lr;
@@ -513,6 +515,14 @@ __device__ __forceinline__ void epilogue_group(const GemmParams& p, uint8_t* sme
         const int orow = (orows != nullptr) ? 0 : prow;
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
+          if (ws_vec) {
+            float4* dst = reinterpret_cast<float4*>(ws + (long long)prow * p.ldc + ti.q0 + col_base + c * 32 + lq * 8);
+            const float2 v0 = f[(a * NCH + c) * 4 + 0], v1 = f[(a * NCH + c) * 4 + 1];
+            const float2 v2 = f[(a * NCH + c) * 4 + 2], v3 = f[(a * NCH + c) * 4 + 3];
+            dst[0] = make_float4(v0.x, v0.y, v1.x, v1.y);
+            dst[1] = make_float4(v2.x, v2.y, v3.x, v3.y);
+            continue;
+          }
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const float2 v = f[(a * NCH + c) * 4 + kk];
@@ -602,10 +612,20 @@ __device__ __forceinline__ void epilogue_channel(const GemmParams& p, uint8_t* s
         // split-K: this work item covers a range of K groups; its integer sums go out as fp32 (exact: below
         // 2^24), element (m, n) at ws[split][m * ldc + n], and a second kernel adds the ranges and scales
         float* ws = p.split_ws + (long long)ti.split * p.ws_stride;
+        // unswapped, converted tiles: a lane's four pairs of a chunk are eight consecutive floats of a row
+        const bool ws_vec = QP && !SWAP && ((p.ldc & 3) == 0) && (ti.q0 + col_base + CW <= ti.q_lim);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int prow = ti.p0 + quad * 32 + 8 * (sl * 2 + h) + lr;
           if (prow >= ti.p_lim) continue;
+          if (ws_vec) {
+            float4* dst = reinterpret_cast<float4*>(ws + (long long)prow * p.ldc + ti.q0 + col_base + c * 32 + lq * 8);
+            dst[0] = make_float4(__int2float_rn((int32_t)r[2 * h]) * kInv256, __int2float_rn((int32_t)r[2 * h + 1]) * kInv256,
+                                 __int2float_rn((int32_t)r[4 + 2 * h]) * kInv256, __int2float_rn((int32_t)r[4 + 2 * h + 1]) * kInv256);
+            dst[1] = make_float4(__int2float_rn((int32_t)r[8 + 2 * h]) * kInv256, __int2float_rn((int32_t)r[8 + 2 * h + 1]) * kInv256,
+                                 __int2float_rn((int32_t)r[12 + 2 * h]) * kInv256, __int2float_rn((int32_t)r[12 + 2 * h + 1]) * kInv256);
+            continue;
+          }
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const int q = ti.q0 + col_base + c * 32 + pair_col<QP>(kk, lq);
