@@ -249,10 +249,11 @@ class ExpertParallelMoE:
 
     ``transport``: ``"nccl"`` exchanges the fixed-size blocks with two ``all_to_all_single`` calls; ``"peer"`` maps
     every rank's receive and return buffers into the others' address space (``torch.distributed._symmetric_memory``)
-    and lets the quantise and return kernels store rows straight into the destination's buffer over NVLink, ordered by
-    device-side flags with bounded waits -- no collective at all, no capacity padding on the wire, and the return
-    rows land in the source's own sorted order; ``"auto"`` (default) takes ``"peer"`` when symmetric memory can be
-    set up for the group and ``"nccl"`` otherwise.
+    and lets the dispatch kernel and the down projection's epilogue store rows straight into the destination's buffer
+    over NVLink, ordered by device-side flags with bounded waits -- no collective at all, no capacity padding on the
+    wire, the return rows land in the source's own sorted order, and the whole call can be recorded as a CUDA graph
+    (``capture``); ``"auto"`` (default) takes ``"peer"`` when symmetric memory can be set up for the group and
+    ``"nccl"`` otherwise.
 
     ``out = layer(x, expert_ids, expert_w)``; afterwards ``layer.overflowed()`` tells whether any rank ran out of
     capacity in a call since the last check (it synchronises and reduces the flag over the ranks), in which case the
